@@ -1,0 +1,161 @@
+/* plz.h -- C ABI of libplz.so: the PalettizedLinear hot path (2-bit palette look-up-table Linear)
+ * on NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - Every pointer is a CUDA device pointer on the current device unless stated otherwise.
+ *   - Every entry point enqueues work on `stream` (a cudaStream_t passed as void*; NULL = legacy
+ *     default stream) and returns without synchronizing. Nothing here allocates device memory:
+ *     outputs and workspaces come from the caller.
+ *   - Return value: 0 on success, a PLZ_ERR_* code otherwise; plz_last_error() gives the text.
+ *     Nothing throws. Launch errors are checked (cudaGetLastError) on every call.
+ *   - Device-side waits are bounded. A kernel that gives up records a code in a per-device status
+ *     word; plz_device_status() synchronizes the device and reads (and clears) it.
+ *   - bf16 matrices are row-major with an explicit row pitch in ELEMENTS; bases and pitches must be
+ *     multiples of 16 bytes (TMA requirement).
+ *
+ * Weight format (plz_weight_t)
+ *   W[n, k] = palette[(n / gs_n) * (K / gs_k) + k / gs_k][ idx[n, k] ],  idx in {0,1,2,3}
+ *   packed: N rows of `packed_pitch` bytes; element k of a row is bits 2*(k%4)..2*(k%4)+1 of byte k/4
+ *           (the bit order of the reference's .idx2 files, scripts/palettize_core.py:31-42).
+ *   palette: bf16, 4 entries per group, groups ordered (n-group major, k-group minor).
+ *   The reference's runtime layout -- one palette per 256 output columns, shared by every input row
+ *   (scripts/qwen_model.py:98-102) -- is gs_n = 256, gs_k = K. One palette per output row and 256
+ *   input columns is gs_n = 1, gs_k = 256.
+ */
+#ifndef PLZ_H_
+#define PLZ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PLZ_OK 0
+#define PLZ_ERR_BAD_SHAPE 1
+#define PLZ_ERR_BAD_ALIGN 2
+#define PLZ_ERR_UNSUPPORTED 3
+#define PLZ_ERR_CUDA 4
+#define PLZ_ERR_WORKSPACE 5
+#define PLZ_ERR_DEVICE_WAIT 6
+#define PLZ_ERR_NULL 7
+#define PLZ_ERR_TOO_LARGE 8
+
+typedef struct plz_weight {
+    int32_t N, K;          /* out features, in features */
+    int32_t gs_n, gs_k;    /* palette group extents along n and k; gs_k % 64 == 0, K % gs_k == 0 */
+    const void* packed;    /* uint8 [N][packed_pitch], 16-byte aligned rows */
+    int64_t packed_pitch;  /* bytes, >= K/4, multiple of 16 */
+    const void* palette;   /* bf16 [(N/gs_n) * (K/gs_k)][4], 8-byte aligned */
+} plz_weight_t;
+
+/* LoRA branch y += (scale * x A^T) B^T.  A: [rank, K] bf16, B: [N, rank] bf16 (both row-major).
+ * rank must be a multiple of 8, at most 64. The reference stores lora_A as (K, rank)
+ * (scripts/qwen_model.py:262-277); its transpose is what goes here. */
+typedef struct plz_lora {
+    int32_t rank;
+    float scale;
+    const void* A; int64_t lda;
+    const void* B; int64_t ldb;
+} plz_lora_t;
+
+/* Index logits: element (n, k, p) at ptr[n * s_n + k * s_k + p * s_p] (strides in elements).
+ * dtype 0 = fp32, 1 = fp16. Interleaved fp32 [N, K, 4]: (4K, 4, 1). The reference's planar
+ * fp16 (4, K, N) (scripts/qwen_model.py:135-143): (1, N, K*N). */
+typedef struct plz_logits {
+    void* ptr;
+    int32_t dtype;
+    int64_t s_n, s_k, s_p;
+} plz_logits_t;
+
+/* Gumbel noise. mode 0: none (g = 0). mode 1: explicit fp32 tensor with its own strides.
+ * mode 2: counter-based, g = gumbel(seed, (k * N + n) * 4 + p) -- the reference's sampler
+ * (scripts/fused_lut_kernel.cu:1245-1256, noise index :1296-1299). */
+typedef struct plz_noise {
+    int32_t mode;
+    uint32_t seed;
+    const float* ptr;
+    int64_t s_n, s_k, s_p;
+} plz_noise_t;
+
+int32_t plz_version(void);
+const char* plz_last_error(void);
+/* Synchronizes the current device, copies the 4-word status {code, where, count, 0} to the HOST
+ * array `out4` (may be NULL) and clears it. Returns PLZ_ERR_DEVICE_WAIT if a kernel gave up. */
+int32_t plz_device_status(uint32_t* out4);
+
+/* ---- formats ---------------------------------------------------------------------------------
+ * Pack unpacked int8/uint8 indices, element (n, k) at src[n * s_n + k * s_k], into `dst`.
+ * Replaces pack_indices_2bit (scripts/palettize_core.py:31-42) as a device kernel; the reference
+ * keeps int8 (K, N) on the GPU (scripts/qwen_model.py:80). */
+int32_t plz_pack_indices(const void* src, int64_t s_n, int64_t s_k, int32_t N, int32_t K, void* dst,
+                         int64_t pitch, void* stream);
+/* Inverse of plz_pack_indices (unpack_indices_2bit, scripts/palettize_core.py:45-56). */
+int32_t plz_unpack_indices(const void* src, int64_t pitch, int32_t N, int32_t K, void* dst, int64_t s_n,
+                           int64_t s_k, void* stream);
+/* Materialize W as bf16, element (n, k) at dst[n * d_n + k * d_k]. The gather of the reference's
+ * fallback forward (scripts/qwen_model.py:183-186) / compute_hard_W_kernel
+ * (scripts/triton_hard_forward.py:48). Used by tests to check the decode bit for bit. */
+int32_t plz_dequantize(const plz_weight_t* w, void* dst, int64_t d_n, int64_t d_k, void* stream);
+
+/* ---- forward ---------------------------------------------------------------------------------
+ * y[M, N] = x[M, K] W^T (+ LoRA). Hard forward of PalettizedLinear: fused_lut_linear_fwd
+ * (scripts/fused_lut_linear_cuda.py:74-117), fallback scripts/qwen_model.py:183-192, plus
+ * QwenLoRA.forward (scripts/qwen_model.py:291-304) when `lora` is not NULL.
+ * With LoRA, `t` is a caller-provided bf16 [M, rank] workspace (pitch = rank) that receives
+ * scale * x A^T; keep it for plz_lora_bwd. */
+int32_t plz_hard_fwd(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const plz_lora_t* lora,
+                     void* t, void* y, int64_t ldy, void* stream);
+
+/* Same product for 1 <= M <= 64 rows (token decode), written for the HBM roofline of the packed
+ * weights: every SM streams its own range of weight rows exactly once. No LoRA branch. The
+ * reference has no separate small-batch kernel: its hard forward (scripts/qwen_model.py:164-192,
+ * scripts/fused_lut_kernel.cu:309) serves every batch size and reads one byte per weight. */
+int32_t plz_hard_fwd_smallm(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, void* y, int64_t ldy,
+                            void* stream);
+
+/* One pass over the index logits: packed hard indices (argmax over the plain logits, first maximum
+ * wins: scripts/triton_soft_forward.py:160-168) into w->packed (written!), and/or the soft weights
+ * W_soft = softmax((logits + g) / tau) . palette as bf16 at w_soft[n * ws_n + k * ws_k]
+ * (compute_P_W kernels, scripts/fused_lut_kernel.cu:1946-2004; scripts/triton_soft_forward.py:83-181).
+ * Either output may be skipped (want_packed = 0 / w_soft = NULL). */
+int32_t plz_soft_select(const plz_weight_t* w, const plz_logits_t* logits, const plz_noise_t* noise, float tau,
+                        int32_t want_packed, void* w_soft, int64_t ws_n, int64_t ws_k, void* stream);
+
+/* y = x Wd^T (+ LoRA) with a dense bf16 Wd [N, K] (pitch ldw): the soft forward without the
+ * straight-through estimator, y = x W_soft (scripts/fused_lut_linear_cuda.py:239-275). */
+int32_t plz_dense_fwd(const void* Wd, int64_t ldw, int32_t N, int32_t K, const void* x, int64_t ldx, int32_t M,
+                      const plz_lora_t* lora, void* t, void* y, int64_t ldy, void* stream);
+
+/* ---- backward --------------------------------------------------------------------------------
+ * dX[M, K] = dY[M, N] W (+ LoRA: dt = scale * dY B into the bf16 [M, rank] workspace `dt`, then
+ * dX += dt A). fused_lut_linear_bwd_grad_x_tc_kernel (scripts/fused_lut_kernel.cu:551) and
+ * grad_x = grad_y @ W.T (scripts/fused_lut_linear_cuda.py:944). */
+int32_t plz_bwd_dx(const plz_weight_t* w, const void* dY, int64_t lddy, int32_t M, const plz_lora_t* lora,
+                   void* dt, void* dX, int64_t lddx, void* stream);
+int32_t plz_dense_bwd_dx(const void* Wd, int64_t ldw, int32_t N, int32_t K, const void* dY, int64_t lddy,
+                         int32_t M, const plz_lora_t* lora, void* dt, void* dX, int64_t lddx, void* stream);
+
+/* Weight-gradient product dW = x^T dY, never written to memory, fused with the soft backward:
+ *   dLogits[n,k,p] = dW[n,k] * P[p] * (palette[p] - W_soft)   (same dtype/strides as `logits`)
+ *   dPalette[group][p] += sum dW * P[p]                        (fp32, ACCUMULATED: zero it first)
+ * P is recomputed from logits and noise. Either output pointer may be NULL.
+ * grad_W + soft_bwd_elementwise (scripts/fused_lut_linear_cuda.py:952-961,
+ * scripts/fused_lut_kernel.cu:1877-1924; scripts/triton_soft_backward.py:165-325). */
+int32_t plz_bwd_dw_soft(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy,
+                        int32_t M, const plz_logits_t* logits, const plz_noise_t* noise, float tau,
+                        void* dlogits, float* dpalette, void* stream);
+/* Hard-mode palette gradient dPalette[group][idx[n,k]] += dW[n,k] (fp32, accumulated):
+ * fused_lut_linear_bwd_grad_palette_kernel (scripts/fused_lut_kernel.cu:902-1127). */
+int32_t plz_bwd_dw_hard(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy,
+                        int32_t M, float* dpalette, void* stream);
+/* LoRA factor gradients, fp32, ACCUMULATED (zero them first):
+ *   dA[rank, K] += dt^T x,   dB[N, rank] += dY^T t     (t, dt as left by plz_hard_fwd / plz_bwd_dx).
+ * Autograd of scripts/qwen_model.py:300-304. */
+int32_t plz_lora_bwd(const void* x, int64_t ldx, const void* dY, int64_t lddy, const void* t, const void* dt,
+                     int32_t M, int32_t N, int32_t K, int32_t rank, float* dA, float* dB, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PLZ_H_ */

@@ -1,0 +1,377 @@
+// extern "C" entry points of libplz.so (declared and documented in include/plz.h) and the small amount
+// of host state behind them: last-error text, the per-device status word, the tensor-map encoder.
+#include <stdarg.h>
+#include <string.h>
+
+#include "../../include/plz.h"
+#include "plz_launch.h"
+#include "soft_math.cuh"
+
+namespace plz {
+
+// ---- host state ------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+void set_last_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+__device__ StatusWord g_status_word;
+
+StatusWord* device_status_ptr() {
+    static StatusWord* ptrs[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    dev &= 63;
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+        ptrs[dev] = (StatusWord*)p;
+    }
+    return ptrs[dev];
+}
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                   uint32_t box_cols, uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return PLZ_ERR_CUDA; }
+    if (!base) { set_last_error("null matrix pointer"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)base & 15) || ((ld * 2) & 15)) {
+        set_last_error("bf16 matrix base (%p) and row pitch (%llu elements) must be multiples of 16 bytes", base,
+                       (unsigned long long)ld);
+        return PLZ_ERR_BAD_ALIGN;
+    }
+    if (ld < cols) { set_last_error("row pitch %llu < columns %llu", (unsigned long long)ld, (unsigned long long)cols); return PLZ_ERR_BAD_SHAPE; }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed with CUresult %d (rows %llu cols %llu ld %llu box %ux%u)", (int)r,
+                       (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, box_cols, box_rows);
+        return PLZ_ERR_CUDA;
+    }
+    return PLZ_OK;
+}
+
+static int check_weight(const plz_weight_t* w, bool need_packed) {
+    if (!w) { set_last_error("null weight descriptor"); return PLZ_ERR_NULL; }
+    if (w->N <= 0 || w->K <= 0) { set_last_error("weight is empty (N=%d, K=%d)", w->N, w->K); return PLZ_ERR_BAD_SHAPE; }
+    if (w->K % 64) { set_last_error("K=%d must be a multiple of 64", w->K); return PLZ_ERR_BAD_SHAPE; }
+    if (w->N % 8) { set_last_error("N=%d must be a multiple of 8", w->N); return PLZ_ERR_BAD_SHAPE; }
+    if (w->gs_n <= 0 || w->gs_k <= 0 || w->gs_k % 64 || w->K % w->gs_k || w->N % w->gs_n) {
+        set_last_error("palette groups (gs_n=%d, gs_k=%d) must tile (N=%d, K=%d); gs_k %% 64 == 0", w->gs_n, w->gs_k, w->N, w->K);
+        return PLZ_ERR_BAD_SHAPE;
+    }
+    if (need_packed) {
+        if (!w->packed) { set_last_error("null packed indices"); return PLZ_ERR_NULL; }
+        if (w->packed_pitch < w->K / 4 || (w->packed_pitch & 15) || ((uintptr_t)w->packed & 15)) {
+            set_last_error("packed rows must be 16-byte aligned with pitch >= K/4 (pitch=%lld)", (long long)w->packed_pitch);
+            return PLZ_ERR_BAD_ALIGN;
+        }
+    }
+    if (!w->palette) { set_last_error("null palette"); return PLZ_ERR_NULL; }
+    if ((uintptr_t)w->palette & 7) { set_last_error("palette must be 8-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    return PLZ_OK;
+}
+
+static int check_lora(const plz_lora_t* l, const void* ws) {
+    if (!l) return PLZ_OK;
+    if (l->rank <= 0 || l->rank > 64 || l->rank % 8) { set_last_error("LoRA rank %d must be a multiple of 8 in [8, 64]", l->rank); return PLZ_ERR_BAD_SHAPE; }
+    if (!l->A || !l->B) { set_last_error("null LoRA factor"); return PLZ_ERR_NULL; }
+    if (!ws) { set_last_error("LoRA needs the [M, rank] bf16 workspace"); return PLZ_ERR_WORKSPACE; }
+    if ((uintptr_t)ws & 15) { set_last_error("LoRA workspace must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    return PLZ_OK;
+}
+
+// t = scale * x A^T  (bf16 [M, rank])
+static int lora_down(const plz_lora_t* l, const void* x, long long ldx, int M, int K, void* t, cudaStream_t s) {
+    LutGemmArgs g = {};
+    g.bmode = B_TMA_K; g.M = M; g.J = l->rank; g.R = K;
+    g.A = x; g.lda = ldx; g.Bdense = l->A; g.ldb = l->lda;
+    g.out = t; g.ld_out = l->rank; g.alpha = l->scale;
+    return launch_lut_gemm(g, s);
+}
+// dt = scale * dY B  (bf16 [M, rank]); reduction over N, B is [N, rank] -> MN-major operand
+static int lora_up_bwd(const plz_lora_t* l, const void* dY, long long lddy, int M, int N, void* dt, cudaStream_t s) {
+    if (N % 64) { set_last_error("LoRA backward needs N %% 64 == 0 (N=%d)", N); return PLZ_ERR_BAD_SHAPE; }
+    LutGemmArgs g = {};
+    g.bmode = B_TMA_MN; g.M = M; g.J = l->rank; g.R = N;
+    g.A = dY; g.lda = lddy; g.Bdense = l->B; g.ldb = l->ldb;
+    g.out = dt; g.ld_out = l->rank; g.alpha = l->scale;
+    return launch_lut_gemm(g, s);
+}
+
+}  // namespace plz
+
+using namespace plz;
+
+extern "C" {
+
+int32_t plz_version(void) { return 100; }
+const char* plz_last_error(void) { return g_err; }
+
+int32_t plz_device_status(uint32_t* out4) {
+    StatusWord* d = device_status_ptr();
+    if (!d) { set_last_error("no CUDA device / status word unavailable"); return PLZ_ERR_CUDA; }
+    PLZ_CUDA_CHECK(cudaDeviceSynchronize());
+    StatusWord h;
+    PLZ_CUDA_CHECK(cudaMemcpy(&h, d, sizeof(h), cudaMemcpyDeviceToHost));
+    if (out4) { out4[0] = h.code; out4[1] = h.where; out4[2] = h.count; out4[3] = 0; }
+    if (h.code != 0) {
+        PLZ_CUDA_CHECK(cudaMemset(d, 0, sizeof(h)));
+        set_last_error("a kernel gave up waiting: code %u, block %u, role %u, %u reports", h.code, h.where & 0xFFFFFFu,
+                       h.where >> 24, h.count);
+        return PLZ_ERR_DEVICE_WAIT;
+    }
+    return PLZ_OK;
+}
+
+int32_t plz_pack_indices(const void* src, int64_t s_n, int64_t s_k, int32_t N, int32_t K, void* dst, int64_t pitch,
+                         void* stream) {
+    if (N < 0 || K < 0) { set_last_error("negative extent"); return PLZ_ERR_BAD_SHAPE; }
+    if (N == 0 || K == 0) return PLZ_OK;
+    if (!src || !dst) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (pitch < (K + 3) / 4) { set_last_error("pitch %lld < K/4", (long long)pitch); return PLZ_ERR_BAD_SHAPE; }
+    return launch_pack_indices(src, s_n, s_k, N, K, dst, pitch, (cudaStream_t)stream);
+}
+
+int32_t plz_unpack_indices(const void* src, int64_t pitch, int32_t N, int32_t K, void* dst, int64_t s_n, int64_t s_k,
+                           void* stream) {
+    if (N < 0 || K < 0) { set_last_error("negative extent"); return PLZ_ERR_BAD_SHAPE; }
+    if (N == 0 || K == 0) return PLZ_OK;
+    if (!src || !dst) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    return launch_unpack_indices(src, pitch, N, K, dst, s_n, s_k, (cudaStream_t)stream);
+}
+
+int32_t plz_dequantize(const plz_weight_t* w, void* dst, int64_t d_n, int64_t d_k, void* stream) {
+    int rc = check_weight(w, true);
+    if (rc) return rc;
+    if (!dst) { set_last_error("null output"); return PLZ_ERR_NULL; }
+    return launch_dequant(w->packed, w->packed_pitch, w->palette, w->gs_n, w->gs_k, w->N, w->K, dst, d_n, d_k,
+                          (cudaStream_t)stream);
+}
+
+int32_t plz_hard_fwd(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const plz_lora_t* lora, void* t,
+                     void* y, int64_t ldy, void* stream) {
+    int rc = check_weight(w, true);
+    if (rc) return rc;
+    if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !y) { set_last_error("null activation pointer"); return PLZ_ERR_NULL; }
+    if ((rc = check_lora(lora, t))) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (lora && (rc = lora_down(lora, x, ldx, M, w->K, t, s))) return rc;
+    LutGemmArgs g = {};
+    g.bmode = B_DECODE_K; g.M = M; g.J = w->N; g.R = w->K;
+    g.A = x; g.lda = ldx;
+    g.packed = w->packed; g.packed_pitch = w->packed_pitch; g.palette = w->palette;
+    g.gs_n = w->gs_n; g.gs_k = w->gs_k; g.Wn = w->N; g.Wk = w->K;
+    if (lora) { g.r2 = lora->rank; g.A2 = t; g.lda2 = lora->rank; g.B2 = lora->B; g.ldb2 = lora->ldb; }
+    g.out = y; g.ld_out = ldy; g.alpha = 1.0f;
+    return launch_lut_gemm(g, s);
+}
+
+int32_t plz_hard_fwd_smallm(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, void* y, int64_t ldy,
+                            void* stream) {
+    int rc = check_weight(w, true);
+    if (rc) return rc;
+    if (M < 0 || M > 64) { set_last_error("plz_hard_fwd_smallm handles 0 <= M <= 64 (M=%d); use plz_hard_fwd", M); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !y) { set_last_error("null activation pointer"); return PLZ_ERR_NULL; }
+    GemvArgs g = {};
+    g.M = M; g.N = w->N; g.K = w->K; g.x = x; g.ldx = ldx;
+    g.packed = w->packed; g.packed_pitch = w->packed_pitch; g.palette = w->palette;
+    g.gs_n = w->gs_n; g.gs_k = w->gs_k; g.out = y; g.ld_out = ldy;
+    int dev = 0, sms = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    g.sm_count = sms;
+    return launch_lut_gemv(g, (cudaStream_t)stream);
+}
+
+int32_t plz_dense_fwd(const void* Wd, int64_t ldw, int32_t N, int32_t K, const void* x, int64_t ldx, int32_t M,
+                      const plz_lora_t* lora, void* t, void* y, int64_t ldy, void* stream) {
+    if (N <= 0 || K <= 0 || M < 0 || K % 64 || N % 8) { set_last_error("dense_fwd: bad shape M=%d N=%d K=%d", M, N, K); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!Wd || !x || !y) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    int rc;
+    if ((rc = check_lora(lora, t))) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (lora && (rc = lora_down(lora, x, ldx, M, K, t, s))) return rc;
+    LutGemmArgs g = {};
+    g.bmode = B_TMA_K; g.M = M; g.J = N; g.R = K;
+    g.A = x; g.lda = ldx; g.Bdense = Wd; g.ldb = ldw;
+    if (lora) { g.r2 = lora->rank; g.A2 = t; g.lda2 = lora->rank; g.B2 = lora->B; g.ldb2 = lora->ldb; }
+    g.out = y; g.ld_out = ldy; g.alpha = 1.0f;
+    return launch_lut_gemm(g, s);
+}
+
+int32_t plz_soft_select(const plz_weight_t* w, const plz_logits_t* logits, const plz_noise_t* noise, float tau,
+                        int32_t want_packed, void* w_soft, int64_t ws_n, int64_t ws_k, void* stream) {
+    int rc = check_weight(w, want_packed != 0);
+    if (rc) return rc;
+    if (!logits || !logits->ptr) { set_last_error("null logits"); return PLZ_ERR_NULL; }
+    if (!(tau > 0.f)) { set_last_error("tau must be positive"); return PLZ_ERR_BAD_SHAPE; }
+    SelectParams p = {};
+    p.logits = logits->ptr; p.ls_n = logits->s_n; p.ls_k = logits->s_k; p.ls_p = logits->s_p;
+    if (noise) { p.noise = noise->ptr; p.ns_n = noise->s_n; p.ns_k = noise->s_k; p.ns_p = noise->s_p; p.noise_mode = noise->mode; p.seed = noise->seed; }
+    p.inv_tau = 1.0f / tau;
+    p.palette = (const __nv_bfloat16*)w->palette; p.gs_n = w->gs_n; p.gs_k = w->gs_k; p.n_kgroups = w->K / w->gs_k;
+    p.N = w->N; p.K = w->K;
+    p.packed = want_packed ? (uint8_t*)const_cast<void*>(w->packed) : nullptr; p.pitch = w->packed_pitch;
+    p.w_soft = (__nv_bfloat16*)w_soft; p.ws_n = ws_n; p.ws_k = ws_k;
+    if (!p.packed && !p.w_soft) return PLZ_OK;
+    return launch_soft_select(p, logits->dtype == 1, (cudaStream_t)stream);
+}
+
+int32_t plz_bwd_dx(const plz_weight_t* w, const void* dY, int64_t lddy, int32_t M, const plz_lora_t* lora, void* dt,
+                   void* dX, int64_t lddx, void* stream) {
+    int rc = check_weight(w, true);
+    if (rc) return rc;
+    if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (w->N % 64) { set_last_error("bwd_dx needs N %% 64 == 0 (N=%d)", w->N); return PLZ_ERR_BAD_SHAPE; }
+    if (!dY || !dX) { set_last_error("null gradient pointer"); return PLZ_ERR_NULL; }
+    if ((rc = check_lora(lora, dt))) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (lora && (rc = lora_up_bwd(lora, dY, lddy, M, w->N, dt, s))) return rc;
+    LutGemmArgs g = {};
+    g.bmode = B_DECODE_MN; g.M = M; g.J = w->K; g.R = w->N;
+    g.A = dY; g.lda = lddy;
+    g.packed = w->packed; g.packed_pitch = w->packed_pitch; g.palette = w->palette;
+    g.gs_n = w->gs_n; g.gs_k = w->gs_k; g.Wn = w->N; g.Wk = w->K;
+    if (lora) { g.r2 = lora->rank; g.A2 = dt; g.lda2 = lora->rank; g.B2 = lora->A; g.ldb2 = lora->lda; }
+    g.out = dX; g.ld_out = lddx; g.alpha = 1.0f;
+    return launch_lut_gemm(g, s);
+}
+
+int32_t plz_dense_bwd_dx(const void* Wd, int64_t ldw, int32_t N, int32_t K, const void* dY, int64_t lddy, int32_t M,
+                         const plz_lora_t* lora, void* dt, void* dX, int64_t lddx, void* stream) {
+    if (N <= 0 || K <= 0 || M < 0 || N % 64 || K % 8) { set_last_error("dense_bwd_dx: bad shape M=%d N=%d K=%d", M, N, K); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!Wd || !dY || !dX) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    int rc;
+    if ((rc = check_lora(lora, dt))) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (lora && (rc = lora_up_bwd(lora, dY, lddy, M, N, dt, s))) return rc;
+    LutGemmArgs g = {};
+    g.bmode = B_TMA_MN; g.M = M; g.J = K; g.R = N;
+    g.A = dY; g.lda = lddy; g.Bdense = Wd; g.ldb = ldw;
+    if (lora) { g.r2 = lora->rank; g.A2 = dt; g.lda2 = lora->rank; g.B2 = lora->A; g.ldb2 = lora->lda; }
+    g.out = dX; g.ld_out = lddx; g.alpha = 1.0f;
+    return launch_lut_gemm(g, s);
+}
+
+static int bwd_dw_common(int epi, const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy,
+                         int32_t M, const plz_logits_t* logits, const plz_noise_t* noise, float tau, void* dlogits,
+                         float* dpalette, void* stream) {
+    int rc = check_weight(w, epi == EPI_HARD);
+    if (rc) return rc;
+    if (M <= 0) { if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; } return PLZ_OK; }
+    if (!x || !dY) { set_last_error("null activation pointer"); return PLZ_ERR_NULL; }
+    TnArgs a = {};
+    a.epi = epi; a.M = M;
+    // Which of (n, k) runs along the TMEM lanes is chosen so that lanes walk the contiguous axis of
+    // the logits: k for interleaved [N, K, 4], n for planar (4, K, N). The hard epilogue reads one
+    // byte per element and follows the palette grouping instead.
+    bool rows_are_k;
+    if (epi == EPI_SOFT) {
+        if (!logits || !logits->ptr) { set_last_error("null logits"); return PLZ_ERR_NULL; }
+        rows_are_k = logits->s_k < logits->s_n;
+    } else {
+        rows_are_k = (w->gs_n == 1);
+    }
+    a.rows_are_k = rows_are_k ? 1 : 0;
+    if (rows_are_k) { a.I = w->K; a.J = w->N; a.P = x; a.ldp = ldx; a.Q = dY; a.ldq = lddy; }
+    else { a.I = w->N; a.J = w->K; a.P = dY; a.ldp = lddy; a.Q = x; a.ldq = ldx; }
+    if (epi == EPI_SOFT) {
+        a.logits = logits->ptr; a.dlogits = dlogits; a.logits_f16 = logits->dtype == 1;
+        a.ls_p = logits->s_p;
+        a.ls_row = rows_are_k ? logits->s_k : logits->s_n;
+        a.ls_col = rows_are_k ? logits->s_n : logits->s_k;
+        if (noise) {
+            a.noise_mode = noise->mode; a.noise = noise->ptr; a.seed = noise->seed; a.ns_p = noise->s_p;
+            a.ns_row = rows_are_k ? noise->s_k : noise->s_n;
+            a.ns_col = rows_are_k ? noise->s_n : noise->s_k;
+        }
+        a.hashN = w->N;
+        a.tau = tau;
+    } else {
+        a.tau = 1.0f;
+    }
+    a.palette = w->palette; a.dpalette = dpalette;
+    a.gs_n = w->gs_n; a.gs_k = w->gs_k; a.n_kgroups = w->K / w->gs_k;
+    a.packed = w->packed; a.packed_pitch = w->packed_pitch;
+    int dev = 0, sms = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    a.sm_count = sms;
+    return launch_tn_gemm(a, (cudaStream_t)stream);
+}
+
+int32_t plz_bwd_dw_soft(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M,
+                        const plz_logits_t* logits, const plz_noise_t* noise, float tau, void* dlogits,
+                        float* dpalette, void* stream) {
+    if (!(tau > 0.f)) { set_last_error("tau must be positive"); return PLZ_ERR_BAD_SHAPE; }
+    return bwd_dw_common(EPI_SOFT, w, x, ldx, dY, lddy, M, logits, noise, tau, dlogits, dpalette, stream);
+}
+
+int32_t plz_bwd_dw_hard(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M,
+                        float* dpalette, void* stream) {
+    if (!dpalette) { set_last_error("null dpalette"); return PLZ_ERR_NULL; }
+    return bwd_dw_common(EPI_HARD, w, x, ldx, dY, lddy, M, nullptr, nullptr, 1.0f, nullptr, dpalette, stream);
+}
+
+int32_t plz_lora_bwd(const void* x, int64_t ldx, const void* dY, int64_t lddy, const void* t, const void* dt, int32_t M,
+                     int32_t N, int32_t K, int32_t rank, float* dA, float* dB, void* stream) {
+    if (M < 0 || N <= 0 || K <= 0 || rank <= 0 || rank > 64 || rank % 8) { set_last_error("lora_bwd: bad shape"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !dY || !t || !dt) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    int dev = 0, sms = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc;
+    if (dA) {
+        // D[r, k] = sum_m dt[m, r] x[m, k]  -> dA[r * K + k]
+        TnArgs a = {};
+        a.epi = EPI_STORE; a.M = M; a.I = rank; a.J = K;
+        a.P = dt; a.ldp = rank; a.Q = x; a.ldq = ldx;
+        a.out = dA; a.out_si = K; a.out_sj = 1; a.alpha = 1.0f; a.out_I = rank; a.out_J = K;
+        const int tiles = (K + 255) / 256;
+        a.splits = (sms + tiles - 1) / tiles; a.sm_count = sms;
+        if ((rc = launch_tn_gemm(a, s))) return rc;
+    }
+    if (dB) {
+        // D[r, n] = sum_m t[m, r] dY[m, n] -> dB[n * rank + r]
+        TnArgs a = {};
+        a.epi = EPI_STORE; a.M = M; a.I = rank; a.J = N;
+        a.P = t; a.ldp = rank; a.Q = dY; a.ldq = lddy;
+        a.out = dB; a.out_si = 1; a.out_sj = rank; a.alpha = 1.0f; a.out_I = rank; a.out_J = N;
+        const int tiles = (N + 255) / 256;
+        a.splits = (sms + tiles - 1) / tiles; a.sm_count = sms;
+        if ((rc = launch_tn_gemm(a, s))) return rc;
+    }
+    return PLZ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,289 @@
+// Small-M hard forward (token decode): y[M, N] = x[M, K] W^T for M <= 64, bound by the HBM read of the
+// packed 2-bit weights (N*K/4 bytes of indices + the palettes), each read exactly once.
+//
+// One CTA per SM owns a contiguous range of weight rows (any length up to 128, so that N rows split
+// evenly over the SMs whatever N is). At entry every thread issues cp.async copies for the CTA's
+// whole block of packed indices -- tens of KB in flight per SM, which is what it takes to cover
+// HBM latency at full bandwidth -- in one commit group per 256 input columns. As each group lands,
+// the decode warps expand it (byte permutes against the 4-entry palettes) into the swizzled A tile of
+// a tcgen05 MMA whose B operand is the TMA-loaded activation tile: D[n, m] += W[n, k] x[m, k]
+// ("swap-AB": the 128 TMEM lanes are weight rows, the <= 64 columns are tokens). The tensor core
+// does the multiply-accumulate for every token at once, so the cost per weight does not grow with M.
+//
+// Replaces the reference's hard forward at decode batch sizes (scripts/qwen_model.py:164-192 dispatching to
+// fused_lut_linear_fwd_tc_kernel, scripts/fused_lut_kernel.cu:309, which reads 1 byte per weight).
+#include "plz_launch.h"
+
+namespace plz {
+
+struct GemvParams {
+    int M, N, K;
+    int mpad;       // 16, 32 or 64: MMA N extent
+    const uint8_t* packed; long long packed_pitch;
+    const __nv_bfloat16* palette; int gs_n, gs_k, n_kgroups;
+    __nv_bfloat16* out; long long ld_out;
+    uint32_t idx_bytes;  // shared-memory bytes reserved for the packed block (rows_max * K/4, 16-aligned)
+    uint32_t pal_bytes;  // shared-memory bytes reserved for palettes (rows_max * n_kgroups_per_row * 8)
+    StatusWord* status;
+};
+
+constexpr int kGvThreads = 320;
+constexpr int kGvStages = 4;
+constexpr uint32_t kGvABytes = 128 * 64 * 2;
+constexpr uint32_t kGvBBytes = 64 * 64 * 2;
+constexpr uint32_t kGvStageBytes = kGvABytes + kGvBBytes;
+constexpr int kGvMaxGroups = 64;  // commit groups (256 input columns each): K <= 16384
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// wait until at most `n` of this thread's most recent commit groups are pending (n runtime, <= 63)
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+    switch (n) {
+#define PLZ_CASE(i) case i: asm volatile("cp.async.wait_group " #i ";" ::: "memory"); break;
+        PLZ_CASE(0) PLZ_CASE(1) PLZ_CASE(2) PLZ_CASE(3) PLZ_CASE(4) PLZ_CASE(5) PLZ_CASE(6) PLZ_CASE(7)
+        PLZ_CASE(8) PLZ_CASE(9) PLZ_CASE(10) PLZ_CASE(11) PLZ_CASE(12) PLZ_CASE(13) PLZ_CASE(14) PLZ_CASE(15)
+        PLZ_CASE(16) PLZ_CASE(17) PLZ_CASE(18) PLZ_CASE(19) PLZ_CASE(20) PLZ_CASE(21) PLZ_CASE(22) PLZ_CASE(23)
+        PLZ_CASE(24) PLZ_CASE(25) PLZ_CASE(26) PLZ_CASE(27) PLZ_CASE(28) PLZ_CASE(29) PLZ_CASE(30) PLZ_CASE(31)
+        PLZ_CASE(32) PLZ_CASE(33) PLZ_CASE(34) PLZ_CASE(35) PLZ_CASE(36) PLZ_CASE(37) PLZ_CASE(38) PLZ_CASE(39)
+        PLZ_CASE(40) PLZ_CASE(41) PLZ_CASE(42) PLZ_CASE(43) PLZ_CASE(44) PLZ_CASE(45) PLZ_CASE(46) PLZ_CASE(47)
+        PLZ_CASE(48) PLZ_CASE(49) PLZ_CASE(50) PLZ_CASE(51) PLZ_CASE(52) PLZ_CASE(53) PLZ_CASE(54) PLZ_CASE(55)
+        PLZ_CASE(56) PLZ_CASE(57) PLZ_CASE(58) PLZ_CASE(59) PLZ_CASE(60) PLZ_CASE(61) PLZ_CASE(62) PLZ_CASE(63)
+#undef PLZ_CASE
+        default: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    }
+}
+
+__global__ void __launch_bounds__(kGvThreads, 1)
+lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    // layout: [stages][A | B] | packed block | palettes | barriers
+    const uint32_t idx_off = kGvStages * kGvStageBytes;
+    const uint32_t pal_off = idx_off + p.idx_bytes;
+    const uint32_t bar_off = pal_off + p.pal_bytes;
+    const uint32_t bar_base = base + bar_off;
+    auto full_a = [&](int s) { return bar_base + 8u * s; };
+    auto full_b = [&](int s) { return bar_base + 8u * (kGvStages + s); };
+    auto empty = [&](int s) { return bar_base + 8u * (2 * kGvStages + s); };
+    const uint32_t accum_full = bar_base + 8u * (3 * kGvStages);
+    const uint32_t grp_ready = bar_base + 8u * (3 * kGvStages + 1);  // all decode threads' copies of a group landed
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + bar_off + 8 * (3 * kGvStages + 2));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_begin = (int)(((long long)blockIdx.x * p.N) / gridDim.x);
+    const int n_end = (int)(((long long)(blockIdx.x + 1) * p.N) / gridDim.x);
+    const int rows = n_end - n_begin;  // <= 128 by construction of the grid
+    const int nkb = p.K / 64;
+    const int kb_per_grp = 4;          // 256 input columns per commit group
+    const int n_grp = (nkb + kb_per_grp - 1) / kb_per_grp;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGvStages; ++s) {
+            mbar_init(full_a(s), 1);
+            mbar_init(full_b(s), 8);
+            mbar_init(empty(s), 1);
+        }
+        mbar_init(accum_full, 1);
+        mbar_init(grp_ready, 256);
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmX);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_slot), 64);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (rows > 0) {
+        if (warp == 0) {
+            // ---------------------------------------------------------- TMA producer: activation tiles
+            if (lane == 0) {
+                int last_fill[kGvStages];
+                for (int s = 0; s < kGvStages; ++s) last_fill[s] = -1;
+                bool ok = true;
+                const uint32_t bytes = (uint32_t)p.mpad * 128u;
+                for (int it = 0; it < nkb && ok; ++it) {
+                    const int s = it % kGvStages;
+                    const uint32_t ph = (it / kGvStages) & 1;
+                    ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 0);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(full_a(s), bytes);
+                    tma_load_2d(base + s * kGvStageBytes + kGvABytes, &tmX, full_a(s), it * 64, 0);
+                    last_fill[s] = it;
+                }
+                if (!ok) {
+                    for (int s = 0; s < kGvStages; ++s) {
+                        if (last_fill[s] < 0) continue;
+                        const uint32_t ph = (last_fill[s] / kGvStages) & 1;
+                        const uint64_t t0 = globaltimer_ns();
+                        while (!mbar_try_wait(full_a(s), ph)) {
+                            if (globaltimer_ns() - t0 > 100000000ull) {
+                                report(p.status, ST_TIMEOUT_DRAIN, 0);
+                                break;
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // ---------------------------------------------------------- MMA issuer
+            if (lane == 0) {
+                const uint32_t idesc = make_idesc(128, p.mpad, 0, 0);
+                bool ok = true;
+                for (int it = 0; it < nkb && ok; ++it) {
+                    const int s = it % kGvStages;
+                    const uint32_t ph = (it / kGvStages) & 1;
+                    ok = mbar_wait(full_a(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
+                    if (ok) ok = mbar_wait(full_b(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 2);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t sW = base + s * kGvStageBytes;  // decoded weights: MMA operand A
+                    const uint32_t sX = sW + kGvABytes;            // activations: MMA operand B
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        umma_bf16(tmem_base, make_sdesc(sW + ks * 32u, 16u, 1024u), make_sdesc(sX + ks * 32u, 16u, 1024u),
+                                  idesc, (it > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty(s));
+                }
+                if (ok) umma_commit(accum_full);
+            }
+        } else {
+            // ---------------------------------------------------------- decode warps
+            const int t = threadIdx.x - 64;
+            const uint32_t s_idx = base + idx_off;  // [kb][row][16 bytes]
+            const uint32_t s_pal = base + pal_off;  // [kgroup][row][8 bytes]
+            const int kg_per_row = (p.K + p.gs_k - 1) / p.gs_k;
+            // 1) put the whole packed block (and the palettes) in flight
+            for (int u = t; u < rows * kg_per_row; u += 256) {
+                const int r = u % rows, kg = u / rows;
+                const long long g = (long long)((n_begin + r) / p.gs_n) * p.n_kgroups + kg;
+                cp_async8(s_pal + (uint32_t)(kg * rows + r) * 8u, p.palette + g * 4);
+            }
+            for (int grp = 0; grp < n_grp; ++grp) {
+                const int kb0 = grp * kb_per_grp;
+                const int nb = (nkb - kb0 < kb_per_grp) ? (nkb - kb0) : kb_per_grp;
+                for (int u = t; u < rows * nb; u += 256) {
+                    const int r = u / nb, j = u % nb;  // consecutive threads: consecutive 16 bytes of one row
+                    cp_async16(s_idx + (uint32_t)((kb0 + j) * rows + r) * 16u,
+                               p.packed + (long long)(n_begin + r) * p.packed_pitch + (kb0 + j) * 16);
+                }
+                cp_async_commit();
+            }
+            // 2) decode group by group
+            bool ok = true;
+            const int units = rows * 4;  // (row, 16-column word) per 64-column block
+            for (int it = 0; it < nkb && ok; ++it) {
+                if (it % kb_per_grp == 0) {
+                    const int grp = it / kb_per_grp;
+                    cp_async_wait_pending(n_grp - 1 - grp);
+                    mbar_arrive(grp_ready);  // once all 256 have arrived, every thread's copies are visible
+                    ok = mbar_wait(grp_ready, grp & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 5);
+                    if (!ok) break;
+                }
+                const int s = it % kGvStages;
+                const uint32_t ph = (it / kGvStages) & 1;
+                ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 3);
+                if (!ok) break;
+                uint8_t* sW = smem + s * kGvStageBytes;
+                const int kg = (it * 64) / p.gs_k;
+                for (int u = t; u < units; u += 256) {
+                    const int r = u >> 2, w = u & 3;
+                    const uint32_t word = *reinterpret_cast<const uint32_t*>(smem + idx_off + (uint32_t)(it * rows + r) * 16u + w * 4u);
+                    const uint2 praw = *reinterpret_cast<const uint2*>(smem + pal_off + (uint32_t)(kg * rows + r) * 8u);
+                    const PalRegs pal = pal_split(praw.x, praw.y);
+                    uint32_t o[8];
+                    decode16(word, pal, o);
+                    uint8_t* row = sW + r * 128;
+                    *reinterpret_cast<uint4*>(row + (((2 * w) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(row + (((2 * w + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_b(s));
+            }
+            if (!ok) cp_async_wait_pending(0);
+            // 3) epilogue: warps 2..5 cover the 128 TMEM lanes (weight rows); columns are tokens
+            if (warp < 6) {
+                if (ok) ok = mbar_wait(accum_full, 0, abort_flag, p.status, ST_TIMEOUT_ACCUM, 4);
+                if (ok) {
+                    tc_fence_after_sync();
+                    const int lane_group = warp & 3;
+                    const int r = lane_group * 32 + lane;
+                    for (int c0 = 0; c0 < p.mpad; c0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + c0, v);
+                        if (r < rows) {
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) {
+                                const int m = c0 + c;
+                                if (m < p.M) p.out[(long long)m * p.ld_out + n_begin + r] = __float2bfloat16_rn(__uint_as_float(v[c]));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 64);
+    }
+}
+
+int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream) {
+    if (a.M <= 0 || a.M > 64) { set_last_error("small-M forward handles 1 <= M <= 64 (M=%d)", a.M); return PLZ_ERR_BAD_SHAPE; }
+    if (a.K % 64 || a.K / 256 + 1 > kGvMaxGroups) { set_last_error("small-M forward needs K %% 64 == 0 and K <= 16128 (K=%d)", a.K); return PLZ_ERR_BAD_SHAPE; }
+    CUtensorMap tmX;
+    const int mpad = a.M <= 16 ? 16 : (a.M <= 32 ? 32 : 64);
+    int rc;
+    if ((rc = make_tmap_bf16(&tmX, a.x, a.M, a.K, a.ldx, 64, mpad))) return rc;
+    // grid: one CTA per SM unless a CTA's packed block would not fit in shared memory or exceed 128 rows
+    const int row_bytes = a.K / 4;
+    const int kg_per_row = (a.K + a.gs_k - 1) / a.gs_k;
+    const uint32_t budget = 100 * 1024;
+    int max_rows = (int)(budget / (uint32_t)(row_bytes + kg_per_row * 8));
+    if (max_rows > 128) max_rows = 128;
+    if (max_rows < 1) { set_last_error("small-M forward: K=%d too large for shared memory", a.K); return PLZ_ERR_TOO_LARGE; }
+    int sms = a.sm_count > 0 ? a.sm_count : 148;
+    int grid = sms;
+    if ((a.N + grid - 1) / grid > max_rows) grid = (a.N + max_rows - 1) / max_rows;
+    if (grid > a.N) grid = a.N;
+    const int rows_max = (a.N + grid - 1) / grid;
+    GemvParams p = {};
+    p.M = a.M; p.N = a.N; p.K = a.K; p.mpad = mpad;
+    p.packed = (const uint8_t*)a.packed; p.packed_pitch = a.packed_pitch;
+    p.palette = (const __nv_bfloat16*)a.palette; p.gs_n = a.gs_n; p.gs_k = a.gs_k; p.n_kgroups = a.K / a.gs_k;
+    p.out = (__nv_bfloat16*)a.out; p.ld_out = a.ld_out;
+    p.idx_bytes = (uint32_t)(rows_max * row_bytes + 15) & ~15u;
+    p.pal_bytes = (uint32_t)(rows_max * kg_per_row * 8 + 15) & ~15u;
+    p.status = device_status_ptr();
+    const uint32_t smem = kGvStages * kGvStageBytes + p.idx_bytes + p.pal_bytes + 256 + 1024;
+    static int attr_smem[64] = {};
+    int dev = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    if (attr_smem[dev & 63] < (int)smem) {
+        PLZ_CUDA_CHECK(cudaFuncSetAttribute(lut_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_smem[dev & 63] = 227 * 1024;
+    }
+    lut_gemv_kernel<<<grid, kGvThreads, smem, stream>>>(tmX, p);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
+}  // namespace plz

@@ -1,0 +1,345 @@
+// lut_gemm: D[M, J] = alpha * ( A[M, R] * B(R, J) (+ A2[M, R2] * B2(R2, J)) ), bf16 in, fp32 accumulate
+// in TMEM, bf16 out, on the sm_100a tensor cores (tcgen05.mma, cta_group::1, 128 x 256 x 16).
+//
+// A always arrives by TMA (row-major, reduction index contiguous: the activations x or the
+// upstream gradient dY). B is the palettized weight matrix W[N, K] and is *produced inside the
+// kernel*: eight decode warps read the packed 2-bit indices and the 4-entry bf16 palettes from
+// global memory and write bf16 tiles straight into the 128-byte-swizzled shared-memory layout the
+// tensor core reads, so no decoded weight ever exists in HBM.
+//
+//   B_DECODE_K   forward     y  = x  * W^T   reduction over K, B tile rows = n (K-major operand)
+//   B_DECODE_MN  backward    dX = dY * W     reduction over N, B tile rows = n (MN-major operand)
+//   B_TMA_K / B_TMA_MN       same two products with a dense bf16 W (soft weights, LoRA factors)
+//
+// The optional second product (A2, B2) is one extra 64-wide reduction block appended to the main
+// loop: the LoRA branch y += (s x A^T) B^T, or dX += dt A, accumulated into the same TMEM tile.
+//
+// Replaces, in the reference: fused_lut_linear_fwd_tc_kernel (scripts/fused_lut_kernel.cu:309),
+// fused_lut_linear_bwd_grad_x_tc_kernel (:551), the cuBLAS calls of the soft path
+// (scripts/fused_lut_linear_cuda.py:912, :944) and the eager LoRA matmuls (scripts/qwen_model.py:300-304).
+#include "plz_launch.h"
+
+namespace plz {
+
+
+struct LutGemmParams {
+    int M, J, R;         // D is [M, J]; R = reduction length of the main product (multiple of 64)
+    int n_extra;         // 64-wide reduction blocks taken from (A2, B2): 0 or 1
+    const uint8_t* packed;  // W indices, [Wn, packed_pitch] bytes, 4 per byte along K, LSB first
+    long long packed_pitch;
+    const __nv_bfloat16* palette;  // [(n / gs_n) * n_kgroups + k / gs_k][4]
+    int gs_n, gs_k, n_kgroups;
+    int Wn, Wk;          // weight matrix extents (N, K)
+    __nv_bfloat16* out;
+    long long ld_out;
+    float alpha;
+    StatusWord* status;
+};
+
+constexpr int kThreads = 320;       // warp 0: TMA, warp 1: MMA, warps 2..9: decode + epilogue
+constexpr int kDecodeThreads = 256;
+constexpr int kBK = 64;             // reduction elements per stage (128 bytes of bf16)
+constexpr int kBN = 256;            // D columns per CTA
+constexpr uint32_t kBBytes = kBN * kBK * 2;
+
+template <int MT>
+struct Cfg {
+    static constexpr int STAGES = (MT == 2) ? 3 : 4;
+    static constexpr uint32_t A_BYTES = MT * 128 * kBK * 2;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + kBBytes;
+    static constexpr uint32_t TMEM_COLS = MT * 256;
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int MT, int BMODE>
+__global__ void __launch_bounds__(kThreads, 1)
+lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                const LutGemmParams p) {
+    using C = Cfg<MT>;
+    constexpr bool kDecode = (BMODE == B_DECODE_K || BMODE == B_DECODE_MN);
+    constexpr bool kBMn = (BMODE == B_DECODE_MN || BMODE == B_TMA_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const uint32_t bar_base = base + C::STAGES * C::STAGE_BYTES;
+    auto full_a = [&](int s) { return bar_base + 8u * s; };
+    auto full_b = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+    auto empty = [&](int s) { return bar_base + 8u * (2 * C::STAGES + s); };
+    const uint32_t accum_full = bar_base + 8u * (3 * C::STAGES);
+    volatile uint32_t* tmem_slot =
+        reinterpret_cast<volatile uint32_t*>(smem + C::STAGES * C::STAGE_BYTES + 8 * (3 * C::STAGES + 1));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int j0 = blockIdx.x * kBN;
+    const int m0 = blockIdx.y * (128 * MT);
+    const int nkb = p.R / kBK;
+    const int nkb_total = nkb + p.n_extra;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full_a(s), 1);
+            mbar_init(full_b(s), kDecodeThreads / 32);
+            mbar_init(empty(s), 1);
+        }
+        mbar_init(accum_full, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmA);
+        if (!kDecode) tma_prefetch_desc(&tmB);
+        if (p.n_extra) {
+            tma_prefetch_desc(&tmA2);
+            tma_prefetch_desc(&tmB2);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_slot), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int last_fill[C::STAGES];
+            for (int s = 0; s < C::STAGES; ++s) last_fill[s] = -1;
+            bool ok = true;
+            for (int it = 0; it < nkb_total && ok; ++it) {
+                const int s = it % C::STAGES;
+                const uint32_t ph = (it / C::STAGES) & 1;
+                ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 0);
+                if (!ok) break;
+                const uint32_t sA = base + s * C::STAGE_BYTES;
+                const uint32_t sB = sA + C::A_BYTES;
+                const bool extra = it >= nkb;
+                const uint32_t bytes = C::A_BYTES + ((extra || !kDecode) ? kBBytes : 0u);
+                mbar_arrive_expect_tx(full_a(s), bytes);
+                const CUtensorMap* ma = extra ? &tmA2 : &tmA;
+                const CUtensorMap* mb = extra ? &tmB2 : &tmB;
+                const int r0 = (extra ? (it - nkb) : it) * kBK;
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) tma_load_2d(sA + mt * 16384u, ma, full_a(s), r0, m0 + mt * 128);
+                if (extra || !kDecode) {
+                    if (kBMn) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) tma_load_2d(sB + q * 8192u, mb, full_a(s), j0 + q * 64, r0);
+                    } else {
+                        tma_load_2d(sB, mb, full_a(s), r0, j0);
+                    }
+                }
+                last_fill[s] = it;
+            }
+            if (!ok) {
+                // give copies already in flight a bounded chance to land before the CTA exits
+                for (int s = 0; s < C::STAGES; ++s) {
+                    if (last_fill[s] < 0) continue;
+                    const uint32_t ph = (last_fill[s] / C::STAGES) & 1;
+                    const uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(full_a(s), ph)) {
+                        if (globaltimer_ns() - t0 > 100000000ull) {
+                            report(p.status, ST_TIMEOUT_DRAIN, 0);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_main = make_idesc(128, kBN, 0, kBMn ? 1 : 0);
+            bool ok = true;
+            for (int it = 0; it < nkb_total && ok; ++it) {
+                const int s = it % C::STAGES;
+                const uint32_t ph = (it / C::STAGES) & 1;
+                const bool extra = it >= nkb;
+                ok = mbar_wait(full_a(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
+                if (ok && kDecode && !extra)
+                    ok = mbar_wait(full_b(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 2);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t sA = base + s * C::STAGE_BYTES;
+                const uint32_t sB = sA + C::A_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < kBK / 16; ++ks) {
+                    const uint64_t bdesc = kBMn ? make_sdesc(sB + ks * 2048u, 8192u, 1024u)
+                                                : make_sdesc(sB + ks * 32u, 16u, 1024u);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const uint64_t adesc = make_sdesc(sA + mt * 16384u + ks * 32u, 16u, 1024u);
+                        umma_bf16(tmem_base + mt * 256u, adesc, bdesc, idesc_main, (it > 0 || ks > 0) ? 1u : 0u);
+                    }
+                }
+                umma_commit(empty(s));
+            }
+            if (ok) umma_commit(accum_full);
+        }
+    } else {
+        // ------------------------------------------------------------- decode warps, then epilogue
+        const int t = threadIdx.x - 64;
+        bool ok = true;
+        if (kDecode) {
+            // forward: thread owns tile row n = j0 + t and decodes 64 consecutive k per stage.
+            // backward: thread owns (n = it*64 + t/4, 64 consecutive k starting at j0 + (t%4)*64).
+            const int q = t & 3;
+            const int rr = (BMODE == B_DECODE_K) ? t : (t >> 2);
+            auto src_n = [&](int it) { return (BMODE == B_DECODE_K) ? (j0 + t) : (it * kBK + rr); };
+            auto src_k = [&](int it) { return (BMODE == B_DECODE_K) ? (it * kBK) : (j0 + q * 64); };
+            auto in_range = [&](int it) { return it < nkb && src_n(it) < p.Wn && src_k(it) < p.Wk; };
+            auto load_idx = [&](int it) -> uint4 {
+                if (!in_range(it)) return make_uint4(0, 0, 0, 0);
+                return __ldg(reinterpret_cast<const uint4*>(p.packed + (long long)src_n(it) * p.packed_pitch +
+                                                            (src_k(it) >> 2)));
+            };
+            auto load_pal = [&](int it) -> uint2 {
+                if (!in_range(it)) return make_uint2(0, 0);
+                const long long g = (long long)(src_n(it) / p.gs_n) * p.n_kgroups + src_k(it) / p.gs_k;
+                return __ldg(reinterpret_cast<const uint2*>(p.palette + g * 4));
+            };
+            uint4 idx_cur = load_idx(0);
+            uint2 pal_cur = load_pal(0);
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % C::STAGES;
+                const uint32_t ph = (it / C::STAGES) & 1;
+                const uint4 idx_nxt = load_idx(it + 1);
+                const uint2 pal_nxt = load_pal(it + 1);
+                ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 3);
+                if (!ok) break;
+                uint8_t* sB = smem + s * C::STAGE_BYTES + C::A_BYTES;
+                uint8_t* row = (BMODE == B_DECODE_K) ? (sB + rr * 128) : (sB + q * 8192 + rr * 128);
+                const PalRegs pal = pal_split(pal_cur.x, pal_cur.y);
+                const uint32_t w[4] = {idx_cur.x, idx_cur.y, idx_cur.z, idx_cur.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t o[8];
+                    decode16(w[i], pal, o);
+                    // word i covers 16 elements = 16-byte chunks 2i and 2i+1 of the 128-byte row
+                    *reinterpret_cast<uint4*>(row + (((2 * i) ^ (rr & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(row + (((2 * i + 1) ^ (rr & 7)) << 4)) =
+                        make_uint4(o[4], o[5], o[6], o[7]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_b(s));
+                idx_cur = idx_nxt;
+                pal_cur = pal_nxt;
+            }
+        }
+        // ---- epilogue: TMEM -> registers -> bf16 -> global
+        if (ok) ok = mbar_wait(accum_full, 0, abort_flag, p.status, ST_TIMEOUT_ACCUM, 4);
+        if (ok) {
+            tc_fence_after_sync();
+            const int lane_group = warp & 3;      // TMEM lanes this warp may read
+            const int col_half = (warp - 2) >> 2;  // which 128 columns of the tile
+#pragma unroll 1
+            for (int mt = 0; mt < MT; ++mt) {
+                const int m = m0 + mt * 128 + lane_group * 32 + lane;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    const int col = col_half * 128 + c * 32;
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + mt * 256u + col, v);
+                    if (m < p.M) {
+                        __nv_bfloat16* dst = p.out + (long long)m * p.ld_out + j0 + col;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (j0 + col + g * 8 < p.J) {
+                                uint4 o;
+                                o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * p.alpha, __uint_as_float(v[g * 8 + 1]) * p.alpha);
+                                o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * p.alpha, __uint_as_float(v[g * 8 + 3]) * p.alpha);
+                                o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * p.alpha, __uint_as_float(v[g * 8 + 5]) * p.alpha);
+                                o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * p.alpha, __uint_as_float(v[g * 8 + 7]) * p.alpha);
+                                *reinterpret_cast<uint4*>(dst + g * 8) = o;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+
+template <int MT, int BMODE>
+static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
+    using C = Cfg<MT>;
+    CUtensorMap tmA, tmB, tmA2, tmB2;
+    int rc;
+    if ((rc = make_tmap_bf16(&tmA, a.A, a.M, a.R, a.lda, 64, 128))) return rc;
+    tmB = tmA; tmA2 = tmA; tmB2 = tmA;
+    constexpr bool kMn = (BMODE == B_DECODE_MN || BMODE == B_TMA_MN);
+    if (BMODE == B_TMA_K) {
+        if ((rc = make_tmap_bf16(&tmB, a.Bdense, a.J, a.R, a.ldb, 64, 256))) return rc;
+    } else if (BMODE == B_TMA_MN) {
+        if ((rc = make_tmap_bf16(&tmB, a.Bdense, a.R, a.J, a.ldb, 64, 64))) return rc;
+    }
+    if (a.r2 > 0) {
+        if ((rc = make_tmap_bf16(&tmA2, a.A2, a.M, a.r2, a.lda2, 64, 128))) return rc;
+        if (kMn) {
+            if ((rc = make_tmap_bf16(&tmB2, a.B2, a.r2, a.J, a.ldb2, 64, 64))) return rc;
+        } else {
+            if ((rc = make_tmap_bf16(&tmB2, a.B2, a.J, a.r2, a.ldb2, 64, 256))) return rc;
+        }
+    }
+    LutGemmParams p;
+    p.M = a.M; p.J = a.J; p.R = a.R; p.n_extra = a.r2 > 0 ? 1 : 0;
+    p.packed = (const uint8_t*)a.packed; p.packed_pitch = a.packed_pitch;
+    p.palette = (const __nv_bfloat16*)a.palette;
+    p.gs_n = a.gs_n > 0 ? a.gs_n : 1; p.gs_k = a.gs_k > 0 ? a.gs_k : 1;
+    p.n_kgroups = a.gs_k > 0 ? (a.Wk / a.gs_k) : 1;
+    p.Wn = a.Wn; p.Wk = a.Wk;
+    p.out = (__nv_bfloat16*)a.out; p.ld_out = a.ld_out; p.alpha = a.alpha;
+    p.status = device_status_ptr();
+    auto kern = lut_gemm_kernel<MT, BMODE>;
+    static bool attr_set = false;  // per instantiation; the attribute is per device function
+    if (!attr_set) {
+        PLZ_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        attr_set = true;
+    }
+    dim3 grid((a.J + kBN - 1) / kBN, (a.M + 128 * MT - 1) / (128 * MT));
+    kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
+int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream) {
+    if (a.M <= 0 || a.J <= 0 || a.R <= 0) { set_last_error("lut_gemm: empty problem"); return PLZ_ERR_BAD_SHAPE; }
+    if (a.R % kBK) { set_last_error("lut_gemm: reduction length %d is not a multiple of 64", a.R); return PLZ_ERR_BAD_SHAPE; }
+    if (a.J % 8) { set_last_error("lut_gemm: output width %d is not a multiple of 8", a.J); return PLZ_ERR_BAD_SHAPE; }
+    if (a.r2 < 0 || a.r2 > 64 || (a.r2 % 8)) { set_last_error("lut_gemm: extra rank %d must be a multiple of 8 in [0, 64]", a.r2); return PLZ_ERR_BAD_SHAPE; }
+    if (((uintptr_t)a.out & 15) || ((a.ld_out * 2) & 15)) { set_last_error("lut_gemm: output must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    const bool decode = (a.bmode == B_DECODE_K || a.bmode == B_DECODE_MN);
+    if (decode) {
+        if (!a.packed || !a.palette) { set_last_error("lut_gemm: null packed weights"); return PLZ_ERR_NULL; }
+        if (((uintptr_t)a.packed & 15) || (a.packed_pitch & 15)) { set_last_error("lut_gemm: packed index rows must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+        if ((uintptr_t)a.palette & 7) { set_last_error("lut_gemm: palette must be 8-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+        if (a.gs_k % 64 || a.Wk % a.gs_k || a.Wk % 64) { set_last_error("lut_gemm: K group size %d must be a multiple of 64 dividing K=%d", a.gs_k, a.Wk); return PLZ_ERR_BAD_SHAPE; }
+    }
+    const bool big = a.M > 128;
+    switch (a.bmode) {
+        case B_DECODE_K: return big ? launch_t<2, B_DECODE_K>(a, stream) : launch_t<1, B_DECODE_K>(a, stream);
+        case B_DECODE_MN: return big ? launch_t<2, B_DECODE_MN>(a, stream) : launch_t<1, B_DECODE_MN>(a, stream);
+        case B_TMA_K: return big ? launch_t<2, B_TMA_K>(a, stream) : launch_t<1, B_TMA_K>(a, stream);
+        case B_TMA_MN: return big ? launch_t<2, B_TMA_MN>(a, stream) : launch_t<1, B_TMA_MN>(a, stream);
+    }
+    set_last_error("lut_gemm: unknown B mode %d", a.bmode);
+    return PLZ_ERR_UNSUPPORTED;
+}
+
+}  // namespace plz

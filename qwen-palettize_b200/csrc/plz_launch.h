@@ -1,0 +1,73 @@
+// Argument structures and prototypes of the kernel launchers (one per .cu file).
+#pragma once
+#include "plz_host.h"
+
+namespace plz {
+
+// ---- lut_gemm.cu ------------------------------------------------------------------------------
+enum BMode { B_DECODE_K = 0, B_DECODE_MN = 1, B_TMA_K = 2, B_TMA_MN = 3 };
+struct LutGemmArgs {
+    int bmode;
+    int M, J, R;
+    const void* A; long long lda;           // [M, R] bf16
+    // dense B (TMA modes): B_TMA_K: [J, R] row-major; B_TMA_MN: [R, J] row-major
+    const void* Bdense; long long ldb;
+    // packed B (decode modes)
+    const void* packed; long long packed_pitch; const void* palette;
+    int gs_n, gs_k, Wn, Wk;
+    // optional extra block: A2 [M, r2] (pitch lda2); B2: K-major modes [J, r2], MN-major modes [r2, J]
+    int r2; const void* A2; long long lda2; const void* B2; long long ldb2;
+    void* out; long long ld_out; float alpha;
+};
+int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream);
+
+// ---- tn_gemm.cu -------------------------------------------------------------------------------
+enum Epi { EPI_STORE = 0, EPI_SOFT = 1, EPI_HARD = 2 };
+struct TnArgs {
+    int epi;
+    int M, I, J;
+    const void* P; long long ldp;  // [M, I] bf16
+    const void* Q; long long ldq;  // [M, J] bf16
+    // EPI_STORE (results are atomically added to `out`)
+    float* out; long long out_si, out_sj; float alpha; int out_I, out_J; int splits;
+    // EPI_SOFT / EPI_HARD
+    int rows_are_k; int logits_f16;
+    const void* logits; void* dlogits; long long ls_row, ls_col, ls_p;
+    const float* noise; long long ns_row, ns_col, ns_p; int noise_mode; uint32_t seed; int hashN;
+    float tau;
+    const void* palette; float* dpalette; int gs_n, gs_k, n_kgroups;
+    const void* packed; long long packed_pitch;
+    int sm_count;
+};
+int launch_tn_gemm(const TnArgs& a, cudaStream_t stream);
+
+// ---- gemv.cu ----------------------------------------------------------------------------------
+struct GemvArgs {
+    int M, N, K;
+    const void* x; long long ldx;
+    const void* packed; long long packed_pitch; const void* palette;
+    int gs_n, gs_k;
+    void* out; long long ld_out;
+    int sm_count;
+};
+int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream);
+
+// ---- elementwise.cu ---------------------------------------------------------------------------
+struct SelectParams {
+    const void* logits; long long ls_n, ls_k, ls_p;
+    const float* noise; long long ns_n, ns_k, ns_p;
+    int noise_mode; uint32_t seed; float inv_tau;
+    const __nv_bfloat16* palette; int gs_n, gs_k, n_kgroups;
+    int N, K;
+    uint8_t* packed; long long pitch;             // may be null
+    __nv_bfloat16* w_soft; long long ws_n, ws_k;  // may be null; element (n, k) at n * ws_n + k * ws_k
+};
+int launch_soft_select(const SelectParams& p, int logits_f16, cudaStream_t stream);
+int launch_pack_indices(const void* src, long long s_n, long long s_k, int N, int K, void* dst, long long pitch,
+                        cudaStream_t stream);
+int launch_unpack_indices(const void* src, long long pitch, int N, int K, void* dst, long long s_n, long long s_k,
+                          cudaStream_t stream);
+int launch_dequant(const void* packed, long long pitch, const void* palette, int gs_n, int gs_k, int N, int K,
+                   void* dst, long long d_n, long long d_k, cudaStream_t stream);
+
+}  // namespace plz

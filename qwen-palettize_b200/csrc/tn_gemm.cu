@@ -1,0 +1,468 @@
+// tn_gemm: D[I, J] = sum_m P[m, i] * Q[m, j]  -- a reduction over the token axis m of two row-major
+// bf16 matrices (both operands MN-major for the tensor core), fp32 accumulation in TMEM, persistent
+// CTAs with two TMEM accumulators so that the epilogue of one tile overlaps the main loop of the next.
+//
+// This is the weight-gradient product dW = x^T dY of the palettized Linear. dW never reaches HBM:
+// the epilogue turns each fp32 tile into what the optimizer needs.
+//
+//   EPI_SOFT   dLogits[p] = dW * P[p] * (c[p] - W_soft),  dPalette[group][p] += sum dW * P[p]
+//              with P recomputed from logits (+ the same noise the forward used)
+//   EPI_HARD   dPalette[group][idx] += dW   (gradient of the hard gather)
+//   EPI_STORE  plain fp32 store / atomic add (LoRA factor gradients dA, dB), optional split over m
+//
+// Layout B ("native"): D rows = k, columns = n; logits fp32 [N, K, 4]; one palette per (n, k / gs_k).
+// Layout R (reference API): D rows = n, columns = k; logits fp16 [4, K, N]; one palette per n / gs_n.
+// In both cases consecutive TMEM lanes (threads of a warp) touch consecutive addresses of the
+// logits, so every global access of the epilogue is fully coalesced.
+//
+// Replaces, in the reference: grad_W = x^T dY (scripts/fused_lut_linear_cuda.py:952,
+// scripts/triton_soft_backward.py:165-206), soft_bwd_elementwise_aos_kernel
+// (scripts/fused_lut_kernel.cu:1877-1924), fused_soft_bwd_elementwise_kernel
+// (scripts/triton_soft_backward.py:227-325) and fused_lut_linear_bwd_grad_palette_kernel
+// (scripts/fused_lut_kernel.cu:902).
+#include "plz_launch.h"
+#include "soft_math.cuh"
+
+namespace plz {
+
+
+struct TnParams {
+    int M, I, J;       // P is [M, I], Q is [M, J], D is [I, J]
+    int splits;        // EPI_STORE only: the m range is cut into `splits` chunks, results atomically added
+    int m_chunk;       // rows of m per split (multiple of 64)
+    // EPI_STORE
+    float* out; long long out_si, out_sj; float alpha; int out_I, out_J;  // store bounds
+    // EPI_SOFT / EPI_HARD
+    int rows_are_k;    // 1: D rows = k, cols = n (layout B); 0: D rows = n, cols = k (layout R)
+    const void* logits; void* dlogits;       // element strides below, dtype by template
+    long long ls_row, ls_col, ls_p;          // strides of the logits for D row, D col, plane
+    const float* noise; long long ns_row, ns_col, ns_p;
+    int noise_mode; uint32_t seed; int hashN;  // hash noise index = (k * hashN + n) * 4 + p
+    float inv_tau;
+    const __nv_bfloat16* palette; float* dpalette;
+    int gs_n, gs_k, n_kgroups;
+    const uint8_t* packed; long long packed_pitch;  // EPI_HARD
+    StatusWord* status;
+};
+
+constexpr int kTnThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
+constexpr int kTnStages = 4;
+constexpr uint32_t kTnABytes = 128 * 64 * 2;  // 2 boxes of [64 m][64 i]
+constexpr uint32_t kTnBBytes = 256 * 64 * 2;  // 4 boxes of [64 m][64 j]
+constexpr uint32_t kTnStageBytes = kTnABytes + kTnBBytes;
+constexpr uint32_t kTnRedBytes = 4 * 256 * 4 * 4;  // per-warp palette-gradient partials
+constexpr uint32_t kTnSmemBytes = kTnStages * kTnStageBytes + kTnRedBytes + 1024 + 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int EPI, typename LogitT>
+__global__ void __launch_bounds__(kTnThreads, 1)
+tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
+               const TnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    float* red = reinterpret_cast<float*>(smem + kTnStages * kTnStageBytes);
+    const uint32_t bar_base = base + kTnStages * kTnStageBytes + kTnRedBytes;
+    auto full = [&](int s) { return bar_base + 8u * s; };
+    auto empty = [&](int s) { return bar_base + 8u * (kTnStages + s); };
+    auto acc_full = [&](int b) { return bar_base + 8u * (2 * kTnStages + b); };
+    auto acc_empty = [&](int b) { return bar_base + 8u * (2 * kTnStages + 2 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
+        smem + kTnStages * kTnStageBytes + kTnRedBytes + 8 * (2 * kTnStages + 4));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_i = (p.I + 127) / 128;
+    const int tiles_j = (p.J + 255) / 256;
+    const int n_tiles = tiles_i * tiles_j * p.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTnStages; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmP);
+        tma_prefetch_desc(&tmQ);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // tile -> (split, i tile, j tile); i fastest so that one wave of CTAs covers every i tile
+    auto tile_coords = [&](int t, int& sp, int& ti, int& tj) {
+        ti = t % tiles_i;
+        const int r = t / tiles_i;
+        tj = r % tiles_j;
+        sp = r / tiles_j;
+    };
+    auto m_range = [&](int sp, int& m_begin, int& nkb) {
+        m_begin = sp * p.m_chunk;
+        int m_end = m_begin + p.m_chunk;
+        if (m_end > p.M) m_end = p.M;
+        nkb = (m_end - m_begin + 63) / 64;
+        if (nkb < 0) nkb = 0;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int last_fill[kTnStages];
+            for (int s = 0; s < kTnStages; ++s) last_fill[s] = -1;
+            bool ok = true;
+            int git = 0;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                int sp, ti, tj, m_begin, nkb;
+                tile_coords(t, sp, ti, tj);
+                m_range(sp, m_begin, nkb);
+                for (int it = 0; it < nkb; ++it, ++git) {
+                    const int s = git % kTnStages;
+                    const uint32_t ph = (git / kTnStages) & 1;
+                    ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 0);
+                    if (!ok) break;
+                    const uint32_t sA = base + s * kTnStageBytes;
+                    const uint32_t sB = sA + kTnABytes;
+                    mbar_arrive_expect_tx(full(s), kTnStageBytes);
+                    const int m = m_begin + it * 64;
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) tma_load_2d(sA + q * 8192u, &tmP, full(s), ti * 128 + q * 64, m);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) tma_load_2d(sB + q * 8192u, &tmQ, full(s), tj * 256 + q * 64, m);
+                    last_fill[s] = git;
+                }
+            }
+            if (!ok) {
+                for (int s = 0; s < kTnStages; ++s) {
+                    if (last_fill[s] < 0) continue;
+                    const uint32_t ph = (last_fill[s] / kTnStages) & 1;
+                    const uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(full(s), ph)) {
+                        if (globaltimer_ns() - t0 > 100000000ull) {
+                            report(p.status, ST_TIMEOUT_DRAIN, 0);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(128, 256, 1, 1);
+            bool ok = true;
+            int git = 0, lt = 0;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+                int sp, ti, tj, m_begin, nkb;
+                tile_coords(t, sp, ti, tj);
+                m_range(sp, m_begin, nkb);
+                const int buf = lt & 1;
+                ok = mbar_wait(acc_empty(buf), ((lt >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_ACCUM, 1);
+                if (!ok) break;
+                tc_fence_after_sync();
+                for (int it = 0; it < nkb; ++it, ++git) {
+                    const int s = git % kTnStages;
+                    const uint32_t ph = (git / kTnStages) & 1;
+                    ok = mbar_wait(full(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t sA = base + s * kTnStageBytes;
+                    const uint32_t sB = sA + kTnABytes;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t adesc = make_sdesc(sA + ks * 2048u, 8192u, 1024u);
+                        const uint64_t bdesc = make_sdesc(sB + ks * 2048u, 8192u, 1024u);
+                        umma_bf16(tmem_base + buf * 256u, adesc, bdesc, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty(s));
+                }
+                if (ok) umma_commit(acc_full(buf));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const int lane_group = warp & 3;
+        const int ew = warp - 2;  // 0..3, index into the reduction scratch
+        bool ok = true;
+        int lt = 0;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+            int sp, ti, tj, m_begin, nkb;
+            tile_coords(t, sp, ti, tj);
+            m_range(sp, m_begin, nkb);
+            const int buf = lt & 1;
+            ok = mbar_wait(acc_full(buf), (lt >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 2);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = ti * 128 + lane_group * 32 + lane;  // D row of this thread
+            const uint32_t trow = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * 256u;
+            const bool row_ok = row < p.I;
+
+            if (EPI == EPI_STORE) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < 256; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(trow + c0, v);
+                    if (nkb > 0 && row < p.out_I) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const int col = tj * 256 + c0 + c;
+                            if (col < p.out_J) {
+                                float* dst = p.out + (long long)row * p.out_si + (long long)col * p.out_sj;
+                                const float val = __uint_as_float(v[c]) * p.alpha;
+                                atomicAdd(dst, val);
+                            }
+                        }
+                    }
+                }
+            } else {
+                const LogitT* lg = reinterpret_cast<const LogitT*>(p.logits);
+                LogitT* dlg = reinterpret_cast<LogitT*>(p.dlogits);
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};  // layout R: running sums over the whole tile
+#pragma unroll 1
+                for (int c0 = 0; c0 < 256; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(trow + c0, v);
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int col = tj * 256 + c0 + c;
+                        const bool valid = row_ok && col < p.J;
+                        const int k = p.rows_are_k ? row : col;
+                        const int n = p.rows_are_k ? col : row;
+                        const float dw = __uint_as_float(v[c]);
+                        float contrib[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (valid) {
+                            const long long pg = ((long long)(n / p.gs_n) * p.n_kgroups + k / p.gs_k) * 4;
+                            if (EPI == EPI_SOFT) {
+                                const uint2 praw = __ldg(reinterpret_cast<const uint2*>(p.palette + pg));
+                                float cpal[4];
+                                cpal[0] = __uint_as_float(praw.x << 16);
+                                cpal[1] = __uint_as_float(praw.x & 0xFFFF0000u);
+                                cpal[2] = __uint_as_float(praw.y << 16);
+                                cpal[3] = __uint_as_float(praw.y & 0xFFFF0000u);
+                                const long long lo = (long long)row * p.ls_row + (long long)col * p.ls_col;
+                                float l[4], g[4];
+                                if (sizeof(LogitT) == 4 && p.ls_p == 1) {
+                                    const float4 lv = __ldcs(reinterpret_cast<const float4*>(
+                                        reinterpret_cast<const float*>(p.logits) + lo));
+                                    l[0] = lv.x; l[1] = lv.y; l[2] = lv.z; l[3] = lv.w;
+                                } else {
+#pragma unroll
+                                    for (int q = 0; q < 4; ++q) l[q] = to_f32(lg[lo + q * p.ls_p]);
+                                }
+                                if (p.noise_mode == NOISE_TENSOR) {
+                                    const long long no = (long long)row * p.ns_row + (long long)col * p.ns_col;
+                                    if (p.ns_p == 1) {
+                                        const float4 gv = __ldcs(reinterpret_cast<const float4*>(p.noise + no));
+                                        g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
+                                    } else {
+#pragma unroll
+                                        for (int q = 0; q < 4; ++q) g[q] = __ldcs(p.noise + no + q * p.ns_p);
+                                    }
+                                } else if (p.noise_mode == NOISE_HASH) {
+                                    const uint32_t e = ((uint32_t)k * (uint32_t)p.hashN + (uint32_t)n) * 4u;
+#pragma unroll
+                                    for (int q = 0; q < 4; ++q) g[q] = gumbel_hash(p.seed, e + q);
+                                } else {
+                                    g[0] = g[1] = g[2] = g[3] = 0.f;
+                                }
+                                const Soft4 s4 = soft4(l, g, cpal, p.inv_tau);
+                                float dl[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    contrib[q] = dw * s4.P[q];
+                                    dl[q] = contrib[q] * (cpal[q] - s4.w_soft);
+                                }
+                                if (dlg != nullptr) {
+                                    if (sizeof(LogitT) == 4 && p.ls_p == 1) {
+                                        __stcs(reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dlogits) + lo),
+                                               make_float4(dl[0], dl[1], dl[2], dl[3]));
+                                    } else {
+#pragma unroll
+                                        for (int q = 0; q < 4; ++q) from_f32(dlg[lo + q * p.ls_p], dl[q]);
+                                    }
+                                }
+                            } else {  // EPI_HARD
+                                const uint8_t byte = __ldg(p.packed + (long long)n * p.packed_pitch + (k >> 2));
+                                const int idx = (byte >> (2 * (k & 3))) & 3;
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) contrib[q] = (q == idx) ? dw : 0.f;
+                            }
+                        }
+                        if (p.dpalette != nullptr) {
+                            if (p.rows_are_k) {
+                                // one palette group per column: reduce over the 32 rows of this warp now
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const float s = warp_sum(contrib[q]);
+                                    if (lane == 0) red[(ew * 256 + c0 + c) * 4 + q] = s;
+                                }
+                            } else {
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) acc[q] += contrib[q];
+                            }
+                        }
+                    }
+                }
+                if (p.dpalette != nullptr) {
+                    if (p.rows_are_k) {
+                        epi_bar_sync();
+                        // 128 threads x 2 columns: add the four warps' partials in a fixed order
+                        const int et = threadIdx.x - 64;
+                        const int k0 = ti * 128;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int c = et + h * 128;
+                            const int n = tj * 256 + c;
+                            if (n < p.J && k0 < p.I) {
+                                const long long pg = ((long long)(n / p.gs_n) * p.n_kgroups + k0 / p.gs_k) * 4;
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const float s = ((red[(0 * 256 + c) * 4 + q] + red[(1 * 256 + c) * 4 + q]) +
+                                                     red[(2 * 256 + c) * 4 + q]) + red[(3 * 256 + c) * 4 + q];
+                                    atomicAdd(p.dpalette + pg + q, s);
+                                }
+                            }
+                        }
+                        epi_bar_sync();
+                    } else {
+                        // whole tile lies in one palette group
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float s = warp_sum(acc[q]);
+                            if (lane == 0) red[ew * 4 + q] = s;
+                        }
+                        epi_bar_sync();
+                        if (threadIdx.x - 64 < 4) {
+                            const int q = threadIdx.x - 64;
+                            const int n0 = ti * 128, k0 = tj * 256;
+                            if (n0 < p.I) {
+                                const long long pg = ((long long)(n0 / p.gs_n) * p.n_kgroups + k0 / p.gs_k) * 4;
+                                const float s = ((red[0 * 4 + q] + red[1 * 4 + q]) + red[2 * 4 + q]) + red[3 * 4 + q];
+                                atomicAdd(p.dpalette + pg + q, s);
+                            }
+                        }
+                        epi_bar_sync();
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+
+template <int EPI, typename LogitT>
+static int launch_tn_t(const TnArgs& a, const TnParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ,
+                       int grid, cudaStream_t stream) {
+    auto kern = tn_gemm_kernel<EPI, LogitT>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+        PLZ_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTnSmemBytes));
+        attr_set[dev & 63] = true;
+    }
+    kern<<<grid, kTnThreads, kTnSmemBytes, stream>>>(tmP, tmQ, p);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
+int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
+    if (a.M <= 0 || a.I <= 0 || a.J <= 0) { set_last_error("tn_gemm: empty problem"); return PLZ_ERR_BAD_SHAPE; }
+    CUtensorMap tmP, tmQ;
+    int rc;
+    if ((rc = make_tmap_bf16(&tmP, a.P, a.M, a.I, a.ldp, 64, 64))) return rc;
+    if ((rc = make_tmap_bf16(&tmQ, a.Q, a.M, a.J, a.ldq, 64, 64))) return rc;
+    TnParams p = {};
+    p.M = a.M; p.I = a.I; p.J = a.J;
+    p.splits = 1; p.m_chunk = ((a.M + 63) / 64) * 64;
+    if (a.epi == EPI_STORE) {
+        if (!a.out) { set_last_error("tn_gemm: null output"); return PLZ_ERR_NULL; }
+        int s = a.splits > 0 ? a.splits : 1;
+        int blocks = (a.M + 63) / 64;
+        if (s > blocks) s = blocks;
+        p.m_chunk = ((blocks + s - 1) / s) * 64;
+        p.splits = (a.M + p.m_chunk - 1) / p.m_chunk;
+        p.out = a.out; p.out_si = a.out_si; p.out_sj = a.out_sj; p.alpha = a.alpha;
+        p.out_I = a.out_I; p.out_J = a.out_J;
+    } else {
+        if (!a.palette) { set_last_error("tn_gemm: null palette"); return PLZ_ERR_NULL; }
+        if (a.gs_n <= 0 || a.gs_k <= 0) { set_last_error("tn_gemm: bad group sizes"); return PLZ_ERR_BAD_SHAPE; }
+        if (a.rows_are_k) {
+            // a 128-row tile of k must not straddle two palette groups, one group per column n
+            if (a.gs_n != 1 || a.gs_k % 128) {
+                set_last_error("tn_gemm: rows=k layout needs gs_n == 1 and gs_k %% 128 == 0 (got %d, %d)", a.gs_n, a.gs_k);
+                return PLZ_ERR_UNSUPPORTED;
+            }
+        } else {
+            if (a.gs_n % 128 || a.gs_k % 256 || a.I % 128) {
+                set_last_error("tn_gemm: rows=n layout needs gs_n %% 128 == 0, gs_k %% 256 == 0, N %% 128 == 0 (got %d, %d, %d)", a.gs_n, a.gs_k, a.I);
+                return PLZ_ERR_UNSUPPORTED;
+            }
+        }
+        p.rows_are_k = a.rows_are_k;
+        p.logits = a.logits; p.dlogits = a.dlogits;
+        p.ls_row = a.ls_row; p.ls_col = a.ls_col; p.ls_p = a.ls_p;
+        p.noise = a.noise; p.ns_row = a.ns_row; p.ns_col = a.ns_col; p.ns_p = a.ns_p;
+        p.noise_mode = a.noise_mode; p.seed = a.seed; p.hashN = a.hashN;
+        p.inv_tau = 1.0f / a.tau;
+        p.palette = (const __nv_bfloat16*)a.palette; p.dpalette = a.dpalette;
+        p.gs_n = a.gs_n; p.gs_k = a.gs_k; p.n_kgroups = a.n_kgroups;
+        p.packed = (const uint8_t*)a.packed; p.packed_pitch = a.packed_pitch;
+        if (a.epi == EPI_SOFT) {
+            if (!a.logits) { set_last_error("tn_gemm: null logits"); return PLZ_ERR_NULL; }
+            if (a.noise_mode == NOISE_TENSOR && !a.noise) { set_last_error("tn_gemm: null noise"); return PLZ_ERR_NULL; }
+            if (!(a.tau > 0.f)) { set_last_error("tn_gemm: tau must be positive"); return PLZ_ERR_BAD_SHAPE; }
+            if (!a.logits_f16 && a.ls_p == 1) {
+                if (((uintptr_t)a.logits & 15) || (a.dlogits && ((uintptr_t)a.dlogits & 15)) || (a.ls_row % 4) || (a.ls_col % 4)) {
+                    set_last_error("tn_gemm: interleaved fp32 logits must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN;
+                }
+            }
+            if (a.noise_mode == NOISE_TENSOR && a.ns_p == 1 && (((uintptr_t)a.noise & 15) || (a.ns_row % 4) || (a.ns_col % 4))) {
+                set_last_error("tn_gemm: interleaved noise must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN;
+            }
+        } else if (!a.packed) { set_last_error("tn_gemm: null packed indices"); return PLZ_ERR_NULL; }
+        if ((uintptr_t)a.palette & 7) { set_last_error("tn_gemm: palette must be 8-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    }
+    p.status = device_status_ptr();
+    const int tiles = ((a.I + 127) / 128) * ((a.J + 255) / 256) * p.splits;
+    int sms = a.sm_count > 0 ? a.sm_count : 148;
+    const int grid = tiles < sms ? tiles : sms;
+    switch (a.epi) {
+        case EPI_STORE: return launch_tn_t<EPI_STORE, float>(a, p, tmP, tmQ, grid, stream);
+        case EPI_HARD: return launch_tn_t<EPI_HARD, float>(a, p, tmP, tmQ, grid, stream);
+        case EPI_SOFT:
+            return a.logits_f16 ? launch_tn_t<EPI_SOFT, __half>(a, p, tmP, tmQ, grid, stream)
+                                : launch_tn_t<EPI_SOFT, float>(a, p, tmP, tmQ, grid, stream);
+    }
+    set_last_error("tn_gemm: unknown epilogue %d", a.epi);
+    return PLZ_ERR_UNSUPPORTED;
+}
+
+}  // namespace plz
