@@ -421,8 +421,8 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
                 return PLZ_ERR_UNSUPPORTED;
             }
         } else {
-            if (a.gs_n % 128 || a.gs_k % 256 || a.I % 128) {
-                set_last_error("tn_gemm: rows=n layout needs gs_n %% 128 == 0, gs_k %% 256 == 0, N %% 128 == 0 (got %d, %d, %d)", a.gs_n, a.gs_k, a.I);
+            if (a.gs_n % 128 || (a.gs_k % 256 && a.n_kgroups != 1) || a.I % 128) {
+                set_last_error("tn_gemm: rows=n layout needs gs_n %% 128 == 0, gs_k %% 256 == 0 (or gs_k == K), N %% 128 == 0 (got %d, %d, %d)", a.gs_n, a.gs_k, a.I);
                 return PLZ_ERR_UNSUPPORTED;
             }
         }

@@ -1,0 +1,194 @@
+"""Drop-in replacement for the reference's `fused_lut_linear_cuda` module (scripts/fused_lut_linear_cuda.py).
+
+Same names, argument order, dtypes and gradients as the reference, so that the reference's
+`PalettizedLinear` (scripts/qwen_model.py:123-130) picks this file up unchanged when its directory
+comes first on sys.path:
+
+    fused_lut_linear(x, palette, indices, bias=None, group_size=256)              :821-829
+    fused_lut_linear_soft(x, palette, logits, bias=None, group_size=256, tau=1.0) :973-994
+    CUDAFusedLUTLinear / CUDAFusedLUTLinearSoft (autograd Functions)              :755, :846
+    GROUP_SIZE, _SOFT_STEP_SEED, _next_soft_step_seed()                           :752, :837-843
+
+Tensors stay in the reference's runtime layout (x (M, K) bf16; indices (K, N) int8; palette (N/gs, 4)
+bf16; logits (4, K, N) fp16).  The work is done by libplz.so: packed 2-bit indices decoded inside the
+tcgen05 GEMMs, the weight gradient fused with the logit/palette gradients.  There is no CPU path and
+no alternative backend; a missing library or a non-CUDA tensor raises.
+
+Differences from the reference's CUDA wrapper, all on the side of its PyTorch/Triton semantics:
+  * the hard index under soft training is argmax of the plain logits (scripts/triton_soft_forward.py:160-168),
+    not of the noised probabilities (scripts/fused_lut_kernel.cu:1996-2003);
+  * dW is accumulated in fp32 and never stored; P is recomputed in fp32 in the backward from the logits and
+    the same counter-based noise instead of being saved as fp16 (10 bytes per weight less to keep);
+  * kernels run on the current torch stream, not on stream 0.
+Keyword-only extras (defaults reproduce the reference): `noise` -- an explicit (4, K, N) fp32 Gumbel tensor
+instead of the counter-based sampler; `ste=False` -- forward with W_soft instead of the straight-through W_hard.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+from torch import Tensor
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+if _HERE not in sys.path:
+    sys.path.insert(0, _HERE)
+
+import plz_native as _P  # noqa: E402
+import plz_ops as _ops  # noqa: E402
+
+GROUP_SIZE = 256
+SMALL_M = 64  # at or below this many rows the HBM-bound small-M kernel is used
+
+_SOFT_STEP_SEED = 0
+
+
+def _next_soft_step_seed() -> int:
+    """Global step counter for the Gumbel seed, one increment per soft forward call
+    (scripts/fused_lut_linear_cuda.py:837-843)."""
+    global _SOFT_STEP_SEED
+    _SOFT_STEP_SEED = (_SOFT_STEP_SEED + 1) & 0xFFFFFFFF
+    return _SOFT_STEP_SEED
+
+
+def _get_module():
+    """The reference returns its JIT-built pybind extension here; this returns the loaded C-ABI library
+    binding (raises if libplz.so has not been built)."""
+    _P.lib()
+    return _P
+
+
+# packed copies of frozen int8 index buffers, keyed on storage identity and version counter
+_PACK_CACHE: dict = {}
+
+
+def _packed_for(indices: Tensor) -> Tensor:
+    key = (indices.data_ptr(), tuple(indices.shape), indices._version, indices.device.index)
+    hit = _PACK_CACHE.get(key)
+    if hit is None:
+        if len(_PACK_CACHE) > 512:
+            _PACK_CACHE.clear()
+        hit = _ops.pack_indices(indices, n_major=False)
+        _PACK_CACHE[key] = hit
+    return hit
+
+
+def _check_common(x: Tensor, palette: Tensor, K: int, N: int, group_size: int):
+    if not x.is_cuda:
+        raise RuntimeError("fused_lut_linear_cuda: CUDA tensors only (there is no CPU implementation)")
+    if x.dtype != torch.bfloat16 or palette.dtype != torch.bfloat16:
+        raise RuntimeError("x and palette must be bfloat16")
+    if x.dim() != 2 or x.shape[1] != K:
+        raise RuntimeError(f"x must be (M, {K}), got {tuple(x.shape)}")
+    if palette.dim() != 2 or palette.shape[1] != 4:
+        raise RuntimeError(f"palette last dim must be 4, got {tuple(palette.shape)}")
+    if N % group_size != 0 or N // group_size != palette.shape[0]:
+        raise RuntimeError(f"G mismatch: N//GS={N // group_size} vs palette.size(0)={palette.shape[0]}")
+
+
+def _forward_weight(w, x):
+    if x.shape[0] <= SMALL_M:
+        return _ops.hard_forward_smallm(w, x)
+    return _ops.hard_forward(w, x)[0]
+
+
+class CUDAFusedLUTLinear(torch.autograd.Function):
+    """forward(ctx, x, palette, indices, bias, group_size) -> y; gradients to x, palette, (bias).
+    Mirrors scripts/fused_lut_linear_cuda.py:755-818."""
+
+    @staticmethod
+    def forward(ctx, x, palette, indices, bias, group_size):
+        x = x.contiguous()
+        palette = palette.contiguous()
+        indices = indices if indices.dtype == torch.int8 else indices.to(torch.int8)
+        indices = indices.contiguous()
+        K, N = indices.shape
+        _check_common(x, palette, K, N, group_size)
+        w = _ops.PackedWeight(_packed_for(indices), palette.detach(), N, K, group_size, K)
+        y = _forward_weight(w, x)
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        ctx.save_for_backward(x, palette, w.packed)
+        ctx.dims = (N, K, group_size)
+        ctx.has_bias = bias is not None
+        ctx.bias_requires_grad = bias is not None and bias.requires_grad
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, palette, packed = ctx.saved_tensors
+        N, K, gs = ctx.dims
+        grad_y = grad_y.contiguous()
+        w = _ops.PackedWeight(packed, palette.detach(), N, K, gs, K)
+        grad_x = _ops.backward_dx(w, grad_y)[0] if ctx.needs_input_grad[0] else None
+        grad_palette = None
+        if ctx.needs_input_grad[1]:
+            grad_palette = _ops.backward_dw_hard(w, x, grad_y).to(palette.dtype)
+        grad_bias = grad_y.sum(dim=0) if (ctx.has_bias and ctx.bias_requires_grad) else None
+        return grad_x, grad_palette, None, grad_bias, None
+
+
+def fused_lut_linear(x: Tensor, palette: Tensor, indices: Tensor, bias: Tensor | None = None,
+                     group_size: int = GROUP_SIZE) -> Tensor:
+    """Functional interface -- supports autograd."""
+    return CUDAFusedLUTLinear.apply(x, palette, indices, bias, group_size)
+
+
+class CUDAFusedLUTLinearSoft(torch.autograd.Function):
+    """forward(ctx, x, palette, logits, bias, group_size, tau[, noise, ste]) -> y
+    backward -> (grad_x, grad_palette, grad_logits (4, K, N) fp16, grad_bias, None, None[, None, None]).
+    Mirrors scripts/fused_lut_linear_cuda.py:846-970 (straight-through estimator :908-912)."""
+
+    @staticmethod
+    def forward(ctx, x, palette, logits, bias, group_size, tau, noise=None, ste=True):
+        x = x.contiguous()
+        palette = palette.contiguous()
+        logits = logits.contiguous()
+        assert logits.dim() == 3 and logits.shape[0] == 4, f"logits first dim must be 4, got {tuple(logits.shape)}"
+        _, K, N = logits.shape
+        _check_common(x, palette, K, N, group_size)
+        if logits.dtype not in (torch.float16, torch.float32):
+            raise RuntimeError("logits must be float16 (reference layout) or float32")
+        seed = _next_soft_step_seed()
+        nz = noise if noise is not None else "hash"
+        w = _ops.PackedWeight(_ops.empty_packed(N, K, x.device), palette.detach(), N, K, group_size, K)
+        w_soft = _ops.soft_select(w, logits.detach(), "4kn", noise=nz, tau=tau, seed=seed, want_packed=True,
+                                  want_soft=not ste)
+        if ste:
+            y = _forward_weight(w, x)
+        else:
+            y = _ops.dense_forward(w_soft, x)[0]
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        ctx.save_for_backward(x, palette, logits, w.packed, w_soft if not ste else None,
+                              noise if noise is not None else None)
+        ctx.cfg = (N, K, group_size, float(tau), seed, ste)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, palette, logits, packed, w_soft, noise = ctx.saved_tensors
+        N, K, gs, tau, seed, ste = ctx.cfg
+        grad_y = grad_y.contiguous()
+        w = _ops.PackedWeight(packed, palette.detach(), N, K, gs, K)
+        grad_x = None
+        if ctx.needs_input_grad[0]:
+            grad_x = _ops.backward_dx(w, grad_y)[0] if ste else _ops.dense_backward_dx(w_soft, grad_y)[0]
+        grad_palette = grad_logits = None
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            grad_logits, grad_palette = _ops.backward_dw_soft(
+                w, x, grad_y, logits.detach(), "4kn", noise=noise if noise is not None else "hash", tau=tau, seed=seed,
+                want_dlogits=ctx.needs_input_grad[2], want_dpalette=ctx.needs_input_grad[1])
+            if grad_palette is not None:
+                grad_palette = grad_palette.to(palette.dtype)
+        grad_bias = grad_y.sum(dim=0) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
+        return grad_x, grad_palette, grad_logits, grad_bias, None, None, None, None
+
+
+def fused_lut_linear_soft(x: Tensor, palette: Tensor, logits: Tensor, bias: Tensor | None = None,
+                          group_size: int = GROUP_SIZE, tau: float = 1.0, *, noise: Tensor | None = None,
+                          ste: bool = True) -> Tensor:
+    """Soft (Gumbel-Softmax) functional interface -- supports autograd."""
+    return CUDAFusedLUTLinearSoft.apply(x, palette, logits, bias, group_size, tau, noise, ste)

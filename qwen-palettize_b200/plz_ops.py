@@ -1,0 +1,192 @@
+"""Functional wrappers over the C ABI: one Python function per entry point of include/plz.h.
+
+Tensors are torch CUDA tensors; outputs are allocated here with torch (the library itself never
+allocates) and every call goes to the current torch stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+import plz_native as P
+
+
+@dataclass
+class PackedWeight:
+    """W[n, k] = palette[(n // gs_n) * (K // gs_k) + k // gs_k][idx[n, k]] with idx packed 4 per byte along k."""
+    packed: torch.Tensor   # uint8 [N, K // 4]
+    palette: torch.Tensor  # bf16, (N // gs_n) * (K // gs_k) * 4 elements, contiguous
+    N: int
+    K: int
+    gs_n: int
+    gs_k: int
+
+    def desc(self) -> P.Weight:
+        return P.weight_desc(self.packed, self.palette, self.N, self.K, self.gs_n, self.gs_k)
+
+
+def _pitch(K: int) -> int:
+    return (K // 4 + 15) // 16 * 16
+
+
+def empty_packed(N: int, K: int, device) -> torch.Tensor:
+    buf = torch.empty(N, _pitch(K), dtype=torch.uint8, device=device)
+    return buf[:, : K // 4] if _pitch(K) != K // 4 else buf
+
+
+def pack_indices(idx: torch.Tensor, n_major: bool) -> torch.Tensor:
+    """idx int8/uint8: [N, K] if n_major else (K, N) (the reference's runtime layout) -> packed uint8 [N, K//4]."""
+    P._need_cuda(idx)
+    assert idx.dtype in (torch.int8, torch.uint8) and idx.dim() == 2
+    if n_major:
+        N, K = idx.shape
+        s_n, s_k = idx.stride(0), idx.stride(1)
+    else:
+        K, N = idx.shape
+        s_k, s_n = idx.stride(0), idx.stride(1)
+    out = empty_packed(N, K, idx.device)
+    P.check(P.lib().plz_pack_indices(idx.data_ptr(), s_n, s_k, N, K, out.data_ptr(), out.stride(0), P.stream_ptr()),
+            "plz_pack_indices")
+    return out
+
+
+def unpack_indices(packed: torch.Tensor, K: int, n_major: bool = True) -> torch.Tensor:
+    N = packed.shape[0]
+    out = torch.empty((N, K) if n_major else (K, N), dtype=torch.int8, device=packed.device)
+    s_n, s_k = (K, 1) if n_major else (1, N)
+    P.check(P.lib().plz_unpack_indices(packed.data_ptr(), packed.stride(0), N, K, out.data_ptr(), s_n, s_k,
+                                       P.stream_ptr()), "plz_unpack_indices")
+    return out
+
+
+def dequantize(w: PackedWeight) -> torch.Tensor:
+    out = torch.empty(w.N, w.K, dtype=torch.bfloat16, device=w.packed.device)
+    d = w.desc()
+    P.check(P.lib().plz_dequantize(C.byref(d), out.data_ptr(), w.K, 1, P.stream_ptr()), "plz_dequantize")
+    return out
+
+
+def _lora_args(lora, M, device):
+    """lora = (A [r, K], B [N, r], scale) or None -> (descriptor pointer or None, workspace or None)."""
+    if lora is None:
+        return None, None, None
+    a, b, scale = lora
+    d = P.lora_desc(a, b, scale)
+    ws = torch.empty(M, a.shape[0], dtype=torch.bfloat16, device=device)
+    return d, C.byref(d), ws
+
+
+def _mat(x: torch.Tensor, cols: int):
+    P._need_cuda(x)
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == cols and x.stride(1) == 1, \
+        f"expected bf16 [M, {cols}] with unit column stride, got {tuple(x.shape)} {x.dtype}"
+    return x
+
+
+def hard_forward(w: PackedWeight, x: torch.Tensor, lora=None):
+    """y = x W^T (+ LoRA).  Returns (y, t) where t = scale * x A^T (None without LoRA)."""
+    _mat(x, w.K)
+    M = x.shape[0]
+    y = torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device)
+    keep, lp, t = _lora_args(lora, M, x.device)
+    d = w.desc()
+    P.check(P.lib().plz_hard_fwd(C.byref(d), x.data_ptr(), x.stride(0), M, lp, t.data_ptr() if t is not None else None,
+                                 y.data_ptr(), y.stride(0), P.stream_ptr()), "plz_hard_fwd")
+    return y, t
+
+
+def hard_forward_smallm(w: PackedWeight, x: torch.Tensor) -> torch.Tensor:
+    _mat(x, w.K)
+    M = x.shape[0]
+    y = torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device)
+    d = w.desc()
+    P.check(P.lib().plz_hard_fwd_smallm(C.byref(d), x.data_ptr(), x.stride(0), M, y.data_ptr(), y.stride(0),
+                                        P.stream_ptr()), "plz_hard_fwd_smallm")
+    return y
+
+
+def soft_select(w: PackedWeight, logits: torch.Tensor, layout: str, noise=None, tau: float = 1.0, seed: int = 0,
+                want_packed: bool = True, want_soft: bool = False):
+    """Writes argmax indices into w.packed (if want_packed) and returns W_soft bf16 [N, K] (if want_soft)."""
+    ld, nd = P.logits_desc(logits, layout), P.noise_desc(noise, layout, seed)
+    w_soft = torch.empty(w.N, w.K, dtype=torch.bfloat16, device=logits.device) if want_soft else None
+    d = w.desc()
+    P.check(P.lib().plz_soft_select(C.byref(d), C.byref(ld), C.byref(nd), float(tau), int(want_packed),
+                                    w_soft.data_ptr() if want_soft else None, w.K, 1, P.stream_ptr()), "plz_soft_select")
+    return w_soft
+
+
+def dense_forward(wd: torch.Tensor, x: torch.Tensor, lora=None):
+    N, K = wd.shape
+    _mat(x, K), _mat(wd, K)
+    M = x.shape[0]
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    keep, lp, t = _lora_args(lora, M, x.device)
+    P.check(P.lib().plz_dense_fwd(wd.data_ptr(), wd.stride(0), N, K, x.data_ptr(), x.stride(0), M, lp,
+                                  t.data_ptr() if t is not None else None, y.data_ptr(), y.stride(0), P.stream_ptr()),
+            "plz_dense_fwd")
+    return y, t
+
+
+def backward_dx(w: PackedWeight, dy: torch.Tensor, lora=None):
+    """dX = dY W (+ LoRA).  Returns (dX, dt) with dt = scale * dY B."""
+    _mat(dy, w.N)
+    M = dy.shape[0]
+    dx = torch.empty(M, w.K, dtype=torch.bfloat16, device=dy.device)
+    keep, lp, dt = _lora_args(lora, M, dy.device)
+    d = w.desc()
+    P.check(P.lib().plz_bwd_dx(C.byref(d), dy.data_ptr(), dy.stride(0), M, lp, dt.data_ptr() if dt is not None else None,
+                               dx.data_ptr(), dx.stride(0), P.stream_ptr()), "plz_bwd_dx")
+    return dx, dt
+
+
+def dense_backward_dx(wd: torch.Tensor, dy: torch.Tensor, lora=None):
+    N, K = wd.shape
+    _mat(dy, N), _mat(wd, K)
+    M = dy.shape[0]
+    dx = torch.empty(M, K, dtype=torch.bfloat16, device=dy.device)
+    keep, lp, dt = _lora_args(lora, M, dy.device)
+    P.check(P.lib().plz_dense_bwd_dx(wd.data_ptr(), wd.stride(0), N, K, dy.data_ptr(), dy.stride(0), M, lp,
+                                     dt.data_ptr() if dt is not None else None, dx.data_ptr(), dx.stride(0),
+                                     P.stream_ptr()), "plz_dense_bwd_dx")
+    return dx, dt
+
+
+def backward_dw_soft(w: PackedWeight, x: torch.Tensor, dy: torch.Tensor, logits: torch.Tensor, layout: str, noise=None,
+                     tau: float = 1.0, seed: int = 0, want_dlogits: bool = True, want_dpalette: bool = True):
+    """Returns (dLogits with the dtype/shape of `logits`, dPalette fp32 [groups, 4])."""
+    _mat(x, w.K), _mat(dy, w.N)
+    M = x.shape[0]
+    ld, nd = P.logits_desc(logits, layout), P.noise_desc(noise, layout, seed)
+    dlog = torch.empty_like(logits) if want_dlogits else None
+    if dlog is not None:
+        assert dlog.stride() == logits.stride()
+    dpal = torch.zeros(w.palette.numel() // 4, 4, dtype=torch.float32, device=x.device) if want_dpalette else None
+    d = w.desc()
+    P.check(P.lib().plz_bwd_dw_soft(C.byref(d), x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), M, C.byref(ld),
+                                    C.byref(nd), float(tau), dlog.data_ptr() if dlog is not None else None,
+                                    dpal.data_ptr() if dpal is not None else None, P.stream_ptr()), "plz_bwd_dw_soft")
+    return dlog, dpal
+
+
+def backward_dw_hard(w: PackedWeight, x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    _mat(x, w.K), _mat(dy, w.N)
+    dpal = torch.zeros(w.palette.numel() // 4, 4, dtype=torch.float32, device=x.device)
+    d = w.desc()
+    P.check(P.lib().plz_bwd_dw_hard(C.byref(d), x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), x.shape[0],
+                                    dpal.data_ptr(), P.stream_ptr()), "plz_bwd_dw_hard")
+    return dpal
+
+
+def lora_backward(x: torch.Tensor, dy: torch.Tensor, t: torch.Tensor, dt: torch.Tensor):
+    """dA fp32 [r, K], dB fp32 [N, r] from the workspaces left by the forward (t) and by backward_dx (dt)."""
+    M, K = x.shape
+    N = dy.shape[1]
+    r = t.shape[1]
+    da = torch.zeros(r, K, dtype=torch.float32, device=x.device)
+    db = torch.zeros(N, r, dtype=torch.float32, device=x.device)
+    P.check(P.lib().plz_lora_bwd(x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), t.data_ptr(), dt.data_ptr(),
+                                 M, N, K, r, da.data_ptr(), db.data_ptr(), P.stream_ptr()), "plz_lora_bwd")
+    return da, db

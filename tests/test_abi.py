@@ -1,0 +1,59 @@
+"""The C-ABI library builds, loads and exports every symbol include/plz.h declares.
+No compute call is made here (there is no GPU): only argument validation that returns before any launch."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    txt = open(os.path.join(ROOT, "include", "plz.h")).read()
+    txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
+    return sorted(set(re.findall(r"\b(plz_[a-z0-9_]+)\s*\(", txt)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    lib = C.CDLL(built_lib)
+    names = declared_symbols()
+    assert len(names) >= 14
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in plz.h but missing from libplz.so"
+
+
+def test_binding_covers_the_header(built_lib):
+    import plz_native as P
+    assert sorted(P.SIGNATURES) == declared_symbols()
+    assert P.lib().plz_version() >= 100
+
+
+def test_argument_validation_without_gpu(built_lib):
+    import plz_native as P
+    lib = P.lib()
+    # empty problems are accepted, null pointers and bad shapes are refused with a message
+    assert lib.plz_pack_indices(None, 1, 1, 0, 0, None, 0, None) == 0
+    assert lib.plz_pack_indices(None, 1, 1, 4, 64, None, 16, None) == 7  # PLZ_ERR_NULL
+    w = P.Weight(256, 100, 1, 64, 0x1000, 32, 0x2000)   # K not a multiple of 64
+    assert lib.plz_hard_fwd(C.byref(w), 0x10, 100, 8, None, None, 0x20, 256, None) == 1
+    assert b"multiple of 64" in lib.plz_last_error()
+    w = P.Weight(256, 256, 1, 256, 0x1001, 64, 0x2000)  # misaligned packed rows
+    assert lib.plz_hard_fwd(C.byref(w), 0x10, 256, 8, None, None, 0x20, 256, None) == 2
+    w = P.Weight(256, 256, 1, 256, 0x1000, 64, 0x2000)
+    assert lib.plz_hard_fwd(C.byref(w), 0x10, 256, 0, None, None, 0x20, 256, None) == 0  # M == 0: nothing to do
+    assert lib.plz_hard_fwd_smallm(C.byref(w), 0x10, 256, 65, 0x20, 256, None) == 1       # M > 64
+    lo = P.Lora(12, 1.0, 0x10, 256, 0x20, 12)                                              # rank not a multiple of 8
+    assert lib.plz_hard_fwd(C.byref(w), 0x10, 256, 8, C.byref(lo), 0x30, 0x20, 256, None) == 1
+    lo = P.Lora(16, 1.0, 0x10, 256, 0x20, 16)
+    assert lib.plz_hard_fwd(C.byref(w), 0x10, 256, 8, C.byref(lo), None, 0x20, 256, None) == 5  # no workspace
+
+
+def test_ops_refuse_cpu_tensors(built_lib):
+    import torch
+    import fused_lut_linear_cuda as F
+    x = torch.zeros(4, 256, dtype=torch.bfloat16)
+    pal = torch.zeros(1, 4, dtype=torch.bfloat16)
+    idx = torch.zeros(256, 256, dtype=torch.int8)
+    with pytest.raises(RuntimeError):
+        F.fused_lut_linear(x, pal, idx, None, 256)

@@ -1,0 +1,110 @@
+"""Hard forward / backward of the palettized Linear on the GPU against the CPU oracle."""
+import pytest
+import torch
+
+import plz_oracle as O
+from helpers import assert_close, check_status
+
+pytestmark = pytest.mark.gpu
+
+
+def _make(M, N, K, gs_n, gs_k, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    dy = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    idx = torch.randint(0, 4, (N, K), generator=g, dtype=torch.uint8)
+    pal = (torch.randn((N // gs_n) * (K // gs_k), 4, generator=g) * 0.02).sort(-1).values.to(torch.bfloat16)
+    return x, dy, idx, pal
+
+
+def _weight(idx, pal, N, K, gs_n, gs_k):
+    import plz_ops as ops
+    return ops.PackedWeight(torch.from_numpy(O.pack_rows(idx.numpy())).cuda(), pal.cuda(), N, K, gs_n, gs_k)
+
+
+SHAPES = [
+    # M, N, K, gs_n, gs_k
+    (128, 256, 64, 1, 64),        # one tile, one stage
+    (128, 256, 512, 1, 256),      # pipeline wraps
+    (100, 512, 256, 1, 256),      # ragged M inside one 128-row tile
+    (300, 768, 1024, 1, 256),     # two M tiles per CTA, ragged
+    (512, 1024, 512, 256, 512),   # reference grouping: one palette per 256 output columns
+    (257, 320, 192, 1, 64),       # N not a multiple of the 256-wide tile
+]
+
+
+@pytest.mark.parametrize("M,N,K,gs_n,gs_k", SHAPES)
+def test_hard_forward(M, N, K, gs_n, gs_k):
+    import plz_ops as ops
+    x, dy, idx, pal = _make(M, N, K, gs_n, gs_k)
+    w = _weight(idx, pal, N, K, gs_n, gs_k)
+    y, _ = ops.hard_forward(w, x.cuda())
+    check_status()
+    assert_close(y, O.hard_forward(x, O.dequantize(idx.long(), pal, gs_n, gs_k)), "y")
+
+
+@pytest.mark.parametrize("M,N,K,gs_n,gs_k", SHAPES)
+def test_backward_dx(M, N, K, gs_n, gs_k):
+    import plz_ops as ops
+    if N % 64:
+        pytest.skip("dX needs N % 64 == 0")
+    x, dy, idx, pal = _make(M, N, K, gs_n, gs_k, seed=1)
+    w = _weight(idx, pal, N, K, gs_n, gs_k)
+    dx, _ = ops.backward_dx(w, dy.cuda())
+    check_status()
+    want, _ = O.hard_backward(x, dy, idx.long(), pal, gs_n, gs_k)
+    assert_close(dx, want, "dX")
+
+
+@pytest.mark.parametrize("M,N,K,gs_n,gs_k", [(128, 256, 256, 1, 256), (300, 512, 512, 1, 256), (200, 512, 256, 256, 256),
+                                             (512, 1024, 512, 256, 512)])
+def test_hard_palette_gradient(M, N, K, gs_n, gs_k):
+    import plz_ops as ops
+    x, dy, idx, pal = _make(M, N, K, gs_n, gs_k, seed=2)
+    w = _weight(idx, pal, N, K, gs_n, gs_k)
+    dpal = ops.backward_dw_hard(w, x.cuda(), dy.cuda())
+    check_status()
+    _, want = O.hard_backward(x, dy, idx.long(), pal, gs_n, gs_k)
+    assert_close(dpal, want, "dPalette")
+
+
+@pytest.mark.parametrize("rank", [16, 32])
+def test_hard_forward_with_lora(rank):
+    import plz_ops as ops
+    M, N, K = 300, 512, 512
+    x, dy, idx, pal = _make(M, N, K, 1, 256, seed=4)
+    g = torch.Generator().manual_seed(8)
+    a = (torch.randn(rank, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+    b = (torch.randn(N, rank, generator=g) * 0.05).to(torch.bfloat16)
+    w = _weight(idx, pal, N, K, 1, 256)
+    lora = (a.cuda(), b.cuda(), 2.0)
+    y, t = ops.hard_forward(w, x.cuda(), lora)
+    dx, dt = ops.backward_dx(w, dy.cuda(), lora)
+    da, db = ops.lora_backward(x.cuda(), dy.cuda(), t, dt)
+    check_status()
+    wd = O.dequantize(idx.long(), pal, 1, 256)
+    want_y = (x.float() @ wd.float().t() + O.lora_forward(x, a, b, 2.0)).to(torch.bfloat16)
+    dxl, want_da, want_db = O.lora_backward(x, dy, a, b, 2.0)
+    assert_close(y, want_y, "y + LoRA")
+    assert_close(t, (x.float() @ a.float().t() * 2.0), "t = s x A^T")
+    assert_close(dx, (dy.float() @ wd.float() + dxl), "dX + LoRA")
+    assert_close(da, want_da, "dA")
+    assert_close(db, want_db, "dB")
+
+
+def test_forward_is_deterministic():
+    import plz_ops as ops
+    x, dy, idx, pal = _make(300, 512, 512, 1, 256, seed=6)
+    w = _weight(idx, pal, 512, 512, 1, 256)
+    xc = x.cuda()
+    y1 = ops.hard_forward(w, xc)[0].clone()
+    y2 = ops.hard_forward(w, xc)[0]
+    assert torch.equal(y1, y2)
+
+
+def test_empty_batch_is_a_no_op():
+    import plz_ops as ops
+    x, dy, idx, pal = _make(1, 256, 64, 1, 64)
+    w = _weight(idx, pal, 256, 64, 1, 64)
+    y, _ = ops.hard_forward(w, torch.empty(0, 64, dtype=torch.bfloat16, device="cuda"))
+    assert y.shape == (0, 256)

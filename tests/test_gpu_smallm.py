@@ -1,0 +1,25 @@
+"""Small-M (token decode) hard forward on the GPU against the CPU oracle and against the large-M kernel."""
+import pytest
+import torch
+
+import plz_oracle as O
+from helpers import assert_close, check_status
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M,N,K,gs_n,gs_k", [(1, 256, 256, 1, 256), (8, 1024, 2560, 1, 256), (16, 9728, 2560, 1, 256),
+                                             (33, 1000, 512, 1, 64), (64, 2560, 9728, 1, 256), (4, 1024, 1024, 256, 1024)])
+def test_small_m_forward(M, N, K, gs_n, gs_k):
+    import plz_ops as ops
+    g = torch.Generator().manual_seed(M * 31 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    idx = torch.randint(0, 4, (N, K), generator=g, dtype=torch.uint8)
+    pal = (torch.randn((N // gs_n) * (K // gs_k), 4, generator=g) * 0.02).sort(-1).values.to(torch.bfloat16)
+    w = ops.PackedWeight(torch.from_numpy(O.pack_rows(idx.numpy())).cuda(), pal.cuda(), N, K, gs_n, gs_k)
+    y = ops.hard_forward_smallm(w, x.cuda())
+    check_status()
+    assert_close(y, O.hard_forward(x, O.dequantize(idx.long(), pal, gs_n, gs_k)), "y")
+    if N % 8 == 0:
+        y_big, _ = ops.hard_forward(w, x.cuda())
+        assert_close(y, y_big, "small-M kernel vs tiled kernel", rel=4e-3)
