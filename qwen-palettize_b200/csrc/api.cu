@@ -49,6 +49,14 @@ EncodeTiledFn get_encode_fn() {
 int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                    uint32_t box_cols, uint32_t box_rows) {
     EncodeTiledFn enc = get_encode_fn();
+    // The driver call needs the device's primary context current on the calling thread; a thread that has
+    // only been handed a device by cudaSetDevice (e.g. an autograd worker) may not have it bound yet.
+    static thread_local int bound_dev = -1;
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev != bound_dev) {
+        cudaFree(nullptr);
+        bound_dev = dev;
+    }
     if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return PLZ_ERR_CUDA; }
     if (!base) { set_last_error("null matrix pointer"); return PLZ_ERR_NULL; }
     if (((uintptr_t)base & 15) || ((ld * 2) & 15)) {
