@@ -14,9 +14,7 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -39,48 +37,54 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock, power and throttle reasons read through NVML (read-only queries) every few milliseconds by a
+    background thread while the timed region runs."""
 
-    def __init__(self, gpu_index):
-        self.gpu_index, self.proc, self.path = gpu_index, None, None
+    def __init__(self, gpu_index, period_s=0.005):
+        self.gpu_index, self.period_s = gpu_index, period_s
+        self.samples, self._stop, self._thr, self._h, self._nv = [], False, None, None, None
 
     def start(self):
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                                          "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            self._nv, self._h = nv, nv.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
         except Exception:
-            self.proc = None
+            self._thr = None
+
+    def _loop(self):
+        nv, h = self._nv, self._h
+        while not self._stop:
+            try:
+                self.samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetPowerUsage(h) / 1000.0,
+                                     nv.nvmlDeviceGetCurrentClocksEventReasons(h)))
+            except Exception:
+                pass
+            time.sleep(self.period_s)
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
+        if self._thr is None:
             return out
-        self.proc.terminate()
+        self._stop = True
+        self._thr.join(timeout=2)
+        nv, h = self._nv, self._h
         try:
-            self.proc.wait(timeout=5)
+            out["sm_max_mhz"] = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
         except Exception:
-            self.proc.kill()
-        sm, smax, power, reasons = [], [], [], set()
-        for line in open(self.path):
-            f = [s.strip() for s in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        os.unlink(self.path)
-        if sm:
-            busy = [s for s, p in zip(sm, power) if p > 300.0] or sm   # samples taken under load
-            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm),
-                       power_w_max=max(power))
+            pass
+        if self.samples:
+            bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                    "hw_power_brake_slowdown": 0x80}
+            seen = 0
+            for _, _, r in self.samples:
+                seen |= r
+            out.update(sm_mhz=statistics.median(s[0] for s in self.samples), samples=len(self.samples),
+                       sm_min_mhz=min(s[0] for s in self.samples), power_w_max=max(s[1] for s in self.samples),
+                       reasons=sorted(k for k, v in bits.items() if seen & v))
         return out
 
 

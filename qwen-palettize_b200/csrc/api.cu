@@ -298,15 +298,13 @@ static int bwd_dw_common(int epi, const plz_weight_t* w, const void* x, int64_t 
     if (!x || !dY) { set_last_error("null activation pointer"); return PLZ_ERR_NULL; }
     TnArgs a = {};
     a.epi = epi; a.M = M;
-    // Which of (n, k) runs along the TMEM lanes is chosen so that lanes walk the contiguous axis of
-    // the logits: k for interleaved [N, K, 4], n for planar (4, K, N). The hard epilogue reads one
-    // byte per element and follows the palette grouping instead.
-    bool rows_are_k;
+    // Which of (n, k) runs along the TMEM lanes (threads of a warp) is chosen so that lanes walk the contiguous
+    // axis of the logits: k for interleaved fp32 [N, K, 4] with a palette per weight row, n otherwise.
+    bool rows_are_k = (w->gs_n == 1) && (w->gs_k % 128 == 0);
     if (epi == EPI_SOFT) {
         if (!logits || !logits->ptr) { set_last_error("null logits"); return PLZ_ERR_NULL; }
-        rows_are_k = logits->s_k < logits->s_n;
-    } else {
-        rows_are_k = (w->gs_n == 1);
+        rows_are_k = rows_are_k && logits->dtype == 0 && logits->s_p == 1 && logits->s_k < logits->s_n &&
+                     (!noise || noise->mode != 1 || (noise->s_p == 1 && noise->s_k < noise->s_n));
     }
     a.rows_are_k = rows_are_k ? 1 : 0;
     if (rows_are_k) { a.I = w->K; a.J = w->N; a.P = x; a.ldp = ldx; a.Q = dY; a.ldq = lddy; }

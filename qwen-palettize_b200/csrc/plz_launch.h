@@ -31,7 +31,8 @@ struct TnArgs {
     // EPI_STORE (results are atomically added to `out`)
     float* out; long long out_si, out_sj; float alpha; int out_I, out_J; int splits;
     // EPI_SOFT / EPI_HARD
-    int rows_are_k; int logits_f16;
+    int rows_are_k;  // 1: D rows = input columns k (interleaved logits); 0: D rows = weight rows n
+    int logits_f16;
     const void* logits; void* dlogits; long long ls_row, ls_col, ls_p;
     const float* noise; long long ns_row, ns_col, ns_p; int noise_mode; uint32_t seed; int hashN;
     float tau;

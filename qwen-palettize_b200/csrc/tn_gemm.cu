@@ -33,7 +33,6 @@ struct TnParams {
     // EPI_STORE
     float* out; long long out_si, out_sj; float alpha; int out_I, out_J;  // store bounds
     // EPI_SOFT / EPI_HARD
-    int rows_are_k;    // 1: D rows = k, cols = n (layout B); 0: D rows = n, cols = k (layout R)
     const void* logits; void* dlogits;       // element strides below, dtype by template
     long long ls_row, ls_col, ls_p;          // strides of the logits for D row, D col, plane
     const float* noise; long long ns_row, ns_col, ns_p;
@@ -45,7 +44,7 @@ struct TnParams {
     StatusWord* status;
 };
 
-constexpr int kTnThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
+constexpr int kTnThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue
 constexpr int kTnStages = 4;
 constexpr uint32_t kTnABytes = 128 * 64 * 2;  // 2 boxes of [64 m][64 i]
 constexpr uint32_t kTnBBytes = 256 * 64 * 2;  // 4 boxes of [64 m][64 j]
@@ -58,9 +57,9 @@ __device__ __forceinline__ float warp_sum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
     return v;
 }
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-template <int EPI, typename LogitT>
+template <int EPI, typename LogitT, bool ROWS_K>
 __global__ void __launch_bounds__(kTnThreads, 1)
 tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                const TnParams p) {
@@ -91,7 +90,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full(b), 1);
-            mbar_init(acc_empty(b), 4);
+            mbar_init(acc_empty(b), 8);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -196,8 +195,12 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
+        // Eight warps: warp w reads TMEM lanes 32*(w%4).., and the two warps of a lane group split the
+        // 256 columns in halves. Columns are processed 8 at a time: all global loads of a batch are issued
+        // before any arithmetic, so that each thread keeps 16 x 16 bytes in flight.
         const int lane_group = warp & 3;
-        const int ew = warp - 2;  // 0..3, index into the reduction scratch
+        const int col_half = (warp - 2) >> 2;
+        const int ew = warp - 2;  // 0..7
         bool ok = true;
         int lt = 0;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
@@ -209,152 +212,249 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             if (!ok) break;
             tc_fence_after_sync();
             const int row = ti * 128 + lane_group * 32 + lane;  // D row of this thread
-            const uint32_t trow = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * 256u;
+            const uint32_t trow = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * 256u + col_half * 128u;
             const bool row_ok = row < p.I;
+            const int colbase = tj * 256 + col_half * 128;
 
             if (EPI == EPI_STORE) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < 256; c0 += 16) {
+                for (int c0 = 0; c0 < 128; c0 += 16) {
                     uint32_t v[16];
                     tmem_ld_32x16(trow + c0, v);
                     if (nkb > 0 && row < p.out_I) {
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
-                            const int col = tj * 256 + c0 + c;
-                            if (col < p.out_J) {
-                                float* dst = p.out + (long long)row * p.out_si + (long long)col * p.out_sj;
-                                const float val = __uint_as_float(v[c]) * p.alpha;
-                                atomicAdd(dst, val);
-                            }
+                            const int col = colbase + c0 + c;
+                            if (col < p.out_J)
+                                atomicAdd(p.out + (long long)row * p.out_si + (long long)col * p.out_sj,
+                                          __uint_as_float(v[c]) * p.alpha);
                         }
                     }
                 }
-            } else {
-                const LogitT* lg = reinterpret_cast<const LogitT*>(p.logits);
-                LogitT* dlg = reinterpret_cast<LogitT*>(p.dlogits);
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};  // layout R: running sums over the whole tile
+            } else if (ROWS_K) {
+                // Interleaved logits [N, K, 4], one palette per (n, 256-wide k group): D rows are input columns k
+                // (the 32 lanes of a warp read 32 consecutive float4 = 512 contiguous bytes), D columns are weight
+                // rows n, each with its own palette. The palette gradient of a column is a sum over lanes: the 32
+                // partials of a batch (8 columns x 4 entries) are reduced with a 31-shuffle transposing butterfly.
+                const int k = row;
+                const int kgi = (row_ok ? k : 0) / p.gs_k;
+                const float* lbase = reinterpret_cast<const float*>(p.logits) + (long long)k * p.ls_row;
+                float* dbase = p.dlogits ? reinterpret_cast<float*>(p.dlogits) + (long long)k * p.ls_row : nullptr;
+                const float* nbase = p.noise ? p.noise + (long long)k * p.ns_row : nullptr;
 #pragma unroll 1
-                for (int c0 = 0; c0 < 256; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld_32x16(trow + c0, v);
+                for (int c0 = 0; c0 < 128; c0 += 8) {
+                    uint32_t v[8];
+                    tmem_ld_32x8(trow + c0, v);
+                    const int nb = colbase + c0;  // first n of the batch
+                    float4 lv[8], gv[8];
+                    uint2 praw[8];
+                    uint32_t hbyte[8];
+                    // ---- phase 1: issue every load of the batch
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const int col = tj * 256 + c0 + c;
-                        const bool valid = row_ok && col < p.J;
-                        const int k = p.rows_are_k ? row : col;
-                        const int n = p.rows_are_k ? col : row;
-                        const float dw = __uint_as_float(v[c]);
-                        float contrib[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int c = 0; c < 8; ++c) {
+                        const int n = nb + c;
+                        const bool valid = row_ok && n < p.J;
+                        lv[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        gv[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        praw[c] = make_uint2(0u, 0u);
+                        hbyte[c] = 0;
                         if (valid) {
-                            const long long pg = ((long long)(n / p.gs_n) * p.n_kgroups + k / p.gs_k) * 4;
                             if (EPI == EPI_SOFT) {
-                                const uint2 praw = __ldg(reinterpret_cast<const uint2*>(p.palette + pg));
-                                float cpal[4];
-                                cpal[0] = __uint_as_float(praw.x << 16);
-                                cpal[1] = __uint_as_float(praw.x & 0xFFFF0000u);
-                                cpal[2] = __uint_as_float(praw.y << 16);
-                                cpal[3] = __uint_as_float(praw.y & 0xFFFF0000u);
-                                const long long lo = (long long)row * p.ls_row + (long long)col * p.ls_col;
-                                float l[4], g[4];
-                                if (sizeof(LogitT) == 4 && p.ls_p == 1) {
-                                    const float4 lv = __ldcs(reinterpret_cast<const float4*>(
-                                        reinterpret_cast<const float*>(p.logits) + lo));
-                                    l[0] = lv.x; l[1] = lv.y; l[2] = lv.z; l[3] = lv.w;
-                                } else {
-#pragma unroll
-                                    for (int q = 0; q < 4; ++q) l[q] = to_f32(lg[lo + q * p.ls_p]);
-                                }
-                                if (p.noise_mode == NOISE_TENSOR) {
-                                    const long long no = (long long)row * p.ns_row + (long long)col * p.ns_col;
-                                    if (p.ns_p == 1) {
-                                        const float4 gv = __ldcs(reinterpret_cast<const float4*>(p.noise + no));
-                                        g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
-                                    } else {
-#pragma unroll
-                                        for (int q = 0; q < 4; ++q) g[q] = __ldcs(p.noise + no + q * p.ns_p);
-                                    }
-                                } else if (p.noise_mode == NOISE_HASH) {
-                                    const uint32_t e = ((uint32_t)k * (uint32_t)p.hashN + (uint32_t)n) * 4u;
-#pragma unroll
-                                    for (int q = 0; q < 4; ++q) g[q] = gumbel_hash(p.seed, e + q);
-                                } else {
-                                    g[0] = g[1] = g[2] = g[3] = 0.f;
-                                }
-                                const Soft4 s4 = soft4(l, g, cpal, p.inv_tau);
-                                float dl[4];
-#pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    contrib[q] = dw * s4.P[q];
-                                    dl[q] = contrib[q] * (cpal[q] - s4.w_soft);
-                                }
-                                if (dlg != nullptr) {
-                                    if (sizeof(LogitT) == 4 && p.ls_p == 1) {
-                                        __stcs(reinterpret_cast<float4*>(reinterpret_cast<float*>(p.dlogits) + lo),
-                                               make_float4(dl[0], dl[1], dl[2], dl[3]));
-                                    } else {
-#pragma unroll
-                                        for (int q = 0; q < 4; ++q) from_f32(dlg[lo + q * p.ls_p], dl[q]);
-                                    }
-                                }
-                            } else {  // EPI_HARD
-                                const uint8_t byte = __ldg(p.packed + (long long)n * p.packed_pitch + (k >> 2));
-                                const int idx = (byte >> (2 * (k & 3))) & 3;
-#pragma unroll
-                                for (int q = 0; q < 4; ++q) contrib[q] = (q == idx) ? dw : 0.f;
+                                praw[c] = __ldg(reinterpret_cast<const uint2*>(p.palette + ((long long)n * p.n_kgroups + kgi) * 4));
+                                lv[c] = __ldcs(reinterpret_cast<const float4*>(lbase + (long long)n * p.ls_col));
+                                if (p.noise_mode == NOISE_TENSOR)
+                                    gv[c] = __ldcs(reinterpret_cast<const float4*>(nbase + (long long)n * p.ns_col));
+                            } else {
+                                hbyte[c] = __ldg(p.packed + (long long)n * p.packed_pitch + (k >> 2));
                             }
                         }
-                        if (p.dpalette != nullptr) {
-                            if (p.rows_are_k) {
-                                // one palette group per column: reduce over the 32 rows of this warp now
+                    }
+                    // ---- phase 2: arithmetic and stores
+                    float part[32];
 #pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    const float s = warp_sum(contrib[q]);
-                                    if (lane == 0) red[(ew * 256 + c0 + c) * 4 + q] = s;
-                                }
-                            } else {
+                    for (int c = 0; c < 8; ++c) {
+                        const int n = nb + c;
+                        const bool valid = row_ok && n < p.J;
+                        const float dw = valid ? __uint_as_float(v[c]) : 0.f;
+                        if (EPI == EPI_SOFT) {
+                            float cp[4], l[4], g[4];
+                            cp[0] = __uint_as_float(praw[c].x << 16);
+                            cp[1] = __uint_as_float(praw[c].x & 0xFFFF0000u);
+                            cp[2] = __uint_as_float(praw[c].y << 16);
+                            cp[3] = __uint_as_float(praw[c].y & 0xFFFF0000u);
+                            l[0] = lv[c].x; l[1] = lv[c].y; l[2] = lv[c].z; l[3] = lv[c].w;
+                            g[0] = gv[c].x; g[1] = gv[c].y; g[2] = gv[c].z; g[3] = gv[c].w;
+                            if (p.noise_mode == NOISE_HASH) {
+                                const uint32_t e = ((uint32_t)k * (uint32_t)p.hashN + (uint32_t)n) * 4u;
 #pragma unroll
-                                for (int q = 0; q < 4; ++q) acc[q] += contrib[q];
+                                for (int q = 0; q < 4; ++q) g[q] = gumbel_hash(p.seed, e + q);
                             }
+                            const Soft4 s4 = soft4(l, g, cp, p.inv_tau);
+                            float dl[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                part[c * 4 + q] = dw * s4.P[q];
+                                dl[q] = part[c * 4 + q] * (cp[q] - s4.w_soft);
+                            }
+                            if (valid && dbase != nullptr)
+                                __stcs(reinterpret_cast<float4*>(dbase + (long long)n * p.ls_col), make_float4(dl[0], dl[1], dl[2], dl[3]));
+                        } else {
+                            const int idx = (hbyte[c] >> (2 * (k & 3))) & 3;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) part[c * 4 + q] = (q == idx) ? dw : 0.f;
+                        }
+                    }
+                    if (p.dpalette != nullptr) {
+                        // transposing butterfly: afterwards lane L holds the sum over all 32 lanes of part[L]
+#pragma unroll
+                        for (int s = 16; s >= 1; s >>= 1) {
+                            const bool up = (lane & s) != 0;
+#pragma unroll
+                            for (int j = 0; j < s; ++j) {
+                                const float send = up ? part[j] : part[j + s];
+                                const float keep = up ? part[j + s] : part[j];
+                                part[j] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, s);
+                            }
+                        }
+                        red[(lane_group * 256 + col_half * 128 + c0) * 4 + lane] = part[0];
+                    }
+                }
+                if (p.dpalette != nullptr) {
+                    epi_bar_sync();
+                    // one thread per column: add the four lane groups' partials in a fixed order
+                    const int et = threadIdx.x - 64;  // 0..255
+                    const int n = tj * 256 + et;
+                    const int k0 = ti * 128;
+                    if (n < p.J && k0 < p.I) {
+                        const long long pg = ((long long)n * p.n_kgroups + k0 / p.gs_k) * 4;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float s = ((red[(0 * 256 + et) * 4 + q] + red[(1 * 256 + et) * 4 + q]) +
+                                             red[(2 * 256 + et) * 4 + q]) + red[(3 * 256 + et) * 4 + q];
+                            atomicAdd(p.dpalette + pg + q, s);
+                        }
+                    }
+                    epi_bar_sync();
+                }
+            } else {
+                // D rows are weight rows n, columns are input columns k. A thread owns one n and walks k, so the
+                // palette (one per n-group and 256-wide k-group) is loaded once per tile and the palette-gradient
+                // partial sums stay in registers for the whole tile.
+                constexpr bool kVec = (sizeof(LogitT) == 4);
+                const bool vec_l = kVec && p.ls_p == 1;
+                const bool vec_n = p.ns_p == 1;
+                const int n = row;
+                const int k_tile0 = tj * 256;
+                const long long pg = ((long long)((row_ok ? n : 0) / p.gs_n) * p.n_kgroups + k_tile0 / p.gs_k) * 4;
+                float cpal[4] = {0.f, 0.f, 0.f, 0.f};
+                if (EPI == EPI_SOFT) {
+                    const uint2 praw = __ldg(reinterpret_cast<const uint2*>(p.palette + pg));
+                    cpal[0] = __uint_as_float(praw.x << 16);
+                    cpal[1] = __uint_as_float(praw.x & 0xFFFF0000u);
+                    cpal[2] = __uint_as_float(praw.y << 16);
+                    cpal[3] = __uint_as_float(praw.y & 0xFFFF0000u);
+                }
+                const LogitT* lrow = reinterpret_cast<const LogitT*>(p.logits) + (long long)n * p.ls_row;
+                LogitT* drow = p.dlogits ? reinterpret_cast<LogitT*>(p.dlogits) + (long long)n * p.ls_row : nullptr;
+                const float* nrow = p.noise ? p.noise + (long long)n * p.ns_row : nullptr;
+                const uint8_t* prow = p.packed ? p.packed + (long long)n * p.packed_pitch : nullptr;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 8) {
+                    uint32_t v[8];
+                    tmem_ld_32x8(trow + c0, v);
+                    const int kb = colbase + c0;  // first k of the batch
+                    float l[8][4], g[8][4];
+                    uint32_t hard_bits = 0;
+                    // ---- phase 1: issue every load of the batch
+                    if (EPI == EPI_SOFT) {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const bool valid = row_ok && (kb + c) < p.J;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) { l[c][q] = 0.f; g[c][q] = 0.f; }
+                            if (valid) {
+                                const long long lo = (long long)(kb + c) * p.ls_col;
+                                if (vec_l) {
+                                    const float4 lv = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(lrow) + lo));
+                                    l[c][0] = lv.x; l[c][1] = lv.y; l[c][2] = lv.z; l[c][3] = lv.w;
+                                } else {
+#pragma unroll
+                                    for (int q = 0; q < 4; ++q) l[c][q] = to_f32(lrow[lo + q * p.ls_p]);
+                                }
+                                if (p.noise_mode == NOISE_TENSOR) {
+                                    const long long no = (long long)(kb + c) * p.ns_col;
+                                    if (vec_n) {
+                                        const float4 gv = __ldcs(reinterpret_cast<const float4*>(nrow + no));
+                                        g[c][0] = gv.x; g[c][1] = gv.y; g[c][2] = gv.z; g[c][3] = gv.w;
+                                    } else {
+#pragma unroll
+                                        for (int q = 0; q < 4; ++q) g[c][q] = __ldcs(nrow + no + q * p.ns_p);
+                                    }
+                                }
+                            }
+                        }
+                    } else if (row_ok && kb < p.J) {
+                        // 8 consecutive k = 16 bits of the packed row
+                        hard_bits = __ldg(reinterpret_cast<const unsigned short*>(prow + (kb >> 2)));
+                    }
+                    // ---- phase 2: arithmetic and stores
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const bool valid = row_ok && (kb + c) < p.J;
+                        const float dw = valid ? __uint_as_float(v[c]) : 0.f;
+                        if (EPI == EPI_SOFT) {
+                            if (p.noise_mode == NOISE_HASH) {
+                                const uint32_t e = ((uint32_t)(kb + c) * (uint32_t)p.hashN + (uint32_t)n) * 4u;
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) g[c][q] = gumbel_hash(p.seed, e + q);
+                            }
+                            const Soft4 s4 = soft4(l[c], g[c], cpal, p.inv_tau);
+                            float dl[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float cq = dw * s4.P[q];
+                                acc[q] += cq;
+                                dl[q] = cq * (cpal[q] - s4.w_soft);
+                            }
+                            if (valid && drow != nullptr) {
+                                const long long lo = (long long)(kb + c) * p.ls_col;
+                                if (vec_l) {
+                                    __stcs(reinterpret_cast<float4*>(reinterpret_cast<float*>(drow) + lo),
+                                           make_float4(dl[0], dl[1], dl[2], dl[3]));
+                                } else {
+#pragma unroll
+                                    for (int q = 0; q < 4; ++q) from_f32(drow[lo + q * p.ls_p], dl[q]);
+                                }
+                            }
+                        } else {
+                            const int idx = (hard_bits >> (2 * c)) & 3;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) acc[q] += (q == idx) ? dw : 0.f;
                         }
                     }
                 }
                 if (p.dpalette != nullptr) {
-                    if (p.rows_are_k) {
-                        epi_bar_sync();
-                        // 128 threads x 2 columns: add the four warps' partials in a fixed order
-                        const int et = threadIdx.x - 64;
-                        const int k0 = ti * 128;
+                    if (p.gs_n == 1) {
+                        // this thread's row has its own palette: the two column halves add up in either order
+                        if (row_ok) {
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int c = et + h * 128;
-                            const int n = tj * 256 + c;
-                            if (n < p.J && k0 < p.I) {
-                                const long long pg = ((long long)(n / p.gs_n) * p.n_kgroups + k0 / p.gs_k) * 4;
-#pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    const float s = ((red[(0 * 256 + c) * 4 + q] + red[(1 * 256 + c) * 4 + q]) +
-                                                     red[(2 * 256 + c) * 4 + q]) + red[(3 * 256 + c) * 4 + q];
-                                    atomicAdd(p.dpalette + pg + q, s);
-                                }
-                            }
+                            for (int q = 0; q < 4; ++q) atomicAdd(p.dpalette + pg + q, acc[q]);
                         }
-                        epi_bar_sync();
                     } else {
-                        // whole tile lies in one palette group
+                        // the whole 128-row tile lies in one palette group: shuffle-reduce, then one add per tile
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             const float s = warp_sum(acc[q]);
                             if (lane == 0) red[ew * 4 + q] = s;
                         }
                         epi_bar_sync();
-                        if (threadIdx.x - 64 < 4) {
-                            const int q = threadIdx.x - 64;
-                            const int n0 = ti * 128, k0 = tj * 256;
-                            if (n0 < p.I) {
-                                const long long pg = ((long long)(n0 / p.gs_n) * p.n_kgroups + k0 / p.gs_k) * 4;
-                                const float s = ((red[0 * 4 + q] + red[1 * 4 + q]) + red[2 * 4 + q]) + red[3 * 4 + q];
-                                atomicAdd(p.dpalette + pg + q, s);
-                            }
+                        const int et = threadIdx.x - 64;
+                        if (et < 4 && ti * 128 < p.I) {
+                            float s = 0.f;
+#pragma unroll
+                            for (int w8 = 0; w8 < 8; ++w8) s += red[w8 * 4 + et];
+                            atomicAdd(p.dpalette + pg - 0 + et, s);
                         }
                         epi_bar_sync();
                     }
@@ -377,10 +477,10 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 // host side
 // ---------------------------------------------------------------------------------------------
 
-template <int EPI, typename LogitT>
+template <int EPI, typename LogitT, bool ROWS_K>
 static int launch_tn_t(const TnArgs& a, const TnParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ,
                        int grid, cudaStream_t stream) {
-    auto kern = tn_gemm_kernel<EPI, LogitT>;
+    auto kern = tn_gemm_kernel<EPI, LogitT, ROWS_K>;
     static bool attr_set[64] = {};
     int dev = 0;
     PLZ_CUDA_CHECK(cudaGetDevice(&dev));
@@ -415,18 +515,21 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
         if (!a.palette) { set_last_error("tn_gemm: null palette"); return PLZ_ERR_NULL; }
         if (a.gs_n <= 0 || a.gs_k <= 0) { set_last_error("tn_gemm: bad group sizes"); return PLZ_ERR_BAD_SHAPE; }
         if (a.rows_are_k) {
-            // a 128-row tile of k must not straddle two palette groups, one group per column n
+            // rows of D are input columns k: every weight row n has its own palettes, a 128-row tile lies in one k-group
             if (a.gs_n != 1 || a.gs_k % 128) {
                 set_last_error("tn_gemm: rows=k layout needs gs_n == 1 and gs_k %% 128 == 0 (got %d, %d)", a.gs_n, a.gs_k);
                 return PLZ_ERR_UNSUPPORTED;
             }
-        } else {
-            if (a.gs_n % 128 || (a.gs_k % 256 && a.n_kgroups != 1) || a.I % 128) {
-                set_last_error("tn_gemm: rows=n layout needs gs_n %% 128 == 0, gs_k %% 256 == 0 (or gs_k == K), N %% 128 == 0 (got %d, %d, %d)", a.gs_n, a.gs_k, a.I);
+            if (a.epi == EPI_SOFT && (a.logits_f16 || a.ls_p != 1 || (a.noise_mode == NOISE_TENSOR && a.ns_p != 1))) {
+                set_last_error("tn_gemm: rows=k layout needs interleaved fp32 logits and noise");
                 return PLZ_ERR_UNSUPPORTED;
             }
+        } else if ((a.gs_n != 1 && a.gs_n % 128) || (a.gs_k % 256 && a.n_kgroups != 1)) {
+            // rows of D are weight rows n: a 128-row tile lies in one n-group (or every row is its own group),
+            // and a 256-column tile in one k-group
+            set_last_error("tn_gemm: palette groups must be gs_n == 1 or gs_n %% 128 == 0, and gs_k %% 256 == 0 or gs_k == K (got %d, %d)", a.gs_n, a.gs_k);
+            return PLZ_ERR_UNSUPPORTED;
         }
-        p.rows_are_k = a.rows_are_k;
         p.logits = a.logits; p.dlogits = a.dlogits;
         p.ls_row = a.ls_row; p.ls_col = a.ls_col; p.ls_p = a.ls_p;
         p.noise = a.noise; p.ns_row = a.ns_row; p.ns_col = a.ns_col; p.ns_p = a.ns_p;
@@ -455,11 +558,14 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
     int sms = a.sm_count > 0 ? a.sm_count : 148;
     const int grid = tiles < sms ? tiles : sms;
     switch (a.epi) {
-        case EPI_STORE: return launch_tn_t<EPI_STORE, float>(a, p, tmP, tmQ, grid, stream);
-        case EPI_HARD: return launch_tn_t<EPI_HARD, float>(a, p, tmP, tmQ, grid, stream);
+        case EPI_STORE: return launch_tn_t<EPI_STORE, float, false>(a, p, tmP, tmQ, grid, stream);
+        case EPI_HARD:
+            return a.rows_are_k ? launch_tn_t<EPI_HARD, float, true>(a, p, tmP, tmQ, grid, stream)
+                                : launch_tn_t<EPI_HARD, float, false>(a, p, tmP, tmQ, grid, stream);
         case EPI_SOFT:
-            return a.logits_f16 ? launch_tn_t<EPI_SOFT, __half>(a, p, tmP, tmQ, grid, stream)
-                                : launch_tn_t<EPI_SOFT, float>(a, p, tmP, tmQ, grid, stream);
+            if (a.rows_are_k) return launch_tn_t<EPI_SOFT, float, true>(a, p, tmP, tmQ, grid, stream);
+            return a.logits_f16 ? launch_tn_t<EPI_SOFT, __half, false>(a, p, tmP, tmQ, grid, stream)
+                                : launch_tn_t<EPI_SOFT, float, false>(a, p, tmP, tmQ, grid, stream);
     }
     set_last_error("tn_gemm: unknown epilogue %d", a.epi);
     return PLZ_ERR_UNSUPPORTED;

@@ -1,0 +1,48 @@
+"""Run one kernel of the hot path a few times on a small case, for `ncu` captures.
+
+    python qwen-palettize_b200/profile_case.py --case fwd|dx|dw|smallm|select [--M 4096] [--N 9728] [--K 2560] [--iters 3]
+
+The shapes keep the full weight matrix of the benchmark Linear (so per-tile behaviour is the benchmark's) and cut
+the token count; everything held on the device stays under 2 GB.
+"""
+import argparse
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import plz_native  # noqa: E402
+import plz_ops as ops  # noqa: E402
+import synth  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True, choices=["fwd", "dx", "dw", "smallm", "select"])
+    ap.add_argument("--M", type=int, default=4096)
+    ap.add_argument("--N", type=int, default=9728)
+    ap.add_argument("--K", type=int, default=2560)
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    d = synth.make_linear_inputs_cuda(a.M, a.N, a.K, seed=0)
+    pal = d["palette"].reshape(-1, 4).contiguous()
+    w = ops.PackedWeight(ops.pack_indices(d["idx"].view(torch.int8), n_major=True), pal, a.N, a.K, 1, 256)
+    lora = (d["lora_a"], d["lora_b"], 1.0)
+    for _ in range(a.iters):
+        if a.case == "fwd":
+            ops.hard_forward(w, d["x"], lora)
+        elif a.case == "dx":
+            ops.backward_dx(w, d["dy"], lora)
+        elif a.case == "dw":
+            ops.backward_dw_soft(w, d["x"], d["dy"], d["logits"], "nk4", noise=d["noise"], tau=1.0)
+        elif a.case == "smallm":
+            ops.hard_forward_smallm(w, d["x"][: min(a.M, 64)].contiguous())
+        else:
+            ops.soft_select(w, d["logits"], "nk4", noise=d["noise"], tau=1.0, want_packed=True)
+    torch.cuda.synchronize()
+    print("status", plz_native.device_status())
+
+
+if __name__ == "__main__":
+    main()
