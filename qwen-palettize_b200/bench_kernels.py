@@ -1,0 +1,96 @@
+"""Per-kernel measurements that complement bench.py (which times the whole training step of one Linear):
+
+  smallm   hard forward at decode batch sizes M in {1, 8, 16, 64}: achieved GB/s on the packed weights
+           (N*K/4 index bytes + palette bytes per launch) against the measured HBM copy bandwidth.
+           The weights rotate over enough copies to exceed the 126 MB L2, so every launch reads HBM.
+  config0  hard forward at M = 512 (BASELINE config 0): time and TFLOP/s of the tiled tcgen05 kernel.
+  select   logits -> packed argmax indices: GB/s on the 16 bytes per weight it reads.
+
+    python qwen-palettize_b200/bench_kernels.py [--iters 200]
+Prints one JSON object per measurement.  Timing: CUDA events on the launching stream around `iters` back-to-back
+launches after 10 warm-up launches.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import plz_native  # noqa: E402
+import plz_ops as ops  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timed(fn_i, iters, warm=10):
+    for i in range(warm):
+        fn_i(i)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fn_i(i)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters  # ms
+
+
+def make_weights(N, K, copies, dev):
+    g = torch.Generator(device=dev).manual_seed(0)
+    ws = []
+    for _ in range(copies):
+        idx = torch.randint(0, 4, (N, K), generator=g, device=dev, dtype=torch.uint8)
+        pal = (torch.randn(N * (K // 256), 4, generator=g, device=dev) * 0.02).sort(-1).values.to(torch.bfloat16)
+        ws.append(ops.PackedWeight(ops.pack_indices(idx.view(torch.int8), n_major=True), pal, N, K, 1, 256))
+        del idx
+    return ws
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=200)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm, tf, src = peaks()
+    for (N, K) in [(9728, 2560), (2560, 9728), (4096, 2560)]:
+        wbytes = N * K // 4 + N * (K // 256) * 8
+        copies = max(2, (2 * 126 * 2 ** 20) // wbytes + 1)
+        ws = make_weights(N, K, copies, dev)
+        for M in (1, 8, 16, 64):
+            x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+            ms = timed(lambda i: ops.hard_forward_smallm(ws[i % copies], x), a.iters)
+            gbs = wbytes / (ms * 1e-3) / 1e9
+            print(json.dumps({"kernel": "lut_gemv_kernel", "case": "smallm", "M": M, "N": N, "K": K, "us": ms * 1e3,
+                              "weight_bytes": wbytes, "GBps": gbs, "hbm_peak_GBps": hbm, "frac": gbs / hbm,
+                              "peak_source": src, "weight_copies_rotated": copies}))
+        if (N, K) == (9728, 2560):
+            x = torch.randn(512, K, device=dev).to(torch.bfloat16)
+            ms = timed(lambda i: ops.hard_forward(ws[i % copies], x), a.iters)
+            fl = 2.0 * 512 * N * K
+            print(json.dumps({"kernel": "lut_gemm_kernel<2,B_DECODE_K>", "case": "config0", "M": 512, "N": N, "K": K,
+                              "us": ms * 1e3, "TFLOPs": fl / (ms * 1e-3) / 1e12, "tensor_peak_TFLOPs": tf,
+                              "frac": fl / (ms * 1e-3) / 1e12 / tf, "peak_source": src}))
+        del ws
+    N, K = 9728, 2560
+    logits = torch.randn(N, K, 4, device=dev)
+    w = ops.PackedWeight(ops.empty_packed(N, K, dev), torch.zeros(N * (K // 256), 4, dtype=torch.bfloat16, device=dev), N, K, 1, 256)
+    ms = timed(lambda i: ops.soft_select(w, logits, "nk4", want_packed=True), 50)
+    rb = N * K * 16 + N * K // 4
+    print(json.dumps({"kernel": "soft_select_kfast_kernel", "case": "select", "N": N, "K": K, "us": ms * 1e3, "bytes": rb,
+                      "GBps": rb / (ms * 1e-3) / 1e9, "hbm_peak_GBps": hbm, "frac": rb / (ms * 1e-3) / 1e9 / hbm,
+                      "peak_source": src}))
+    print(json.dumps({"status": list(plz_native.device_status())}))
+
+
+if __name__ == "__main__":
+    main()

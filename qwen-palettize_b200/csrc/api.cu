@@ -54,7 +54,7 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t c
     static thread_local int bound_dev = -1;
     int dev = -1;
     if (cudaGetDevice(&dev) == cudaSuccess && dev != bound_dev) {
-        cudaFree(nullptr);
+        cudaSetDevice(dev);  // binds the primary context to this thread (allocates nothing)
         bound_dev = dev;
     }
     if (!enc) { set_last_error("cuTensorMapEncodeTiled is not available from the driver"); return PLZ_ERR_CUDA; }
