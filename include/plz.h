@@ -107,6 +107,20 @@ int32_t plz_dequantize(const plz_weight_t* w, void* dst, int64_t d_n, int64_t d_
 int32_t plz_hard_fwd(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const plz_lora_t* lora,
                      void* t, void* y, int64_t ldy, void* stream);
 
+/* plz_hard_fwd with LoRA for callers that must not allocate. (No counterpart in the reference: its wrappers
+ * allocate every intermediate through torch.)  Some hosts hand an operator its inputs and outputs and nothing
+ * else: the host owns the whole device-memory pool, so a cudaMalloc inside the operator can fail or stall the
+ * device, and there is no workspace argument to pass `t` through. For them the [M, rank] intermediate
+ * scale * x A^T lives in a fixed 512 KiB array inside the library (every GPU that loads libplz.so holds it until
+ * the process exits). Limits: M * rank <= 262144 elements (4096 rows at rank 64, 16384 rows at rank 16); larger
+ * calls return PLZ_ERR_TOO_LARGE and change nothing. The first call on each device looks up the array's device
+ * address (cudaGetSymbolAddress); make that first call outside any stream capture. The call itself performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine. All calls on a device share the one array and it
+ * keeps the previous call's contents: rows [0, M) are rewritten before they are read, nothing needs to start at
+ * zero, but two calls whose kernels overlap on the GPU (different streams) race on it -- serialize them. */
+int32_t plz_hard_fwd_lora_static(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const plz_lora_t* lora,
+                                 void* y, int64_t ldy, void* stream);
+
 /* Same product for 1 <= M <= 64 rows (token decode), written for the HBM roofline of the packed
  * weights: every SM streams its own range of weight rows exactly once. No LoRA branch. The
  * reference has no separate small-batch kernel: its hard forward (scripts/qwen_model.py:164-192,

@@ -198,6 +198,48 @@ int32_t plz_hard_fwd(const plz_weight_t* w, const void* x, int64_t ldx, int32_t 
     return launch_lut_gemm(g, s);
 }
 
+// ---- allocation-free LoRA forward ---------------------------------------------------------------
+// Scratch for plz_hard_fwd_lora_static: the [M, rank] bf16 intermediate scale * x A^T. It lives in the
+// library image, so every GPU that loads libplz.so carries these 512 KiB until the process exits.
+#define PLZ_STATIC_LORA_ELEMS (4096 * 64)
+static __device__ __align__(256) __nv_bfloat16 g_lora_scratch[PLZ_STATIC_LORA_ELEMS];
+
+// In host code `g_lora_scratch` is only a handle for the runtime, never an address a kernel may use: the
+// device address is looked up once per device (with that device current) and cached.
+static int lora_scratch_ptr(void** out) {
+    static void* ptrs[64] = {};
+    int dev = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) { set_last_error("device index %d out of range", dev); return PLZ_ERR_UNSUPPORTED; }
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_lora_scratch);
+        if (e != cudaSuccess || !p) {
+            set_last_error("cudaGetSymbolAddress(g_lora_scratch) failed: %s", cudaGetErrorString(e));
+            return PLZ_ERR_CUDA;
+        }
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return PLZ_OK;
+}
+
+int32_t plz_hard_fwd_lora_static(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const plz_lora_t* lora,
+                                 void* y, int64_t ldy, void* stream) {
+    if (!lora) { set_last_error("plz_hard_fwd_lora_static needs a LoRA descriptor; without LoRA call plz_hard_fwd"); return PLZ_ERR_NULL; }
+    if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; }
+    if (lora->rank > 0 && (long long)M * lora->rank > PLZ_STATIC_LORA_ELEMS) {
+        set_last_error("plz_hard_fwd_lora_static: M * rank = %lld exceeds the built-in scratch of %d elements "
+                       "(e.g. 4096 rows at rank 64, 16384 rows at rank 16); use plz_hard_fwd with your own workspace",
+                       (long long)M * lora->rank, PLZ_STATIC_LORA_ELEMS);
+        return PLZ_ERR_TOO_LARGE;
+    }
+    void* t = nullptr;
+    int rc = lora_scratch_ptr(&t);
+    if (rc) return rc;
+    return plz_hard_fwd(w, x, ldx, M, lora, t, y, ldy, stream);
+}
+
 int32_t plz_hard_fwd_smallm(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, void* y, int64_t ldy,
                             void* stream) {
     int rc = check_weight(w, true);

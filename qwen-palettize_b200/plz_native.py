@@ -47,6 +47,7 @@ SIGNATURES = {
     "plz_unpack_indices": [_P, _I64, _I32, _I32, _P, _I64, _I64, _P],
     "plz_dequantize": [_WP, _P, _I64, _I64, _P],
     "plz_hard_fwd": [_WP, _P, _I64, _I32, _LP, _P, _P, _I64, _P],
+    "plz_hard_fwd_lora_static": [_WP, _P, _I64, _I32, _LP, _P, _I64, _P],
     "plz_hard_fwd_smallm": [_WP, _P, _I64, _I32, _P, _I64, _P],
     "plz_soft_select": [_WP, _GP, _NP, _F, _I32, _P, _I64, _I64, _P],
     "plz_dense_fwd": [_P, _I64, _I32, _I32, _P, _I64, _I32, _LP, _P, _P, _I64, _P],
