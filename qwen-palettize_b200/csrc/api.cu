@@ -132,7 +132,13 @@ static int lora_up_bwd(const plz_lora_t* l, const void* dY, long long lddy, int 
 
 using namespace plz;
 
+static void* g_prof_buffer = nullptr;
+
 extern "C" {
+
+// Diagnostics: point the LUT GEMM at a device buffer of 8 x uint64 per CTA that receives the MMA thread's
+// cycle counts (wait for TMA, wait for decode, main loop). NULL (default) turns it off. Not part of the ABI.
+void plz_debug_set_profile_buffer(void* dev_ptr) { g_prof_buffer = dev_ptr; }
 
 int32_t plz_version(void) { return 100; }
 const char* plz_last_error(void) { return g_err; }
@@ -194,7 +200,7 @@ int32_t plz_hard_fwd(const plz_weight_t* w, const void* x, int64_t ldx, int32_t 
     g.packed = w->packed; g.packed_pitch = w->packed_pitch; g.palette = w->palette;
     g.gs_n = w->gs_n; g.gs_k = w->gs_k; g.Wn = w->N; g.Wk = w->K;
     if (lora) { g.r2 = lora->rank; g.A2 = t; g.lda2 = lora->rank; g.B2 = lora->B; g.ldb2 = lora->ldb; }
-    g.out = y; g.ld_out = ldy; g.alpha = 1.0f;
+    g.out = y; g.ld_out = ldy; g.alpha = 1.0f; g.prof = g_prof_buffer;
     return launch_lut_gemm(g, s);
 }
 

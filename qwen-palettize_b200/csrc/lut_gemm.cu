@@ -3,7 +3,7 @@
 //
 // A always arrives by TMA (row-major, reduction index contiguous: the activations x or the
 // upstream gradient dY). B is the palettized weight matrix W[N, K] and is *produced inside the
-// kernel*: eight decode warps read the packed 2-bit indices and the 4-entry bf16 palettes from
+// kernel*: sixteen decode warps read the packed 2-bit indices and the 4-entry bf16 palettes from
 // global memory and write bf16 tiles straight into the 128-byte-swizzled shared-memory layout the
 // tensor core reads, so no decoded weight ever exists in HBM.
 //
@@ -29,15 +29,17 @@ struct LutGemmParams {
     long long packed_pitch;
     const __nv_bfloat16* palette;  // [(n / gs_n) * n_kgroups + k / gs_k][4]
     int gs_n, gs_k, n_kgroups;
+    int gs_n_shift;      // log2(gs_n) when gs_n is a power of two, else -1
     int Wn, Wk;          // weight matrix extents (N, K)
     __nv_bfloat16* out;
     long long ld_out;
     float alpha;
     StatusWord* status;
+    unsigned long long* prof;  // optional [gridDim][8] cycle counters: MMA thread wait A, wait B, main loop; CTA phases
 };
 
-constexpr int kThreads = 320;       // warp 0: TMA, warp 1: MMA, warps 2..9: decode + epilogue
-constexpr int kDecodeThreads = 256;
+constexpr int kThreads = 576;       // warp 0: TMA, warp 1: MMA, warps 2..17: decode + epilogue
+constexpr int kDecodeThreads = 512;
 constexpr int kBK = 64;             // reduction elements per stage (128 bytes of bf16)
 constexpr int kBN = 256;            // D columns per CTA
 constexpr uint32_t kBBytes = kBN * kBK * 2;
@@ -73,6 +75,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         reinterpret_cast<volatile uint32_t*>(smem + C::STAGES * C::STAGE_BYTES + 8 * (3 * C::STAGES + 1));
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
+    const long long t_entry = p.prof ? clock64() : 0;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int j0 = blockIdx.x * kBN;
@@ -156,13 +159,18 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (lane == 0) {
             constexpr uint32_t idesc_main = make_idesc(128, kBN, 0, kBMn ? 1 : 0);
             bool ok = true;
+            long long wait_a = 0, wait_b = 0;
+            const long long t_begin = p.prof ? clock64() : 0;
             for (int it = 0; it < nkb_total && ok; ++it) {
                 const int s = it % C::STAGES;
                 const uint32_t ph = (it / C::STAGES) & 1;
                 const bool extra = it >= nkb;
+                const long long c0 = p.prof ? clock64() : 0;
                 ok = mbar_wait(full_a(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
+                const long long c1 = p.prof ? clock64() : 0;
                 if (ok && kDecode && !extra)
                     ok = mbar_wait(full_b(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 2);
+                if (p.prof) { wait_a += c1 - c0; wait_b += clock64() - c1; }
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t sA = base + s * C::STAGE_BYTES;
@@ -180,70 +188,95 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 umma_commit(empty(s));
             }
             if (ok) umma_commit(accum_full);
+            if (p.prof) {
+                unsigned long long* q = p.prof + 8ull * (blockIdx.y * gridDim.x + blockIdx.x);
+                q[0] = wait_a; q[1] = wait_b; q[2] = clock64() - t_begin; q[3] = t_begin - t_entry;
+            }
         }
     } else {
         // ------------------------------------------------------------- decode warps, then epilogue
         const int t = threadIdx.x - 64;
         bool ok = true;
         if (kDecode) {
-            // forward: thread owns tile row n = j0 + t and decodes 64 consecutive k per stage.
-            // backward: thread owns (n = it*64 + t/4, 64 consecutive k starting at j0 + (t%4)*64).
-            const int q = t & 3;
-            const int rr = (BMODE == B_DECODE_K) ? t : (t >> 2);
-            auto src_n = [&](int it) { return (BMODE == B_DECODE_K) ? (j0 + t) : (it * kBK + rr); };
-            auto src_k = [&](int it) { return (BMODE == B_DECODE_K) ? (it * kBK) : (j0 + q * 64); };
+            // Each of the 512 decode threads produces 32 weights (four 16-byte chunks of one 128-byte operand row)
+            // per stage from 8 bytes of packed indices.
+            // forward:  row = tile row n - j0 = t / 2, chunks 4*(t%2)..; k runs with the stage.
+            // backward: row = n - it*64 = t / 8, 64-wide k block a = (t%8)/2, chunks 4*(t%2)..; n runs with the stage.
+            const int h = t & 1;
+            const int rr = (BMODE == B_DECODE_K) ? (t >> 1) : (t >> 3);
+            const int a = (t >> 1) & 3;
+            const int k_fixed = j0 + a * 64 + h * 32;  // backward only
+            auto src_n = [&](int it) { return (BMODE == B_DECODE_K) ? (j0 + rr) : (it * kBK + rr); };
+            auto src_k = [&](int it) { return (BMODE == B_DECODE_K) ? (it * kBK + h * 32) : k_fixed; };
             auto in_range = [&](int it) { return it < nkb && src_n(it) < p.Wn && src_k(it) < p.Wk; };
-            auto load_idx = [&](int it) -> uint4 {
-                if (!in_range(it)) return make_uint4(0, 0, 0, 0);
-                return __ldg(reinterpret_cast<const uint4*>(p.packed + (long long)src_n(it) * p.packed_pitch +
+            auto load_idx = [&](int it) -> uint2 {
+                if (!in_range(it)) return make_uint2(0, 0);
+                return __ldg(reinterpret_cast<const uint2*>(p.packed + (long long)src_n(it) * p.packed_pitch +
                                                             (src_k(it) >> 2)));
             };
-            auto load_pal = [&](int it) -> uint2 {
+            // palette group of the stage: one of (n / gs_n, k / gs_k) is fixed per thread, the other advances
+            const int ng_fixed = (BMODE == B_DECODE_K) ? ((j0 + rr) / p.gs_n) : 0;
+            const int kg_fixed = (BMODE == B_DECODE_K) ? 0 : (k_fixed / p.gs_k);
+            // kg = k group of stage `it` (forward only), carried incrementally to keep divisions out of the loop
+            auto load_pal = [&](int it, int kg) -> uint2 {
                 if (!in_range(it)) return make_uint2(0, 0);
-                const long long g = (long long)(src_n(it) / p.gs_n) * p.n_kgroups + src_k(it) / p.gs_k;
+                long long g;
+                if (BMODE == B_DECODE_K) g = (long long)ng_fixed * p.n_kgroups + kg;
+                else g = (long long)((p.gs_n_shift >= 0) ? ((it * kBK + rr) >> p.gs_n_shift) : ((it * kBK + rr) / p.gs_n)) * p.n_kgroups + kg_fixed;
                 return __ldg(reinterpret_cast<const uint2*>(p.palette + g * 4));
             };
-            uint4 idx_cur = load_idx(0);
-            uint2 pal_cur = load_pal(0);
+            const int blocks_per_kgroup = p.gs_k / kBK;
+            int pf_kg = 0, pf_cnt = 0;  // k group and position inside it of the next stage to prefetch
+            auto advance_kg = [&]() { if (++pf_cnt == blocks_per_kgroup) { pf_cnt = 0; ++pf_kg; } };
+            // software prefetch kPF stages ahead: the index / palette loads come from L2 or HBM and one stage of
+            // MMA work (about a thousand cycles) does not cover their latency
+            constexpr int kPF = 4;
+            uint2 idx_q[kPF], pal_q[kPF];
+#pragma unroll
+            for (int j = 0; j < kPF; ++j) { idx_q[j] = load_idx(j); pal_q[j] = load_pal(j, pf_kg); advance_kg(); }
             for (int it = 0; it < nkb; ++it) {
                 const int s = it % C::STAGES;
                 const uint32_t ph = (it / C::STAGES) & 1;
-                const uint4 idx_nxt = load_idx(it + 1);
-                const uint2 pal_nxt = load_pal(it + 1);
+                const uint2 idx_cur = idx_q[0], pal_cur = pal_q[0];
+#pragma unroll
+                for (int j = 0; j + 1 < kPF; ++j) { idx_q[j] = idx_q[j + 1]; pal_q[j] = pal_q[j + 1]; }
+                idx_q[kPF - 1] = load_idx(it + kPF);
+                pal_q[kPF - 1] = load_pal(it + kPF, pf_kg);
+                advance_kg();
                 ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 3);
                 if (!ok) break;
                 uint8_t* sB = smem + s * C::STAGE_BYTES + C::A_BYTES;
-                uint8_t* row = (BMODE == B_DECODE_K) ? (sB + rr * 128) : (sB + q * 8192 + rr * 128);
+                uint8_t* row = (BMODE == B_DECODE_K) ? (sB + rr * 128) : (sB + a * 8192 + rr * 128);
                 const PalRegs pal = pal_split(pal_cur.x, pal_cur.y);
-                const uint32_t w[4] = {idx_cur.x, idx_cur.y, idx_cur.z, idx_cur.w};
+                const uint32_t w[2] = {idx_cur.x, idx_cur.y};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < 2; ++i) {
                     uint32_t o[8];
                     decode16(w[i], pal, o);
-                    // word i covers 16 elements = 16-byte chunks 2i and 2i+1 of the 128-byte row
-                    *reinterpret_cast<uint4*>(row + (((2 * i) ^ (rr & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4*>(row + (((2 * i + 1) ^ (rr & 7)) << 4)) =
+                    // word i covers 16 elements = 16-byte chunks 4h + 2i and 4h + 2i + 1 of the 128-byte row
+                    *reinterpret_cast<uint4*>(row + (((4 * h + 2 * i) ^ (rr & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(row + (((4 * h + 2 * i + 1) ^ (rr & 7)) << 4)) =
                         make_uint4(o[4], o[5], o[6], o[7]);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_b(s));
-                idx_cur = idx_nxt;
-                pal_cur = pal_nxt;
             }
         }
         // ---- epilogue: TMEM -> registers -> bf16 -> global
+        const long long t_dec_done = p.prof ? clock64() : 0;
         if (ok) ok = mbar_wait(accum_full, 0, abort_flag, p.status, ST_TIMEOUT_ACCUM, 4);
+        const long long t_acc = p.prof ? clock64() : 0;
         if (ok) {
             tc_fence_after_sync();
-            const int lane_group = warp & 3;      // TMEM lanes this warp may read
-            const int col_half = (warp - 2) >> 2;  // which 128 columns of the tile
+            const int lane_group = warp & 3;          // TMEM lanes this warp may read
+            const int col_quarter = (warp - 2) >> 2;  // which 64 columns of the tile
 #pragma unroll 1
             for (int mt = 0; mt < MT; ++mt) {
                 const int m = m0 + mt * 128 + lane_group * 32 + lane;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    const int col = col_half * 128 + c * 32;
+                for (int c = 0; c < 2; ++c) {
+                    const int col = col_quarter * 64 + c * 32;
                     uint32_t v[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + mt * 256u + col, v);
                     if (m < p.M) {
@@ -263,6 +296,10 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         }
+        if (p.prof && t == 0) {
+            unsigned long long* q = p.prof + 8ull * (blockIdx.y * gridDim.x + blockIdx.x);
+            q[4] = t_dec_done - t_entry; q[5] = t_acc - t_entry; q[6] = clock64() - t_entry;
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -270,6 +307,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
+    if (p.prof && threadIdx.x == 0) p.prof[8ull * (blockIdx.y * gridDim.x + blockIdx.x) + 7] = clock64() - t_entry;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -303,9 +341,12 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
     p.palette = (const __nv_bfloat16*)a.palette;
     p.gs_n = a.gs_n > 0 ? a.gs_n : 1; p.gs_k = a.gs_k > 0 ? a.gs_k : 1;
     p.n_kgroups = a.gs_k > 0 ? (a.Wk / a.gs_k) : 1;
+    p.gs_n_shift = -1;
+    for (int sh = 0; sh < 31; ++sh) if ((1 << sh) == p.gs_n) p.gs_n_shift = sh;
     p.Wn = a.Wn; p.Wk = a.Wk;
     p.out = (__nv_bfloat16*)a.out; p.ld_out = a.ld_out; p.alpha = a.alpha;
     p.status = device_status_ptr();
+    p.prof = (unsigned long long*)a.prof;
     auto kern = lut_gemm_kernel<MT, BMODE>;
     static bool attr_set = false;  // per instantiation; the attribute is per device function
     if (!attr_set) {

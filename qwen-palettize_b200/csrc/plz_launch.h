@@ -18,6 +18,7 @@ struct LutGemmArgs {
     // optional extra block: A2 [M, r2] (pitch lda2); B2: K-major modes [J, r2], MN-major modes [r2, J]
     int r2; const void* A2; long long lda2; const void* B2; long long ldb2;
     void* out; long long ld_out; float alpha;
+    void* prof;  // optional device buffer of cycle counters, 8 x uint64 per CTA (diagnostics)
 };
 int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream);
 
