@@ -14,6 +14,12 @@
 // The optional second product (A2, B2) is one extra 64-wide reduction block appended to the main
 // loop: the LoRA branch y += (s x A^T) B^T, or dX += dt A, accumulated into the same TMEM tile.
 //
+// Persistent: one CTA per SM walks the 256 x 256 output tiles (column tile fastest, so the CTAs that run
+// together share the same rows of A in L2). Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..17
+// decode, warps 18..25 epilogue. While the epilogue warps drain a finished accumulator (TMEM -> bf16 ->
+// swizzled shared memory -> TMA store, full 128-byte lines), the producer and decode warps already fill
+// the pipeline for the next tile; the MMA resumes as soon as the last tcgen05.ld of the tile has retired.
+//
 // Replaces, in the reference: fused_lut_linear_fwd_tc_kernel (scripts/fused_lut_kernel.cu:309),
 // fused_lut_linear_bwd_grad_x_tc_kernel (:551), the cuBLAS calls of the soft path
 // (scripts/fused_lut_linear_cuda.py:912, :944) and the eager LoRA matmuls (scripts/qwen_model.py:300-304).
@@ -21,28 +27,30 @@
 
 namespace plz {
 
-
 struct LutGemmParams {
     int M, J, R;         // D is [M, J]; R = reduction length of the main product (multiple of 64)
     int n_extra;         // 64-wide reduction blocks taken from (A2, B2): 0 or 1
+    int tiles_m, tiles_j;
     const uint8_t* packed;  // W indices, [Wn, packed_pitch] bytes, 4 per byte along K, LSB first
     long long packed_pitch;
     const __nv_bfloat16* palette;  // [(n / gs_n) * n_kgroups + k / gs_k][4]
     int gs_n, gs_k, n_kgroups;
     int gs_n_shift;      // log2(gs_n) when gs_n is a power of two, else -1
     int Wn, Wk;          // weight matrix extents (N, K)
-    __nv_bfloat16* out;
-    long long ld_out;
     float alpha;
     StatusWord* status;
-    unsigned long long* prof;  // optional [gridDim][8] cycle counters: MMA thread wait A, wait B, main loop; CTA phases
+    unsigned long long* prof;  // optional [gridDim][8] cycle counters of the MMA thread (diagnostics)
 };
 
-constexpr int kThreads = 576;       // warp 0: TMA, warp 1: MMA, warps 2..17: decode + epilogue
-constexpr int kDecodeThreads = 512;
+constexpr int kDecodeWarps = 16;
+constexpr int kEpiWarps = 8;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kFirstEpiWarp = 2 + kDecodeWarps;
+constexpr int kThreads = (2 + kDecodeWarps + kEpiWarps) * 32;  // 832
 constexpr int kBK = 64;             // reduction elements per stage (128 bytes of bf16)
-constexpr int kBN = 256;            // D columns per CTA
+constexpr int kBN = 256;            // D columns per tile
 constexpr uint32_t kBBytes = kBN * kBK * 2;
+constexpr uint32_t kEpiStageBytes = 32 * 64 * 2;  // one 32-row x 64-column bf16 box per epilogue warp
 
 template <int MT>
 struct Cfg {
@@ -50,14 +58,16 @@ struct Cfg {
     static constexpr uint32_t A_BYTES = MT * 128 * kBK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + kBBytes;
     static constexpr uint32_t TMEM_COLS = MT * 256;
-    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES;
+    static constexpr uint32_t BAR_OFF = EPI_OFF + kEpiWarps * kEpiStageBytes;
+    static constexpr uint32_t SMEM_BYTES = BAR_OFF + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int MT, int BMODE>
 __global__ void __launch_bounds__(kThreads, 1)
 lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                const LutGemmParams p) {
+                const __grid_constant__ CUtensorMap tmD, const LutGemmParams p) {
     using C = Cfg<MT>;
     constexpr bool kDecode = (BMODE == B_DECODE_K || BMODE == B_DECODE_MN);
     constexpr bool kBMn = (BMODE == B_DECODE_MN || BMODE == B_TMA_MN);
@@ -66,33 +76,33 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (base - raw);
-    const uint32_t bar_base = base + C::STAGES * C::STAGE_BYTES;
+    const uint32_t bar_base = base + C::BAR_OFF;
     auto full_a = [&](int s) { return bar_base + 8u * s; };
     auto full_b = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
     auto empty = [&](int s) { return bar_base + 8u * (2 * C::STAGES + s); };
     const uint32_t accum_full = bar_base + 8u * (3 * C::STAGES);
-    volatile uint32_t* tmem_slot =
-        reinterpret_cast<volatile uint32_t*>(smem + C::STAGES * C::STAGE_BYTES + 8 * (3 * C::STAGES + 1));
+    const uint32_t tmem_empty = bar_base + 8u * (3 * C::STAGES + 1);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::BAR_OFF + 8 * (3 * C::STAGES + 2));
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
-    const long long t_entry = p.prof ? clock64() : 0;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int j0 = blockIdx.x * kBN;
-    const int m0 = blockIdx.y * (128 * MT);
     const int nkb = p.R / kBK;
     const int nkb_total = nkb + p.n_extra;
+    const int n_tiles = p.tiles_m * p.tiles_j;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
             mbar_init(full_a(s), 1);
-            mbar_init(full_b(s), kDecodeThreads / 32);
+            mbar_init(full_b(s), kDecodeWarps);
             mbar_init(empty(s), 1);
         }
         mbar_init(accum_full, 1);
+        mbar_init(tmem_empty, kEpiWarps);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmD);
         if (!kDecode) tma_prefetch_desc(&tmB);
         if (p.n_extra) {
             tma_prefetch_desc(&tmA2);
@@ -108,36 +118,47 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    // tile t -> (row tile, column tile), column tile fastest
+    auto tile_origin = [&](int t, int& m0, int& j0) {
+        j0 = (t % p.tiles_j) * kBN;
+        m0 = (t / p.tiles_j) * (128 * MT);
+    };
+
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer
         if (lane == 0) {
             int last_fill[C::STAGES];
             for (int s = 0; s < C::STAGES; ++s) last_fill[s] = -1;
             bool ok = true;
-            for (int it = 0; it < nkb_total && ok; ++it) {
-                const int s = it % C::STAGES;
-                const uint32_t ph = (it / C::STAGES) & 1;
-                ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 0);
-                if (!ok) break;
-                const uint32_t sA = base + s * C::STAGE_BYTES;
-                const uint32_t sB = sA + C::A_BYTES;
-                const bool extra = it >= nkb;
-                const uint32_t bytes = C::A_BYTES + ((extra || !kDecode) ? kBBytes : 0u);
-                mbar_arrive_expect_tx(full_a(s), bytes);
-                const CUtensorMap* ma = extra ? &tmA2 : &tmA;
-                const CUtensorMap* mb = extra ? &tmB2 : &tmB;
-                const int r0 = (extra ? (it - nkb) : it) * kBK;
+            int git = 0;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                int m0, j0;
+                tile_origin(t, m0, j0);
+                for (int it = 0; it < nkb_total; ++it, ++git) {
+                    const int s = git % C::STAGES;
+                    const uint32_t ph = (git / C::STAGES) & 1;
+                    ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 0);
+                    if (!ok) break;
+                    const uint32_t sA = base + s * C::STAGE_BYTES;
+                    const uint32_t sB = sA + C::A_BYTES;
+                    const bool extra = it >= nkb;
+                    const uint32_t bytes = C::A_BYTES + ((extra || !kDecode) ? kBBytes : 0u);
+                    mbar_arrive_expect_tx(full_a(s), bytes);
+                    const CUtensorMap* ma = extra ? &tmA2 : &tmA;
+                    const CUtensorMap* mb = extra ? &tmB2 : &tmB;
+                    const int r0 = (extra ? (it - nkb) : it) * kBK;
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) tma_load_2d(sA + mt * 16384u, ma, full_a(s), r0, m0 + mt * 128);
-                if (extra || !kDecode) {
-                    if (kBMn) {
+                    for (int mt = 0; mt < MT; ++mt) tma_load_2d(sA + mt * 16384u, ma, full_a(s), r0, m0 + mt * 128);
+                    if (extra || !kDecode) {
+                        if (kBMn) {
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) tma_load_2d(sB + q * 8192u, mb, full_a(s), j0 + q * 64, r0);
-                    } else {
-                        tma_load_2d(sB, mb, full_a(s), r0, j0);
+                            for (int q = 0; q < 4; ++q) tma_load_2d(sB + q * 8192u, mb, full_a(s), j0 + q * 64, r0);
+                        } else {
+                            tma_load_2d(sB, mb, full_a(s), r0, j0);
+                        }
                     }
+                    last_fill[s] = git;
                 }
-                last_fill[s] = it;
             }
             if (!ok) {
                 // give copies already in flight a bounded chance to land before the CTA exits
@@ -159,147 +180,189 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (lane == 0) {
             constexpr uint32_t idesc_main = make_idesc(128, kBN, 0, kBMn ? 1 : 0);
             bool ok = true;
-            long long wait_a = 0, wait_b = 0;
+            long long wait_a = 0, wait_b = 0, wait_t = 0;
             const long long t_begin = p.prof ? clock64() : 0;
-            for (int it = 0; it < nkb_total && ok; ++it) {
-                const int s = it % C::STAGES;
-                const uint32_t ph = (it / C::STAGES) & 1;
-                const bool extra = it >= nkb;
-                const long long c0 = p.prof ? clock64() : 0;
-                ok = mbar_wait(full_a(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
-                const long long c1 = p.prof ? clock64() : 0;
-                if (ok && kDecode && !extra)
-                    ok = mbar_wait(full_b(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 2);
-                if (p.prof) { wait_a += c1 - c0; wait_b += clock64() - c1; }
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t sA = base + s * C::STAGE_BYTES;
-                const uint32_t sB = sA + C::A_BYTES;
-#pragma unroll
-                for (int ks = 0; ks < kBK / 16; ++ks) {
-                    const uint64_t bdesc = kBMn ? make_sdesc(sB + ks * 2048u, 8192u, 1024u)
-                                                : make_sdesc(sB + ks * 32u, 16u, 1024u);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const uint64_t adesc = make_sdesc(sA + mt * 16384u + ks * 32u, 16u, 1024u);
-                        umma_bf16(tmem_base + mt * 256u, adesc, bdesc, idesc_main, (it > 0 || ks > 0) ? 1u : 0u);
-                    }
+            int git = 0, lt = 0;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+                if (lt > 0) {
+                    // the epilogue warps must have read the previous tile out of TMEM
+                    const long long c0 = p.prof ? clock64() : 0;
+                    ok = mbar_wait(tmem_empty, (lt - 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 1);
+                    if (p.prof) wait_t += clock64() - c0;
+                    if (!ok) break;
+                    tc_fence_after_sync();
                 }
-                umma_commit(empty(s));
+                for (int it = 0; it < nkb_total; ++it, ++git) {
+                    const int s = git % C::STAGES;
+                    const uint32_t ph = (git / C::STAGES) & 1;
+                    const bool extra = it >= nkb;
+                    const long long c0 = p.prof ? clock64() : 0;
+                    ok = mbar_wait(full_a(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
+                    const long long c1 = p.prof ? clock64() : 0;
+                    if (ok && kDecode && !extra)
+                        ok = mbar_wait(full_b(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 2);
+                    if (p.prof) { wait_a += c1 - c0; wait_b += clock64() - c1; }
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t sA = base + s * C::STAGE_BYTES;
+                    const uint32_t sB = sA + C::A_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < kBK / 16; ++ks) {
+                        const uint64_t bdesc = kBMn ? make_sdesc(sB + ks * 2048u, 8192u, 1024u)
+                                                    : make_sdesc(sB + ks * 32u, 16u, 1024u);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const uint64_t adesc = make_sdesc(sA + mt * 16384u + ks * 32u, 16u, 1024u);
+                            umma_bf16(tmem_base + mt * 256u, adesc, bdesc, idesc_main, (it > 0 || ks > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(empty(s));
+                }
+                if (ok) umma_commit(accum_full);
             }
-            if (ok) umma_commit(accum_full);
             if (p.prof) {
-                unsigned long long* q = p.prof + 8ull * (blockIdx.y * gridDim.x + blockIdx.x);
-                q[0] = wait_a; q[1] = wait_b; q[2] = clock64() - t_begin; q[3] = t_begin - t_entry;
+                unsigned long long* q = p.prof + 8ull * blockIdx.x;
+                q[0] = wait_a; q[1] = wait_b; q[2] = wait_t; q[3] = clock64() - t_begin; q[4] = lt;
             }
         }
-    } else {
-        // ------------------------------------------------------------- decode warps, then epilogue
-        const int t = threadIdx.x - 64;
-        bool ok = true;
+    } else if (warp < kFirstEpiWarp) {
+        // ------------------------------------------------------------- decode warps
         if (kDecode) {
             // Each of the 512 decode threads produces 32 weights (four 16-byte chunks of one 128-byte operand row)
             // per stage from 8 bytes of packed indices.
             // forward:  row = tile row n - j0 = t / 2, chunks 4*(t%2)..; k runs with the stage.
             // backward: row = n - it*64 = t / 8, 64-wide k block a = (t%8)/2, chunks 4*(t%2)..; n runs with the stage.
+            const int t = threadIdx.x - 64;
             const int h = t & 1;
             const int rr = (BMODE == B_DECODE_K) ? (t >> 1) : (t >> 3);
             const int a = (t >> 1) & 3;
-            const int k_fixed = j0 + a * 64 + h * 32;  // backward only
-            auto src_n = [&](int it) { return (BMODE == B_DECODE_K) ? (j0 + rr) : (it * kBK + rr); };
-            auto src_k = [&](int it) { return (BMODE == B_DECODE_K) ? (it * kBK + h * 32) : k_fixed; };
-            auto in_range = [&](int it) { return it < nkb && src_n(it) < p.Wn && src_k(it) < p.Wk; };
-            auto load_idx = [&](int it) -> uint2 {
-                if (!in_range(it)) return make_uint2(0, 0);
-                return __ldg(reinterpret_cast<const uint2*>(p.packed + (long long)src_n(it) * p.packed_pitch +
-                                                            (src_k(it) >> 2)));
-            };
-            // palette group of the stage: one of (n / gs_n, k / gs_k) is fixed per thread, the other advances
-            const int ng_fixed = (BMODE == B_DECODE_K) ? ((j0 + rr) / p.gs_n) : 0;
-            const int kg_fixed = (BMODE == B_DECODE_K) ? 0 : (k_fixed / p.gs_k);
-            // kg = k group of stage `it` (forward only), carried incrementally to keep divisions out of the loop
-            auto load_pal = [&](int it, int kg) -> uint2 {
-                if (!in_range(it)) return make_uint2(0, 0);
-                long long g;
-                if (BMODE == B_DECODE_K) g = (long long)ng_fixed * p.n_kgroups + kg;
-                else g = (long long)((p.gs_n_shift >= 0) ? ((it * kBK + rr) >> p.gs_n_shift) : ((it * kBK + rr) / p.gs_n)) * p.n_kgroups + kg_fixed;
-                return __ldg(reinterpret_cast<const uint2*>(p.palette + g * 4));
-            };
             const int blocks_per_kgroup = p.gs_k / kBK;
-            int pf_kg = 0, pf_cnt = 0;  // k group and position inside it of the next stage to prefetch
-            auto advance_kg = [&]() { if (++pf_cnt == blocks_per_kgroup) { pf_cnt = 0; ++pf_kg; } };
-            // software prefetch kPF stages ahead: the index / palette loads come from L2 or HBM and one stage of
-            // MMA work (about a thousand cycles) does not cover their latency
-            constexpr int kPF = 4;
-            uint2 idx_q[kPF], pal_q[kPF];
+            bool ok = true;
+            int git = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                int m0, j0;
+                tile_origin(tile, m0, j0);
+                const int k_fixed = j0 + a * 64 + h * 32;  // backward only
+                auto src_n = [&](int it) { return (BMODE == B_DECODE_K) ? (j0 + rr) : (it * kBK + rr); };
+                auto src_k = [&](int it) { return (BMODE == B_DECODE_K) ? (it * kBK + h * 32) : k_fixed; };
+                auto in_range = [&](int it) { return it < nkb && src_n(it) < p.Wn && src_k(it) < p.Wk; };
+                auto load_idx = [&](int it) -> uint2 {
+                    if (!in_range(it)) return make_uint2(0, 0);
+                    return __ldg(reinterpret_cast<const uint2*>(p.packed + (long long)src_n(it) * p.packed_pitch +
+                                                                (src_k(it) >> 2)));
+                };
+                // palette group of the stage: one of (n / gs_n, k / gs_k) is fixed per thread, the other advances
+                const int ng_fixed = (BMODE == B_DECODE_K) ? ((j0 + rr) / p.gs_n) : 0;
+                const int kg_fixed = (BMODE == B_DECODE_K) ? 0 : (k_fixed / p.gs_k);
+                // kg = k group of stage `it` (forward only), carried incrementally to keep divisions out of the loop
+                auto load_pal = [&](int it, int kg) -> uint2 {
+                    if (!in_range(it)) return make_uint2(0, 0);
+                    long long g;
+                    if (BMODE == B_DECODE_K) g = (long long)ng_fixed * p.n_kgroups + kg;
+                    else g = (long long)((p.gs_n_shift >= 0) ? ((it * kBK + rr) >> p.gs_n_shift) : ((it * kBK + rr) / p.gs_n)) * p.n_kgroups + kg_fixed;
+                    return __ldg(reinterpret_cast<const uint2*>(p.palette + g * 4));
+                };
+                int pf_kg = 0, pf_cnt = 0;  // k group and position inside it of the next stage to prefetch
+                auto advance_kg = [&]() { if (++pf_cnt == blocks_per_kgroup) { pf_cnt = 0; ++pf_kg; } };
+                // software prefetch kPF stages ahead: the index / palette loads come from L2 or HBM and one stage
+                // of MMA work (about a thousand cycles) does not cover their latency
+                constexpr int kPF = 4;
+                uint2 idx_q[kPF], pal_q[kPF];
 #pragma unroll
-            for (int j = 0; j < kPF; ++j) { idx_q[j] = load_idx(j); pal_q[j] = load_pal(j, pf_kg); advance_kg(); }
-            for (int it = 0; it < nkb; ++it) {
-                const int s = it % C::STAGES;
-                const uint32_t ph = (it / C::STAGES) & 1;
-                const uint2 idx_cur = idx_q[0], pal_cur = pal_q[0];
+                for (int j = 0; j < kPF; ++j) { idx_q[j] = load_idx(j); pal_q[j] = load_pal(j, pf_kg); advance_kg(); }
+                for (int it = 0; it < nkb_total; ++it, ++git) {
+                    const int s = git % C::STAGES;
+                    const uint32_t ph = (git / C::STAGES) & 1;
+                    if (it >= nkb) {
+                        // the extra (LoRA) block is filled by TMA; arrive all the same (after the stage is free, like
+                        // any other use of it) so that this barrier's phase keeps step with the ring position
+                        ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 3);
+                        if (!ok) break;
+                        if (lane == 0) mbar_arrive(full_b(s));
+                        continue;
+                    }
+                    const uint2 idx_cur = idx_q[0], pal_cur = pal_q[0];
 #pragma unroll
-                for (int j = 0; j + 1 < kPF; ++j) { idx_q[j] = idx_q[j + 1]; pal_q[j] = pal_q[j + 1]; }
-                idx_q[kPF - 1] = load_idx(it + kPF);
-                pal_q[kPF - 1] = load_pal(it + kPF, pf_kg);
-                advance_kg();
-                ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 3);
-                if (!ok) break;
-                uint8_t* sB = smem + s * C::STAGE_BYTES + C::A_BYTES;
-                uint8_t* row = (BMODE == B_DECODE_K) ? (sB + rr * 128) : (sB + a * 8192 + rr * 128);
-                const PalRegs pal = pal_split(pal_cur.x, pal_cur.y);
-                const uint32_t w[2] = {idx_cur.x, idx_cur.y};
+                    for (int j = 0; j + 1 < kPF; ++j) { idx_q[j] = idx_q[j + 1]; pal_q[j] = pal_q[j + 1]; }
+                    idx_q[kPF - 1] = load_idx(it + kPF);
+                    pal_q[kPF - 1] = load_pal(it + kPF, pf_kg);
+                    advance_kg();
+                    ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 3);
+                    if (!ok) break;
+                    uint8_t* sB = smem + s * C::STAGE_BYTES + C::A_BYTES;
+                    uint8_t* row = (BMODE == B_DECODE_K) ? (sB + rr * 128) : (sB + a * 8192 + rr * 128);
+                    const PalRegs pal = pal_split(pal_cur.x, pal_cur.y);
+                    const uint32_t w[2] = {idx_cur.x, idx_cur.y};
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    uint32_t o[8];
-                    decode16(w[i], pal, o);
-                    // word i covers 16 elements = 16-byte chunks 4h + 2i and 4h + 2i + 1 of the 128-byte row
-                    *reinterpret_cast<uint4*>(row + (((4 * h + 2 * i) ^ (rr & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4*>(row + (((4 * h + 2 * i + 1) ^ (rr & 7)) << 4)) =
-                        make_uint4(o[4], o[5], o[6], o[7]);
+                    for (int i = 0; i < 2; ++i) {
+                        uint32_t o[8];
+                        decode16(w[i], pal, o);
+                        // word i covers 16 elements = 16-byte chunks 4h + 2i and 4h + 2i + 1 of the 128-byte row
+                        *reinterpret_cast<uint4*>(row + (((4 * h + 2 * i) ^ (rr & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4*>(row + (((4 * h + 2 * i + 1) ^ (rr & 7)) << 4)) =
+                            make_uint4(o[4], o[5], o[6], o[7]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_b(s));
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_b(s));
             }
         }
-        // ---- epilogue: TMEM -> registers -> bf16 -> global
-        const long long t_dec_done = p.prof ? clock64() : 0;
-        if (ok) ok = mbar_wait(accum_full, 0, abort_flag, p.status, ST_TIMEOUT_ACCUM, 4);
-        const long long t_acc = p.prof ? clock64() : 0;
-        if (ok) {
+    } else {
+        // ------------------------------------------------------------- epilogue warps
+        // warp e reads TMEM lanes 32*(warp%4).. (its 32 output rows) and one half of the 256 columns, 64 columns
+        // at a time: fp32 -> bf16 -> 128-byte-swizzled box in shared memory -> TMA store (clipped at M and J).
+        const int e = warp - kFirstEpiWarp;
+        const int lane_group = warp & 3;
+        const int col_half = e >> 2;
+        uint8_t* stage = smem + C::EPI_OFF + e * kEpiStageBytes;
+        const uint32_t stage_u32 = base + C::EPI_OFF + e * kEpiStageBytes;
+        bool ok = true;
+        int lt = 0;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+            int m0, j0;
+            tile_origin(t, m0, j0);
+            ok = mbar_wait(accum_full, lt & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 4);
+            if (!ok) break;
             tc_fence_after_sync();
-            const int lane_group = warp & 3;          // TMEM lanes this warp may read
-            const int col_quarter = (warp - 2) >> 2;  // which 64 columns of the tile
 #pragma unroll 1
             for (int mt = 0; mt < MT; ++mt) {
-                const int m = m0 + mt * 128 + lane_group * 32 + lane;
 #pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    const int col = col_quarter * 64 + c * 32;
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + mt * 256u + col, v);
-                    if (m < p.M) {
-                        __nv_bfloat16* dst = p.out + (long long)m * p.ld_out + j0 + col;
+                for (int b = 0; b < 2; ++b) {
+                    const int col = col_half * 128 + b * 64;
+                    // the previous box must have been read out of the staging buffer
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + mt * 256u + col + c * 32, v);
+                        if (mt == MT - 1 && b == 1 && c == 1) {
+                            // last read of this tile's accumulators: hand TMEM back to the MMA warp
+                            tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(tmem_empty);
+                        }
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
-                            if (j0 + col + g * 8 < p.J) {
-                                uint4 o;
-                                o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * p.alpha, __uint_as_float(v[g * 8 + 1]) * p.alpha);
-                                o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * p.alpha, __uint_as_float(v[g * 8 + 3]) * p.alpha);
-                                o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * p.alpha, __uint_as_float(v[g * 8 + 5]) * p.alpha);
-                                o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * p.alpha, __uint_as_float(v[g * 8 + 7]) * p.alpha);
-                                *reinterpret_cast<uint4*>(dst + g * 8) = o;
-                            }
+                            uint4 o;
+                            o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * p.alpha, __uint_as_float(v[g * 8 + 1]) * p.alpha);
+                            o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * p.alpha, __uint_as_float(v[g * 8 + 3]) * p.alpha);
+                            o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * p.alpha, __uint_as_float(v[g * 8 + 5]) * p.alpha);
+                            o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * p.alpha, __uint_as_float(v[g * 8 + 7]) * p.alpha);
+                            *reinterpret_cast<uint4*>(stage + swz128(lane, c * 4 + g)) = o;
                         }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && j0 + col < p.J && m0 + mt * 128 + lane_group * 32 < p.M) {
+                        tma_store_2d(&tmD, stage_u32, j0 + col, m0 + mt * 128 + lane_group * 32);
+                        tma_store_commit();
                     }
                 }
             }
         }
-        if (p.prof && t == 0) {
-            unsigned long long* q = p.prof + 8ull * (blockIdx.y * gridDim.x + blockIdx.x);
-            q[4] = t_dec_done - t_entry; q[5] = t_acc - t_entry; q[6] = clock64() - t_entry;
-        }
+        if (lane == 0) tma_store_wait_all();
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -307,7 +370,6 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
-    if (p.prof && threadIdx.x == 0) p.prof[8ull * (blockIdx.y * gridDim.x + blockIdx.x) + 7] = clock64() - t_entry;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -317,7 +379,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 template <int MT, int BMODE>
 static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
     using C = Cfg<MT>;
-    CUtensorMap tmA, tmB, tmA2, tmB2;
+    CUtensorMap tmA, tmB, tmA2, tmB2, tmD;
     int rc;
     if ((rc = make_tmap_bf16(&tmA, a.A, a.M, a.R, a.lda, 64, 128))) return rc;
     tmB = tmA; tmA2 = tmA; tmB2 = tmA;
@@ -335,26 +397,33 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
             if ((rc = make_tmap_bf16(&tmB2, a.B2, a.J, a.r2, a.ldb2, 64, 256))) return rc;
         }
     }
+    if ((rc = make_tmap_bf16(&tmD, a.out, a.M, a.J, a.ld_out, 64, 32))) return rc;
     LutGemmParams p;
     p.M = a.M; p.J = a.J; p.R = a.R; p.n_extra = a.r2 > 0 ? 1 : 0;
+    p.tiles_j = (a.J + kBN - 1) / kBN;
+    p.tiles_m = (a.M + 128 * MT - 1) / (128 * MT);
     p.packed = (const uint8_t*)a.packed; p.packed_pitch = a.packed_pitch;
     p.palette = (const __nv_bfloat16*)a.palette;
-    p.gs_n = a.gs_n > 0 ? a.gs_n : 1; p.gs_k = a.gs_k > 0 ? a.gs_k : 1;
+    p.gs_n = a.gs_n > 0 ? a.gs_n : 1; p.gs_k = a.gs_k > 0 ? a.gs_k : kBK;
     p.n_kgroups = a.gs_k > 0 ? (a.Wk / a.gs_k) : 1;
     p.gs_n_shift = -1;
     for (int sh = 0; sh < 31; ++sh) if ((1 << sh) == p.gs_n) p.gs_n_shift = sh;
     p.Wn = a.Wn; p.Wk = a.Wk;
-    p.out = (__nv_bfloat16*)a.out; p.ld_out = a.ld_out; p.alpha = a.alpha;
+    p.alpha = a.alpha;
     p.status = device_status_ptr();
     p.prof = (unsigned long long*)a.prof;
     auto kern = lut_gemm_kernel<MT, BMODE>;
-    static bool attr_set = false;  // per instantiation; the attribute is per device function
-    if (!attr_set) {
+    static bool attr_set[64] = {};
+    int dev = 0, sms = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
         PLZ_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        attr_set = true;
+        attr_set[dev & 63] = true;
     }
-    dim3 grid((a.J + kBN - 1) / kBN, (a.M + 128 * MT - 1) / (128 * MT));
-    kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
+    PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int tiles = p.tiles_m * p.tiles_j;
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, tmD, p);
     PLZ_CUDA_CHECK(cudaGetLastError());
     return PLZ_OK;
 }
