@@ -139,6 +139,9 @@ extern "C" {
 // Diagnostics: point the LUT GEMM at a device buffer of 8 x uint64 per CTA that receives the MMA thread's
 // cycle counts (wait for TMA, wait for decode, main loop). NULL (default) turns it off. Not part of the ABI.
 void plz_debug_set_profile_buffer(void* dev_ptr) { g_prof_buffer = dev_ptr; }
+// Diagnostics: run the persistent kernels on at most `n` CTAs (0 = one per SM), so that small test problems
+// exercise the multi-tile schedule. Not part of the ABI.
+void plz_debug_set_sm_limit(int n) { g_debug_sm_limit = n; }
 
 int32_t plz_version(void) { return 100; }
 const char* plz_last_error(void) { return g_err; }

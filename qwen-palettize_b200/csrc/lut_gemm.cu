@@ -27,10 +27,14 @@
 
 namespace plz {
 
+int g_debug_sm_limit = 0;  // > 0: persistent kernels use at most this many CTAs (plz_debug_set_sm_limit)
+
 struct LutGemmParams {
     int M, J, R;         // D is [M, J]; R = reduction length of the main product (multiple of 64)
     int n_extra;         // 64-wide reduction blocks taken from (A2, B2): 0 or 1
     int tiles_m, tiles_j;
+    int n_whole;         // tiles [0, n_whole) are whole (MT row blocks); the rest of the list are single 128-row blocks
+    int n_items;         // length of the tile list
     const uint8_t* packed;  // W indices, [Wn, packed_pitch] bytes, 4 per byte along K, LSB first
     long long packed_pitch;
     const __nv_bfloat16* palette;  // [(n / gs_n) * n_kgroups + k / gs_k][4]
@@ -89,7 +93,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int lane = threadIdx.x & 31;
     const int nkb = p.R / kBK;
     const int nkb_total = nkb + p.n_extra;
-    const int n_tiles = p.tiles_m * p.tiles_j;
+    const int n_tiles = p.n_items;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -118,10 +122,18 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // tile t -> (row tile, column tile), column tile fastest
-    auto tile_origin = [&](int t, int& m0, int& j0) {
-        j0 = (t % p.tiles_j) * kBN;
-        m0 = (t / p.tiles_j) * (128 * MT);
+    // work item t -> (first row, first column, number of 128-row blocks); column tile fastest. The items of the last,
+    // partially filled round are cut into single 128-row blocks so that the round costs half as much.
+    auto tile_origin = [&](int t, int& m0, int& j0, int& nmt) {
+        int tile = t, half = 0;
+        nmt = MT;
+        if (MT == 2 && t >= p.n_whole) {
+            tile = p.n_whole + ((t - p.n_whole) >> 1);
+            half = (t - p.n_whole) & 1;
+            nmt = 1;
+        }
+        j0 = (tile % p.tiles_j) * kBN;
+        m0 = (tile / p.tiles_j) * (128 * MT) + half * 128;
     };
 
     if (warp == 0) {
@@ -132,8 +144,8 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             bool ok = true;
             int git = 0;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                int m0, j0;
-                tile_origin(t, m0, j0);
+                int m0, j0, nmt;
+                tile_origin(t, m0, j0, nmt);
                 for (int it = 0; it < nkb_total; ++it, ++git) {
                     const int s = git % C::STAGES;
                     const uint32_t ph = (git / C::STAGES) & 1;
@@ -142,13 +154,14 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const uint32_t sA = base + s * C::STAGE_BYTES;
                     const uint32_t sB = sA + C::A_BYTES;
                     const bool extra = it >= nkb;
-                    const uint32_t bytes = C::A_BYTES + ((extra || !kDecode) ? kBBytes : 0u);
+                    const uint32_t bytes = nmt * 16384u + ((extra || !kDecode) ? kBBytes : 0u);
                     mbar_arrive_expect_tx(full_a(s), bytes);
                     const CUtensorMap* ma = extra ? &tmA2 : &tmA;
                     const CUtensorMap* mb = extra ? &tmB2 : &tmB;
                     const int r0 = (extra ? (it - nkb) : it) * kBK;
 #pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) tma_load_2d(sA + mt * 16384u, ma, full_a(s), r0, m0 + mt * 128);
+                    for (int mt = 0; mt < MT; ++mt)
+                        if (mt < nmt) tma_load_2d(sA + mt * 16384u, ma, full_a(s), r0, m0 + mt * 128);
                     if (extra || !kDecode) {
                         if (kBMn) {
 #pragma unroll
@@ -184,6 +197,8 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const long long t_begin = p.prof ? clock64() : 0;
             int git = 0, lt = 0;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+                int m0, j0, nmt;
+                tile_origin(t, m0, j0, nmt);
                 if (lt > 0) {
                     // the epilogue warps must have read the previous tile out of TMEM
                     const long long c0 = p.prof ? clock64() : 0;
@@ -212,6 +227,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                                     : make_sdesc(sB + ks * 32u, 16u, 1024u);
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt) {
+                            if (mt >= nmt) break;
                             const uint64_t adesc = make_sdesc(sA + mt * 16384u + ks * 32u, 16u, 1024u);
                             umma_bf16(tmem_base + mt * 256u, adesc, bdesc, idesc_main, (it > 0 || ks > 0) ? 1u : 0u);
                         }
@@ -240,8 +256,8 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             bool ok = true;
             int git = 0;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                int m0, j0;
-                tile_origin(tile, m0, j0);
+                int m0, j0, nmt;
+                tile_origin(tile, m0, j0, nmt);
                 const int k_fixed = j0 + a * 64 + h * 32;  // backward only
                 auto src_n = [&](int it) { return (BMODE == B_DECODE_K) ? (j0 + rr) : (it * kBK + rr); };
                 auto src_k = [&](int it) { return (BMODE == B_DECODE_K) ? (it * kBK + h * 32) : k_fixed; };
@@ -320,13 +336,13 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         bool ok = true;
         int lt = 0;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
-            int m0, j0;
-            tile_origin(t, m0, j0);
+            int m0, j0, nmt;
+            tile_origin(t, m0, j0, nmt);
             ok = mbar_wait(accum_full, lt & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 4);
             if (!ok) break;
             tc_fence_after_sync();
 #pragma unroll 1
-            for (int mt = 0; mt < MT; ++mt) {
+            for (int mt = 0; mt < nmt; ++mt) {
 #pragma unroll 1
                 for (int b = 0; b < 2; ++b) {
                     const int col = col_half * 128 + b * 64;
@@ -337,7 +353,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int c = 0; c < 2; ++c) {
                         uint32_t v[32];
                         tmem_ld_32x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + mt * 256u + col + c * 32, v);
-                        if (mt == MT - 1 && b == 1 && c == 1) {
+                        if (mt == nmt - 1 && b == 1 && c == 1) {
                             // last read of this tile's accumulators: hand TMEM back to the MMA warp
                             tc_fence_before_sync();
                             __syncwarp();
@@ -421,8 +437,15 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
         attr_set[dev & 63] = true;
     }
     PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (a.sm_limit > 0 && a.sm_limit < sms) sms = a.sm_limit;
+    if (g_debug_sm_limit > 0 && g_debug_sm_limit < sms) sms = g_debug_sm_limit;
     const int tiles = p.tiles_m * p.tiles_j;
     const int grid = tiles < sms ? tiles : sms;
+    p.n_whole = tiles; p.n_items = tiles;
+    if (MT == 2) {
+        const int rem = tiles % grid;
+        if (tiles > grid && rem > 0 && 2 * rem <= grid) { p.n_whole = tiles - rem; p.n_items = p.n_whole + 2 * rem; }
+    }
     kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, tmD, p);
     PLZ_CUDA_CHECK(cudaGetLastError());
     return PLZ_OK;

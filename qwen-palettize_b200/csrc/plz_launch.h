@@ -18,9 +18,11 @@ struct LutGemmArgs {
     // optional extra block: A2 [M, r2] (pitch lda2); B2: K-major modes [J, r2], MN-major modes [r2, J]
     int r2; const void* A2; long long lda2; const void* B2; long long ldb2;
     void* out; long long ld_out; float alpha;
+    int sm_limit;  // > 0: use at most this many CTAs (tests of the multi-tile schedule)
     void* prof;  // optional device buffer of cycle counters, 8 x uint64 per CTA (diagnostics)
 };
 int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream);
+extern int g_debug_sm_limit;
 
 // ---- tn_gemm.cu -------------------------------------------------------------------------------
 enum Epi { EPI_STORE = 0, EPI_SOFT = 1, EPI_HARD = 2 };

@@ -556,6 +556,7 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
     p.status = device_status_ptr();
     const int tiles = ((a.I + 127) / 128) * ((a.J + 255) / 256) * p.splits;
     int sms = a.sm_count > 0 ? a.sm_count : 148;
+    if (g_debug_sm_limit > 0 && g_debug_sm_limit < sms) sms = g_debug_sm_limit;
     const int grid = tiles < sms ? tiles : sms;
     switch (a.epi) {
         case EPI_STORE: return launch_tn_t<EPI_STORE, float, false>(a, p, tmP, tmQ, grid, stream);

@@ -108,3 +108,31 @@ def test_empty_batch_is_a_no_op():
     w = _weight(idx, pal, 256, 64, 1, 64)
     y, _ = ops.hard_forward(w, torch.empty(0, 64, dtype=torch.bfloat16, device="cuda"))
     assert y.shape == (0, 256)
+
+
+@pytest.mark.parametrize("limit", [1, 3, 5])
+def test_persistent_schedule_with_few_ctas(limit):
+    """Restrict the persistent kernels to a few CTAs so that every CTA walks several tiles (and the last,
+    partially filled round is cut into half tiles): results must not change."""
+    import plz_native as P
+    import plz_ops as ops
+    M, N, K = 1100, 1024, 512
+    x, dy, idx, pal = _make(M, N, K, 1, 256, seed=9)
+    g = torch.Generator().manual_seed(10)
+    a = (torch.randn(16, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+    b = (torch.randn(N, 16, generator=g) * 0.05).to(torch.bfloat16)
+    w = _weight(idx, pal, N, K, 1, 256)
+    lora = (a.cuda(), b.cuda(), 1.0)
+    P.lib().plz_debug_set_sm_limit(limit)
+    try:
+        y, t = ops.hard_forward(w, x.cuda(), lora)
+        dx, dt = ops.backward_dx(w, dy.cuda(), lora)
+        dpal = ops.backward_dw_hard(w, x.cuda(), dy.cuda())
+        check_status()
+    finally:
+        P.lib().plz_debug_set_sm_limit(0)
+    wd = O.dequantize(idx.long(), pal, 1, 256)
+    dxl, _, _ = O.lora_backward(x, dy, a, b, 1.0)
+    assert_close(y, (x.float() @ wd.float().t() + O.lora_forward(x, a, b, 1.0)), "y")
+    assert_close(dx, (dy.float() @ wd.float() + dxl), "dX")
+    assert_close(dpal, O.hard_backward(x, dy, idx.long(), pal, 1, 256)[1], "dPalette")
