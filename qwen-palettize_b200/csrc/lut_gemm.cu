@@ -35,6 +35,7 @@ struct LutGemmParams {
     int tiles_m, tiles_j;
     int n_whole;         // tiles [0, n_whole) are whole (MT row blocks); the rest of the list are single 128-row blocks
     int n_items;         // length of the tile list
+    int mma_n;           // MMA N extent: 256, or the output width rounded up to 16 when it is narrower
     const uint8_t* packed;  // W indices, [Wn, packed_pitch] bytes, 4 per byte along K, LSB first
     long long packed_pitch;
     const __nv_bfloat16* palette;  // [(n / gs_n) * n_kgroups + k / gs_k][4]
@@ -191,7 +192,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_main = make_idesc(128, kBN, 0, kBMn ? 1 : 0);
+            const uint32_t idesc_main = make_idesc(128, p.mma_n, 0, kBMn ? 1 : 0);
             bool ok = true;
             long long wait_a = 0, wait_b = 0, wait_t = 0;
             const long long t_begin = p.prof ? clock64() : 0;
@@ -442,6 +443,7 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
     const int tiles = p.tiles_m * p.tiles_j;
     const int grid = tiles < sms ? tiles : sms;
     p.n_whole = tiles; p.n_items = tiles;
+    p.mma_n = (a.J >= kBN) ? kBN : ((a.J + 15) / 16) * 16;
     if (MT == 2) {
         const int rem = tiles % grid;
         if (tiles > grid && rem > 0 && 2 * rem <= grid) { p.n_whole = tiles - rem; p.n_items = p.n_whole + 2 * rem; }

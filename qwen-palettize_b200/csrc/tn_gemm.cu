@@ -28,6 +28,7 @@ namespace plz {
 
 struct TnParams {
     int M, I, J;       // P is [M, I], Q is [M, J], D is [I, J]
+    int n_whole, n_items;  // items [0, n_whole) are whole 128 x 256 tiles, the rest 128 x 128 halves (last round)
     int splits;        // EPI_STORE only: the m range is cut into `splits` chunks, results atomically added
     int m_chunk;       // rows of m per split (multiple of 64)
     // EPI_STORE
@@ -81,7 +82,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     const int lane = threadIdx.x & 31;
     const int tiles_i = (p.I + 127) / 128;
     const int tiles_j = (p.J + 255) / 256;
-    const int n_tiles = tiles_i * tiles_j * p.splits;
+    const int n_tiles = p.n_items;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTnStages; ++s) {
@@ -107,7 +108,16 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     const uint32_t tmem_base = *tmem_slot;
 
     // tile -> (split, i tile, j tile); i fastest so that one wave of CTAs covers every i tile
-    auto tile_coords = [&](int t, int& sp, int& ti, int& tj) {
+    // item -> (split, i tile, j tile, first column inside the tile, columns); i fastest so that one wave of CTAs
+    // covers every i tile. Items past n_whole are the two 128-column halves of a tile.
+    auto tile_coords = [&](int item, int& sp, int& ti, int& tj, int& c_off, int& c_num) {
+        int t = item;
+        c_off = 0; c_num = 256;
+        if (item >= p.n_whole) {
+            t = p.n_whole + ((item - p.n_whole) >> 1);
+            c_off = ((item - p.n_whole) & 1) * 128;
+            c_num = 128;
+        }
         ti = t % tiles_i;
         const int r = t / tiles_i;
         tj = r % tiles_j;
@@ -128,8 +138,8 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             bool ok = true;
             int git = 0;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                int sp, ti, tj, m_begin, nkb;
-                tile_coords(t, sp, ti, tj);
+                int sp, ti, tj, c_off, c_num, m_begin, nkb;
+                tile_coords(t, sp, ti, tj, c_off, c_num);
                 m_range(sp, m_begin, nkb);
                 for (int it = 0; it < nkb; ++it, ++git) {
                     const int s = git % kTnStages;
@@ -138,12 +148,13 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                     if (!ok) break;
                     const uint32_t sA = base + s * kTnStageBytes;
                     const uint32_t sB = sA + kTnABytes;
-                    mbar_arrive_expect_tx(full(s), kTnStageBytes);
+                    mbar_arrive_expect_tx(full(s), kTnABytes + (uint32_t)c_num * 128u);
                     const int m = m_begin + it * 64;
 #pragma unroll
                     for (int q = 0; q < 2; ++q) tma_load_2d(sA + q * 8192u, &tmP, full(s), ti * 128 + q * 64, m);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) tma_load_2d(sB + q * 8192u, &tmQ, full(s), tj * 256 + q * 64, m);
+                    for (int q = 0; q < 4; ++q)
+                        if (q * 64 < c_num) tma_load_2d(sB + q * 8192u, &tmQ, full(s), tj * 256 + c_off + q * 64, m);
                     last_fill[s] = git;
                 }
             }
@@ -163,14 +174,14 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(128, 256, 1, 1);
             bool ok = true;
             int git = 0, lt = 0;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
-                int sp, ti, tj, m_begin, nkb;
-                tile_coords(t, sp, ti, tj);
+                int sp, ti, tj, c_off, c_num, m_begin, nkb;
+                tile_coords(t, sp, ti, tj, c_off, c_num);
                 m_range(sp, m_begin, nkb);
                 const int buf = lt & 1;
+                const uint32_t idesc = make_idesc(128, c_num, 1, 1);
                 ok = mbar_wait(acc_empty(buf), ((lt >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_ACCUM, 1);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -204,21 +215,22 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         bool ok = true;
         int lt = 0;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
-            int sp, ti, tj, m_begin, nkb;
-            tile_coords(t, sp, ti, tj);
+            int sp, ti, tj, c_off, c_num, m_begin, nkb;
+            tile_coords(t, sp, ti, tj, c_off, c_num);
             m_range(sp, m_begin, nkb);
             const int buf = lt & 1;
             ok = mbar_wait(acc_full(buf), (lt >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 2);
             if (!ok) break;
             tc_fence_after_sync();
             const int row = ti * 128 + lane_group * 32 + lane;  // D row of this thread
-            const uint32_t trow = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * 256u + col_half * 128u;
+            const int wcols = c_num >> 1;  // columns per epilogue warp: 128, or 64 in a half tile
+            const uint32_t trow = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * 256u + col_half * wcols;
             const bool row_ok = row < p.I;
-            const int colbase = tj * 256 + col_half * 128;
+            const int colbase = tj * 256 + c_off + col_half * wcols;
 
             if (EPI == EPI_STORE) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 16) {
+                for (int c0 = 0; c0 < wcols; c0 += 16) {
                     uint32_t v[16];
                     tmem_ld_32x16(trow + c0, v);
                     if (nkb > 0 && row < p.out_I) {
@@ -242,7 +254,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                 float* dbase = p.dlogits ? reinterpret_cast<float*>(p.dlogits) + (long long)k * p.ls_row : nullptr;
                 const float* nbase = p.noise ? p.noise + (long long)k * p.ns_row : nullptr;
 #pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 8) {
+                for (int c0 = 0; c0 < wcols; c0 += 8) {
                     uint32_t v[8];
                     tmem_ld_32x8(trow + c0, v);
                     const int nb = colbase + c0;  // first n of the batch
@@ -316,16 +328,16 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                                 part[j] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, s);
                             }
                         }
-                        red[(lane_group * 256 + col_half * 128 + c0) * 4 + lane] = part[0];
+                        red[(lane_group * 256 + col_half * wcols + c0) * 4 + lane] = part[0];
                     }
                 }
                 if (p.dpalette != nullptr) {
                     epi_bar_sync();
                     // one thread per column: add the four lane groups' partials in a fixed order
                     const int et = threadIdx.x - 64;  // 0..255
-                    const int n = tj * 256 + et;
+                    const int n = tj * 256 + c_off + et;
                     const int k0 = ti * 128;
-                    if (n < p.J && k0 < p.I) {
+                    if (et < c_num && n < p.J && k0 < p.I) {
                         const long long pg = ((long long)n * p.n_kgroups + k0 / p.gs_k) * 4;
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
@@ -344,7 +356,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                 const bool vec_l = kVec && p.ls_p == 1;
                 const bool vec_n = p.ns_p == 1;
                 const int n = row;
-                const int k_tile0 = tj * 256;
+                const int k_tile0 = tj * 256 + c_off;
                 const long long pg = ((long long)((row_ok ? n : 0) / p.gs_n) * p.n_kgroups + k_tile0 / p.gs_k) * 4;
                 float cpal[4] = {0.f, 0.f, 0.f, 0.f};
                 if (EPI == EPI_SOFT) {
@@ -360,7 +372,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                 const uint8_t* prow = p.packed ? p.packed + (long long)n * p.packed_pitch : nullptr;
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 8) {
+                for (int c0 = 0; c0 < wcols; c0 += 8) {
                     uint32_t v[8];
                     tmem_ld_32x8(trow + c0, v);
                     const int kb = colbase + c0;  // first k of the batch
@@ -558,6 +570,12 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
     int sms = a.sm_count > 0 ? a.sm_count : 148;
     if (g_debug_sm_limit > 0 && g_debug_sm_limit < sms) sms = g_debug_sm_limit;
     const int grid = tiles < sms ? tiles : sms;
+    p.n_whole = tiles; p.n_items = tiles;
+    if (a.epi != EPI_STORE) {
+        // the last, partially filled round of the persistent schedule is cut into half tiles
+        const int rem = tiles % grid;
+        if (tiles > grid && rem > 0 && 2 * rem <= grid) { p.n_whole = tiles - rem; p.n_items = p.n_whole + 2 * rem; }
+    }
     switch (a.epi) {
         case EPI_STORE: return launch_tn_t<EPI_STORE, float, false>(a, p, tmP, tmQ, grid, stream);
         case EPI_HARD:

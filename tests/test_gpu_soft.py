@@ -92,3 +92,20 @@ def test_module_autograd_matches_functional():
     m.eval(); m.extract_hard_indices()
     ye = m(d["x"].cuda())
     assert_close(ye, want["y"], "eval y")
+
+
+@pytest.mark.parametrize("limit", [3, 7])
+def test_persistent_schedule_with_few_ctas(limit):
+    """Few CTAs: every CTA walks several tiles of the weight-gradient kernel and the last round is cut into
+    half tiles; all outputs must still match the oracle."""
+    import plz_native as P
+    d = _inputs(300, 1024, 768, seed=11)
+    P.lib().plz_debug_set_sm_limit(limit)
+    try:
+        got = _run(d, 1.0, True)
+        check_status()
+    finally:
+        P.lib().plz_debug_set_sm_limit(0)
+    want = _oracle(d, 1.0, True, noise=d["noise"])
+    for k in ("y", "dx", "dlogits", "dpalette", "da", "db"):
+        assert_close(got[k], want[k], k)
