@@ -263,7 +263,7 @@ int32_t plz_hard_fwd_smallm(const plz_weight_t* w, const void* x, int64_t ldx, i
     int dev = 0, sms = 0;
     PLZ_CUDA_CHECK(cudaGetDevice(&dev));
     PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    g.sm_count = sms;
+    g.sm_count = sms; g.prof = g_prof_buffer;
     return launch_lut_gemv(g, (cudaStream_t)stream);
 }
 

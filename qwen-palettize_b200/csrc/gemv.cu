@@ -25,13 +25,14 @@ struct GemvParams {
     uint32_t idx_bytes;  // shared-memory bytes reserved for the packed block (rows_max * K/4, 16-aligned)
     uint32_t pal_bytes;  // shared-memory bytes reserved for palettes (rows_max * n_kgroups_per_row * 8)
     StatusWord* status;
+    unsigned long long* prof;  // optional [gridDim][8] cycle counters of the MMA thread (diagnostics)
 };
 
 constexpr int kGvThreads = 320;
-constexpr int kGvStages = 4;
+constexpr int kGvStages = 8;                     // decoded-weight ring: one stage per decode warp
+constexpr uint32_t kGvXRingBytes = 32 * 1024;   // activation ring (2..8 KB per stage)
 constexpr uint32_t kGvABytes = 128 * 64 * 2;
-constexpr uint32_t kGvBBytes = 64 * 64 * 2;
-constexpr uint32_t kGvStageBytes = kGvABytes + kGvBBytes;
+constexpr uint32_t kGvStageBytes = kGvABytes;
 constexpr int kGvMaxGroups = 64;  // commit groups (256 input columns each): K <= 16384
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -64,19 +65,24 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (base - raw);
-    // layout: [stages][A | B] | packed block | palettes | barriers
-    const uint32_t idx_off = kGvStages * kGvStageBytes;
+    // layout: decoded-weight ring | activation ring | packed block | palettes | barriers
+    const uint32_t x_off = kGvStages * kGvStageBytes;
+    const uint32_t idx_off = x_off + kGvXRingBytes;
     const uint32_t pal_off = idx_off + p.idx_bytes;
     const uint32_t bar_off = pal_off + p.pal_bytes;
     const uint32_t bar_base = base + bar_off;
-    auto full_a = [&](int s) { return bar_base + 8u * s; };
-    auto full_b = [&](int s) { return bar_base + 8u * (kGvStages + s); };
-    auto empty = [&](int s) { return bar_base + 8u * (2 * kGvStages + s); };
-    const uint32_t accum_full = bar_base + 8u * (3 * kGvStages);
-    const uint32_t grp_ready = bar_base + 8u * (3 * kGvStages + 1);  // all decode threads' copies of a group landed
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + bar_off + 8 * (3 * kGvStages + 2));
+    const uint32_t x_stage_bytes = (uint32_t)p.mpad * 128u;
+    const int x_stages = (int)(kGvXRingBytes / x_stage_bytes);  // 16, 8 or 4
+    auto full_w = [&](int s) { return bar_base + 8u * s; };                       // weights of stage s decoded
+    auto empty_w = [&](int s) { return bar_base + 8u * (kGvStages + s); };        // MMAs reading stage s retired
+    auto full_x = [&](int s) { return bar_base + 8u * (2 * kGvStages + s); };     // activation tile landed
+    auto empty_x = [&](int s) { return bar_base + 8u * (2 * kGvStages + 16 + s); };
+    const uint32_t accum_full = bar_base + 8u * (2 * kGvStages + 32);
+    const uint32_t grp_ready = bar_base + 8u * (2 * kGvStages + 33);  // all decode threads' copies of a group landed
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + bar_off + 8 * (2 * kGvStages + 34));
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
+    const long long t_entry = p.prof ? clock64() : 0;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int n_begin = (int)(((long long)blockIdx.x * p.N) / gridDim.x);
@@ -88,18 +94,21 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGvStages; ++s) {
-            mbar_init(full_a(s), 1);
-            mbar_init(full_b(s), 8);
-            mbar_init(empty(s), 1);
+            mbar_init(full_w(s), 1);
+            mbar_init(empty_w(s), 1);
+        }
+        for (int s = 0; s < 16; ++s) {
+            mbar_init(full_x(s), 1);
+            mbar_init(empty_x(s), 1);
         }
         mbar_init(accum_full, 1);
-        mbar_init(grp_ready, 256);
+        mbar_init(grp_ready, 8);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmX);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32((const void*)tmem_slot), 64);
+        tmem_alloc(smem_u32((const void*)tmem_slot), 8u * p.mpad);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -111,25 +120,22 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
         if (warp == 0) {
             // ---------------------------------------------------------- TMA producer: activation tiles
             if (lane == 0) {
-                int last_fill[kGvStages];
-                for (int s = 0; s < kGvStages; ++s) last_fill[s] = -1;
                 bool ok = true;
-                const uint32_t bytes = (uint32_t)p.mpad * 128u;
+                int issued = 0;
                 for (int it = 0; it < nkb && ok; ++it) {
-                    const int s = it % kGvStages;
-                    const uint32_t ph = (it / kGvStages) & 1;
-                    ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 0);
+                    const int s = it % x_stages;
+                    const uint32_t ph = (it / x_stages) & 1;
+                    ok = mbar_wait(empty_x(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 0);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(full_a(s), bytes);
-                    tma_load_2d(base + s * kGvStageBytes + kGvABytes, &tmX, full_a(s), it * 64, 0);
-                    last_fill[s] = it;
+                    mbar_arrive_expect_tx(full_x(s), x_stage_bytes);
+                    tma_load_2d(base + x_off + s * x_stage_bytes, &tmX, full_x(s), it * 64, 0);
+                    issued = it + 1;
                 }
                 if (!ok) {
-                    for (int s = 0; s < kGvStages; ++s) {
-                        if (last_fill[s] < 0) continue;
-                        const uint32_t ph = (last_fill[s] / kGvStages) & 1;
+                    // give copies already in flight a bounded chance to land before the CTA exits
+                    for (int it = (issued > x_stages ? issued - x_stages : 0); it < issued; ++it) {
                         const uint64_t t0 = globaltimer_ns();
-                        while (!mbar_try_wait(full_a(s), ph)) {
+                        while (!mbar_try_wait(full_x(it % x_stages), (it / x_stages) & 1)) {
                             if (globaltimer_ns() - t0 > 100000000ull) {
                                 report(p.status, ST_TIMEOUT_DRAIN, 0);
                                 break;
@@ -143,27 +149,41 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
             if (lane == 0) {
                 const uint32_t idesc = make_idesc(128, p.mpad, 0, 0);
                 bool ok = true;
+                long long wait_x = 0, wait_w = 0;
+                const long long t_begin = p.prof ? clock64() : 0;
                 for (int it = 0; it < nkb && ok; ++it) {
-                    const int s = it % kGvStages;
-                    const uint32_t ph = (it / kGvStages) & 1;
-                    ok = mbar_wait(full_a(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
-                    if (ok) ok = mbar_wait(full_b(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 2);
+                    const int s = it % kGvStages, xs = it % x_stages;
+                    const long long c0 = p.prof ? clock64() : 0;
+                    ok = mbar_wait(full_x(xs), (it / x_stages) & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
+                    const long long c1 = p.prof ? clock64() : 0;
+                    if (ok) ok = mbar_wait(full_w(s), (it / kGvStages) & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 2);
+                    if (p.prof) { wait_x += c1 - c0; wait_w += clock64() - c1; }
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t sW = base + s * kGvStageBytes;  // decoded weights: MMA operand A
-                    const uint32_t sX = sW + kGvABytes;            // activations: MMA operand B
+                    const uint32_t sW = base + s * kGvStageBytes;         // decoded weights: MMA operand A
+                    const uint32_t sX = base + x_off + xs * x_stage_bytes;  // activations: MMA operand B
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        umma_bf16(tmem_base, make_sdesc(sW + ks * 32u, 16u, 1024u), make_sdesc(sX + ks * 32u, 16u, 1024u),
-                                  idesc, (it > 0 || ks > 0) ? 1u : 0u);
+                        // A narrow MMA (N = 16..64) retires in a few cycles, but accumulating into the tile the previous
+                        // MMA is still writing costs the full TMEM round trip. Eight independent accumulators (four per
+                        // block, alternating with the block parity) keep eight chains in flight; the epilogue adds them.
+                        const uint32_t acc = (uint32_t)(((it & 1) * 4 + ks) * p.mpad);
+                        umma_bf16(tmem_base + acc, make_sdesc(sW + ks * 32u, 16u, 1024u), make_sdesc(sX + ks * 32u, 16u, 1024u),
+                                  idesc, (it > 1) ? 1u : 0u);
                     }
-                    umma_commit(empty(s));
+                    umma_commit(empty_w(s));
+                    umma_commit(empty_x(xs));
                 }
                 if (ok) umma_commit(accum_full);
+                if (p.prof) {
+                    unsigned long long* q = p.prof + 8ull * blockIdx.x;
+                    q[0] = wait_x; q[1] = wait_w; q[2] = clock64() - t_begin; q[3] = t_begin - t_entry;
+                }
             }
         } else {
             // ---------------------------------------------------------- decode warps
             const int t = threadIdx.x - 64;
+            const int dw = warp - 2;                // 0..7
             const uint32_t s_idx = base + idx_off;  // [kb][row][16 bytes]
             const uint32_t s_pal = base + pal_off;  // [kgroup][row][8 bytes]
             const int kg_per_row = (p.K + p.gs_k - 1) / p.gs_k;
@@ -183,24 +203,28 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
                 }
                 cp_async_commit();
             }
-            // 2) decode group by group
+            // 2) warp w decodes the 64-column blocks w, w + 8, ... into ring stage w, so eight blocks are in work at once
             bool ok = true;
             const int units = rows * 4;  // (row, 16-column word) per 64-column block
-            for (int it = 0; it < nkb && ok; ++it) {
-                if (it % kb_per_grp == 0) {
-                    const int grp = it / kb_per_grp;
-                    cp_async_wait_pending(n_grp - 1 - grp);
-                    mbar_arrive(grp_ready);  // once all 256 have arrived, every thread's copies are visible
-                    ok = mbar_wait(grp_ready, grp & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 5);
-                    if (!ok) break;
+            int grp_done = -1;           // commit groups known to have landed
+            for (int it = dw; it < nkb && ok; it += kGvStages) {
+                const int grp = it / kb_per_grp;
+                while (grp_done < grp && ok) {
+                    // all eight decode warps pass here for every group, in order
+                    ++grp_done;
+                    cp_async_wait_pending(n_grp - 1 - grp_done);
+                    __syncwarp();  // every lane's copies of the group have landed: one arrival per warp
+                    if (lane == 0) mbar_arrive(grp_ready);
+                    ok = mbar_wait(grp_ready, grp_done & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 5);
                 }
-                const int s = it % kGvStages;
+                if (!ok) break;
+                const int s = dw;
                 const uint32_t ph = (it / kGvStages) & 1;
-                ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 3);
+                ok = mbar_wait(empty_w(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 3);
                 if (!ok) break;
                 uint8_t* sW = smem + s * kGvStageBytes;
                 const int kg = (it * 64) / p.gs_k;
-                for (int u = t; u < units; u += 256) {
+                for (int u = lane; u < units; u += 32) {
                     const int r = u >> 2, w = u & 3;
                     const uint32_t word = *reinterpret_cast<const uint32_t*>(smem + idx_off + (uint32_t)(it * rows + r) * 16u + w * 4u);
                     const uint2 praw = *reinterpret_cast<const uint2*>(smem + pal_off + (uint32_t)(kg * rows + r) * 8u);
@@ -213,7 +237,15 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(full_b(s));
+                if (lane == 0) mbar_arrive(full_w(s));
+            }
+            // groups this warp did not need still have to be passed so that the other warps' barrier completes
+            while (grp_done < n_grp - 1 && ok) {
+                ++grp_done;
+                cp_async_wait_pending(n_grp - 1 - grp_done);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(grp_ready);
+                ok = mbar_wait(grp_ready, grp_done & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 5);
             }
             if (!ok) cp_async_wait_pending(0);
             // 3) epilogue: warps 2..5 cover the 128 TMEM lanes (weight rows); columns are tokens
@@ -223,14 +255,22 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
                     tc_fence_after_sync();
                     const int lane_group = warp & 3;
                     const int r = lane_group * 32 + lane;
+                    const int n_acc = nkb > 1 ? 8 : 4;  // accumulators that have been written
                     for (int c0 = 0; c0 < p.mpad; c0 += 16) {
-                        uint32_t v[16];
-                        tmem_ld_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + c0, v);
+                        float sum[16];
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) sum[c] = 0.f;
+                        for (int a = 0; a < n_acc; ++a) {
+                            uint32_t v[16];
+                            tmem_ld_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + a * p.mpad + c0, v);
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) sum[c] += __uint_as_float(v[c]);
+                        }
                         if (r < rows) {
 #pragma unroll
                             for (int c = 0; c < 16; ++c) {
                                 const int m = c0 + c;
-                                if (m < p.M) p.out[(long long)m * p.ld_out + n_begin + r] = __float2bfloat16_rn(__uint_as_float(v[c]));
+                                if (m < p.M) p.out[(long long)m * p.ld_out + n_begin + r] = __float2bfloat16_rn(sum[c]);
                             }
                         }
                     }
@@ -242,8 +282,9 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
     __syncthreads();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 64);
+        tmem_dealloc(tmem_base, 8u * p.mpad);
     }
+    if (p.prof && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 4] = clock64() - t_entry;
 }
 
 int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream) {
@@ -256,7 +297,7 @@ int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream) {
     // grid: one CTA per SM unless a CTA's packed block would not fit in shared memory or exceed 128 rows
     const int row_bytes = a.K / 4;
     const int kg_per_row = (a.K + a.gs_k - 1) / a.gs_k;
-    const uint32_t budget = 100 * 1024;
+    const uint32_t budget = 227 * 1024 - (kGvStages * kGvStageBytes + kGvXRingBytes + 1024 + 768 + 64);
     int max_rows = (int)(budget / (uint32_t)(row_bytes + kg_per_row * 8));
     if (max_rows > 128) max_rows = 128;
     if (max_rows < 1) { set_last_error("small-M forward: K=%d too large for shared memory", a.K); return PLZ_ERR_TOO_LARGE; }
@@ -273,7 +314,8 @@ int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream) {
     p.idx_bytes = (uint32_t)(rows_max * row_bytes + 15) & ~15u;
     p.pal_bytes = (uint32_t)(rows_max * kg_per_row * 8 + 15) & ~15u;
     p.status = device_status_ptr();
-    const uint32_t smem = kGvStages * kGvStageBytes + p.idx_bytes + p.pal_bytes + 256 + 1024;
+    p.prof = (unsigned long long*)a.prof;
+    const uint32_t smem = kGvStages * kGvStageBytes + kGvXRingBytes + p.idx_bytes + p.pal_bytes + 768 + 1024;
     static int attr_smem[64] = {};
     int dev = 0;
     PLZ_CUDA_CHECK(cudaGetDevice(&dev));

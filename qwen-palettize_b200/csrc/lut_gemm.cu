@@ -466,7 +466,8 @@ int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream) {
         if ((uintptr_t)a.palette & 7) { set_last_error("lut_gemm: palette must be 8-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
         if (a.gs_k % 64 || a.Wk % a.gs_k || a.Wk % 64) { set_last_error("lut_gemm: K group size %d must be a multiple of 64 dividing K=%d", a.gs_k, a.Wk); return PLZ_ERR_BAD_SHAPE; }
     }
-    const bool big = a.M > 128;
+    // narrow outputs (the rank-16/32 LoRA products) are bound by streaming A: 128-row tiles give twice the CTAs
+    const bool big = a.M > 128 && a.J > 64;
     switch (a.bmode) {
         case B_DECODE_K: return big ? launch_t<2, B_DECODE_K>(a, stream) : launch_t<1, B_DECODE_K>(a, stream);
         case B_DECODE_MN: return big ? launch_t<2, B_DECODE_MN>(a, stream) : launch_t<1, B_DECODE_MN>(a, stream);

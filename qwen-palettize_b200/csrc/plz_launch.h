@@ -53,6 +53,7 @@ struct GemvArgs {
     int gs_n, gs_k;
     void* out; long long ld_out;
     int sm_count;
+    void* prof;  // optional device buffer of cycle counters (diagnostics)
 };
 int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream);
 
