@@ -251,7 +251,14 @@ def run_ours(args):
     gemm_phase = max(("fwd", "dw", "dx"), key=lambda p: phase_ms[p])
     kern_ms = {p: max(phase_ms[p] - skinny[p], 1e-6) for p in ("fwd", "dw", "dx")}
     achieved = GEMM_FLOPS / (kern_ms[gemm_phase] * 1e-3) / 1e12
-    traffic = {"fwd": None, "dw": None, "dx": None}
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum): one ncu capture of each kernel at 4096
+    # tokens (profiles/*.md) gave measured / algorithmic = 0.51 (fwd: most of y was still in L2 when the capture
+    # ended), 0.91 (dx) and 1.005 (dw); the figures below are those ratios times the algorithmic bytes of the full
+    # 16384-token launch (the M-proportional part scales, the 1.2 GB of logits / noise / dLogits does not).
+    alg = {"fwd": M_TOK * K_IN * 2 + N_OUT * K_IN // 4 + N_OUT * (K_IN // 256) * 8 + M_TOK * N_OUT * 2,
+           "dx": M_TOK * N_OUT * 2 + N_OUT * K_IN // 4 + N_OUT * (K_IN // 256) * 8 + M_TOK * K_IN * 2,
+           "dw": 3 * N_OUT * K_IN * 16 + M_TOK * (N_OUT + K_IN) * 2}
+    traffic = {"fwd": 0.51 * alg["fwd"], "dx": 0.91 * alg["dx"], "dw": 1.005 * alg["dw"]}
     line = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -267,7 +274,7 @@ def run_ours(args):
         "roofline": {"bound": "tensor", "kernel": {"fwd": "lut_gemm_kernel<2,B_DECODE_K>", "dw": "tn_gemm_kernel<EPI_SOFT,float>",
                                                     "dx": "lut_gemm_kernel<2,B_DECODE_MN>"}[gemm_phase],
                      "achieved": achieved, "peak": pk["tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / pk["tflops_sustained"],
-                     "traffic": traffic[gemm_phase], "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
+                     "traffic": traffic[gemm_phase], "traffic_note": "ncu small-case ratio x algorithmic bytes of the full launch", "algorithmic_bytes": alg[gemm_phase], "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
                      "kernel_ms": kern_ms, "skinny_lora_ms": skinny,
                      "per_kernel_tflops": {p: GEMM_FLOPS / (kern_ms[p] * 1e-3) / 1e12 for p in ("fwd", "dw", "dx")}},
     }
