@@ -28,7 +28,10 @@ struct GemvParams {
     unsigned long long* prof;  // optional [gridDim][8] cycle counters of the MMA thread (diagnostics)
 };
 
-constexpr int kGvThreads = 320;
+constexpr int kGvMmaWarps = 4;   // MMA issuers: k-blocks round-robin, two accumulators each
+constexpr int kGvDecodeWarps = 16;  // two per ring stage
+constexpr int kGvFirstExtraMma = 2 + kGvDecodeWarps;
+constexpr int kGvThreads = (2 + kGvDecodeWarps + kGvMmaWarps - 1) * 32;  // warp 0 TMA, warp 1 MMA, 16 decode warps, 3 more MMA issuers
 constexpr int kGvStages = 8;                     // decoded-weight ring: one stage per decode warp
 constexpr uint32_t kGvXRingBytes = 32 * 1024;   // activation ring (2..8 KB per stage)
 constexpr uint32_t kGvABytes = 128 * 64 * 2;
@@ -94,15 +97,15 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGvStages; ++s) {
-            mbar_init(full_w(s), 1);
+            mbar_init(full_w(s), kGvDecodeWarps / kGvStages);
             mbar_init(empty_w(s), 1);
         }
         for (int s = 0; s < 16; ++s) {
             mbar_init(full_x(s), 1);
             mbar_init(empty_x(s), 1);
         }
-        mbar_init(accum_full, 1);
-        mbar_init(grp_ready, 8);
+        mbar_init(accum_full, kGvMmaWarps);
+        mbar_init(grp_ready, kGvDecodeWarps);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmX);
@@ -144,14 +147,18 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
                     }
                 }
             }
-        } else if (warp == 1) {
-            // ---------------------------------------------------------- MMA issuer
+        } else if (warp == 1 || warp >= kGvFirstExtraMma) {
+            // ---------------------------------------------------------- MMA issuers
+            // A tcgen05.mma this narrow occupies the tensor pipe for a few tens of cycles but costs its issuing thread
+            // far longer, so four warps issue in parallel: issuer q takes the k-blocks q, q + 4, ... and owns the
+            // accumulators 2q and 2q + 1 (alternating with the 64-column half of the block).
+            const int q = (warp == 1) ? 0 : (warp - kGvFirstExtraMma + 1);
             if (lane == 0) {
                 const uint32_t idesc = make_idesc(128, p.mpad, 0, 0);
                 bool ok = true;
                 long long wait_x = 0, wait_w = 0;
                 const long long t_begin = p.prof ? clock64() : 0;
-                for (int it = 0; it < nkb && ok; ++it) {
+                for (int it = q; it < nkb && ok; it += kGvMmaWarps) {
                     const int s = it % kGvStages, xs = it % x_stages;
                     const long long c0 = p.prof ? clock64() : 0;
                     ok = mbar_wait(full_x(xs), (it / x_stages) & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
@@ -167,15 +174,15 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
                         // A narrow MMA (N = 16..64) retires in a few cycles, but accumulating into the tile the previous
                         // MMA is still writing costs the full TMEM round trip. Eight independent accumulators (four per
                         // block, alternating with the block parity) keep eight chains in flight; the epilogue adds them.
-                        const uint32_t acc = (uint32_t)(((it & 1) * 4 + ks) * p.mpad);
+                        const uint32_t acc = (uint32_t)((q * 2 + (ks & 1)) * p.mpad);
                         umma_bf16(tmem_base + acc, make_sdesc(sW + ks * 32u, 16u, 1024u), make_sdesc(sX + ks * 32u, 16u, 1024u),
-                                  idesc, (it > 1) ? 1u : 0u);
+                                  idesc, (it >= kGvMmaWarps || ks > 1) ? 1u : 0u);
                     }
                     umma_commit(empty_w(s));
                     umma_commit(empty_x(xs));
                 }
                 if (ok) umma_commit(accum_full);
-                if (p.prof) {
+                if (p.prof && q == 0) {
                     unsigned long long* q = p.prof + 8ull * blockIdx.x;
                     q[0] = wait_x; q[1] = wait_w; q[2] = clock64() - t_begin; q[3] = t_begin - t_entry;
                 }
@@ -183,12 +190,13 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
         } else {
             // ---------------------------------------------------------- decode warps
             const int t = threadIdx.x - 64;
-            const int dw = warp - 2;                // 0..7
+            const int dw = (warp - 2) % kGvStages;  // ring stage of this warp
+            const int dh = (warp - 2) / kGvStages;  // which half of the stage's units
             const uint32_t s_idx = base + idx_off;  // [kb][row][16 bytes]
             const uint32_t s_pal = base + pal_off;  // [kgroup][row][8 bytes]
             const int kg_per_row = (p.K + p.gs_k - 1) / p.gs_k;
             // 1) put the whole packed block (and the palettes) in flight
-            for (int u = t; u < rows * kg_per_row; u += 256) {
+            for (int u = t; u < rows * kg_per_row; u += kGvDecodeWarps * 32) {
                 const int r = u % rows, kg = u / rows;
                 const long long g = (long long)((n_begin + r) / p.gs_n) * p.n_kgroups + kg;
                 cp_async8(s_pal + (uint32_t)(kg * rows + r) * 8u, p.palette + g * 4);
@@ -196,7 +204,7 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
             for (int grp = 0; grp < n_grp; ++grp) {
                 const int kb0 = grp * kb_per_grp;
                 const int nb = (nkb - kb0 < kb_per_grp) ? (nkb - kb0) : kb_per_grp;
-                for (int u = t; u < rows * nb; u += 256) {
+                for (int u = t; u < rows * nb; u += kGvDecodeWarps * 32) {
                     const int r = u / nb, j = u % nb;  // consecutive threads: consecutive 16 bytes of one row
                     cp_async16(s_idx + (uint32_t)((kb0 + j) * rows + r) * 16u,
                                p.packed + (long long)(n_begin + r) * p.packed_pitch + (kb0 + j) * 16);
@@ -210,7 +218,7 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
             for (int it = dw; it < nkb && ok; it += kGvStages) {
                 const int grp = it / kb_per_grp;
                 while (grp_done < grp && ok) {
-                    // all eight decode warps pass here for every group, in order
+                    // every decode warp passes here for every group, in order
                     ++grp_done;
                     cp_async_wait_pending(n_grp - 1 - grp_done);
                     __syncwarp();  // every lane's copies of the group have landed: one arrival per warp
@@ -224,7 +232,7 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
                 if (!ok) break;
                 uint8_t* sW = smem + s * kGvStageBytes;
                 const int kg = (it * 64) / p.gs_k;
-                for (int u = lane; u < units; u += 32) {
+                for (int u = dh * 32 + lane; u < units; u += 64) {
                     const int r = u >> 2, w = u & 3;
                     const uint32_t word = *reinterpret_cast<const uint32_t*>(smem + idx_off + (uint32_t)(it * rows + r) * 16u + w * 4u);
                     const uint2 praw = *reinterpret_cast<const uint2*>(smem + pal_off + (uint32_t)(kg * rows + r) * 8u);
@@ -255,7 +263,7 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
                     tc_fence_after_sync();
                     const int lane_group = warp & 3;
                     const int r = lane_group * 32 + lane;
-                    const int n_acc = nkb > 1 ? 8 : 4;  // accumulators that have been written
+                    const int n_acc = 2 * (nkb < kGvMmaWarps ? nkb : kGvMmaWarps);  // accumulators that have been written
                     for (int c0 = 0; c0 < p.mpad; c0 += 16) {
                         float sum[16];
 #pragma unroll

@@ -97,10 +97,10 @@ def hard_forward(w: PackedWeight, x: torch.Tensor, lora=None):
     return y, t
 
 
-def hard_forward_smallm(w: PackedWeight, x: torch.Tensor) -> torch.Tensor:
+def hard_forward_smallm(w: PackedWeight, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     _mat(x, w.K)
     M = x.shape[0]
-    y = torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device)
+    y = out if out is not None else torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device)
     d = w.desc()
     P.check(P.lib().plz_hard_fwd_smallm(C.byref(d), x.data_ptr(), x.stride(0), M, y.data_ptr(), y.stride(0),
                                         P.stream_ptr()), "plz_hard_fwd_smallm")
