@@ -295,8 +295,113 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
     if (p.prof && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 4] = clock64() - t_entry;
 }
 
+// ---------------------------------------------------------------------------------------------
+// M <= 4 (single-token decode): no tensor cores, no barriers. One warp per weight row at a time; the warp reads
+// 128 bytes of packed indices (512 weights) per step with one coalesced load, shuffles them so that lane L owns
+// bytes L, L+32, L+64, L+96 (its activations are then 16 contiguous bytes per lane: conflict-free float4 reads of
+// the fp32 activations staged in shared memory), decodes with the same byte permutes and accumulates in fp32.
+// ---------------------------------------------------------------------------------------------
+template <int MM>
+__global__ void __launch_bounds__(512)
+lut_gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int M, int N, int K,
+                     const uint8_t* __restrict__ packed, long long pitch, const __nv_bfloat16* __restrict__ palette,
+                     int gs_n, int gs_k, int gs_k_shift, int n_kgroups, __nv_bfloat16* __restrict__ out, long long ld_out) {
+    extern __shared__ float xs[];  // [MM][K]
+    for (int i = threadIdx.x; i < MM * K; i += blockDim.x) {
+        const int m = i / K, k = i - m * K;
+        xs[i] = (m < M) ? __bfloat162float(x[(long long)m * ldx + k]) : 0.f;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int warps_per_block = blockDim.x >> 5;
+    const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int total_warps = gridDim.x * warps_per_block;
+    const int segs = (K + 511) / 512;  // 128-byte segments per row
+    for (int n = gw; n < N; n += total_warps) {
+        const uint8_t* prow = packed + (long long)n * pitch;
+        const __nv_bfloat16* pal_row = palette + (long long)(n / gs_n) * n_kgroups * 4;
+        float acc[MM];
+#pragma unroll
+        for (int m = 0; m < MM; ++m) acc[m] = 0.f;
+        uint32_t word = (lane * 16 < K) ? __ldg(reinterpret_cast<const uint32_t*>(prow) + lane) : 0u;
+        for (int sg = 0; sg < segs; ++sg) {
+            const int k_seg = sg * 512;
+            uint32_t next = 0u;
+            if (sg + 1 < segs && (k_seg + 512 + lane * 16) < K)
+                next = __ldg(reinterpret_cast<const uint32_t*>(prow + (sg + 1) * 128) + lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // byte lane + 32 j of the segment lives in word (lane / 4 + 8 j), byte lane % 4
+                const uint32_t wj = __shfl_sync(0xFFFFFFFFu, word, (lane >> 2) + 8 * j);
+                const uint32_t b = (wj >> (8 * (lane & 3))) & 0xFFu;
+                const int k = k_seg + 4 * (lane + 32 * j);
+                if (k < K) {
+                    const int kg = (gs_k_shift >= 0) ? (k >> gs_k_shift) : (k / gs_k);
+                    const uint2 praw = __ldg(reinterpret_cast<const uint2*>(pal_row + kg * 4));
+                    const PalRegs pal = pal_split(praw.x, praw.y);
+                    uint32_t s = (b | (b << 4)) & 0x0F0Fu;
+                    s = (s | (s << 2)) & 0x3333u;  // nibble i = index of weight k + i
+                    const uint32_t L = __byte_perm(pal.lo, 0u, s), H = __byte_perm(pal.hi, 0u, s);
+                    const uint32_t w01 = __byte_perm(L, H, 0x5140), w23 = __byte_perm(L, H, 0x7362);
+                    const float w0 = __uint_as_float(w01 << 16), w1 = __uint_as_float(w01 & 0xFFFF0000u);
+                    const float w2 = __uint_as_float(w23 << 16), w3 = __uint_as_float(w23 & 0xFFFF0000u);
+#pragma unroll
+                    for (int m = 0; m < MM; ++m) {
+                        const float4 xv = *reinterpret_cast<const float4*>(xs + m * K + k);
+                        acc[m] = fmaf(w0, xv.x, acc[m]);
+                        acc[m] = fmaf(w1, xv.y, acc[m]);
+                        acc[m] = fmaf(w2, xv.z, acc[m]);
+                        acc[m] = fmaf(w3, xv.w, acc[m]);
+                    }
+                }
+            }
+            word = next;
+        }
+#pragma unroll
+        for (int m = 0; m < MM; ++m) {
+            float v = acc[m];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+            if (lane == 0 && m < M) out[(long long)m * ld_out + n] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+template <int MM>
+static int launch_rows(const GemvArgs& a, cudaStream_t stream) {
+    const size_t smem = (size_t)MM * a.K * sizeof(float);
+    auto kern = lut_gemv_rows_kernel<MM>;
+    static int attr_smem[64] = {};
+    int dev = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    if (smem > 48 * 1024 && attr_smem[dev & 63] < (int)smem) {
+        PLZ_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_smem[dev & 63] = (int)smem;
+    }
+    const int sms = a.sm_count > 0 ? a.sm_count : 148;
+    int blocks_per_sm = (int)((200u * 1024u) / (smem + 1024));
+    if (blocks_per_sm > 4) blocks_per_sm = 4;
+    if (blocks_per_sm < 1) blocks_per_sm = 1;
+    int grid = sms * blocks_per_sm;
+    const int max_grid = (a.N + 15) / 16;
+    if (grid > max_grid) grid = max_grid;
+    int shift = -1;
+    for (int sh = 0; sh < 31; ++sh) if ((1 << sh) == a.gs_k) shift = sh;
+    kern<<<grid, 512, smem, stream>>>((const __nv_bfloat16*)a.x, a.ldx, a.M, a.N, a.K, (const uint8_t*)a.packed,
+                                      a.packed_pitch, (const __nv_bfloat16*)a.palette, a.gs_n, a.gs_k, shift, a.K / a.gs_k,
+                                      (__nv_bfloat16*)a.out, a.ld_out);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
 int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream) {
     if (a.M <= 0 || a.M > 64) { set_last_error("small-M forward handles 1 <= M <= 64 (M=%d)", a.M); return PLZ_ERR_BAD_SHAPE; }
+    // one to four rows, activations fit in shared memory as fp32: the barrier-free CUDA-core kernel is faster
+    if (a.M <= 4 && (size_t)a.K * 4 * (a.M <= 1 ? 1 : (a.M <= 2 ? 2 : 4)) <= 160 * 1024 && a.K % 16 == 0 && (a.packed_pitch % 4) == 0) {
+        if (a.M <= 1) return launch_rows<1>(a, stream);
+        if (a.M <= 2) return launch_rows<2>(a, stream);
+        return launch_rows<4>(a, stream);
+    }
     if (a.K % 64 || a.K / 256 + 1 > kGvMaxGroups) { set_last_error("small-M forward needs K %% 64 == 0 and K <= 16128 (K=%d)", a.K); return PLZ_ERR_BAD_SHAPE; }
     CUtensorMap tmX;
     const int mpad = a.M <= 16 ? 16 : (a.M <= 32 ? 32 : 64);

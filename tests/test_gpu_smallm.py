@@ -8,7 +8,7 @@ from helpers import assert_close, check_status
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("M,N,K,gs_n,gs_k", [(1, 256, 256, 1, 256), (8, 1024, 2560, 1, 256), (16, 9728, 2560, 1, 256),
+@pytest.mark.parametrize("M,N,K,gs_n,gs_k", [(1, 256, 256, 1, 256), (1, 9728, 2560, 1, 256), (2, 1000, 2560, 1, 256), (3, 2560, 9728, 1, 256), (8, 1024, 2560, 1, 256), (16, 9728, 2560, 1, 256),
                                              (33, 1000, 512, 1, 64), (64, 2560, 9728, 1, 256), (4, 1024, 1024, 256, 1024)])
 def test_small_m_forward(M, N, K, gs_n, gs_k):
     import plz_ops as ops
