@@ -319,7 +319,7 @@ int32_t plz_bwd_dx(const plz_weight_t* w, const void* dY, int64_t lddy, int32_t 
     g.packed = w->packed; g.packed_pitch = w->packed_pitch; g.palette = w->palette;
     g.gs_n = w->gs_n; g.gs_k = w->gs_k; g.Wn = w->N; g.Wk = w->K;
     if (lora) { g.r2 = lora->rank; g.A2 = dt; g.lda2 = lora->rank; g.B2 = lora->A; g.ldb2 = lora->lda; }
-    g.out = dX; g.ld_out = lddx; g.alpha = 1.0f;
+    g.out = dX; g.ld_out = lddx; g.alpha = 1.0f; g.prof = g_prof_buffer;
     return launch_lut_gemm(g, s);
 }
 

@@ -248,11 +248,14 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // Each of the 512 decode threads produces 32 weights (four 16-byte chunks of one 128-byte operand row)
             // per stage from 8 bytes of packed indices.
             // forward:  row = tile row n - j0 = t / 2, chunks 4*(t%2)..; k runs with the stage.
-            // backward: row = n - it*64 = t / 8, 64-wide k block a = (t%8)/2, chunks 4*(t%2)..; n runs with the stage.
+            // backward: 64-wide k block a = t / 128, row = n - it*64 = (t % 128) / 2, chunks 4*(t%2)..; n runs with the stage.
             const int t = threadIdx.x - 64;
+            // In both mappings eight consecutive lanes cover four rows x two halves of ONE 64-wide block, so that
+            // their 16-byte stores land on eight different swizzled chunk positions (a 128-bit store is served a
+            // quarter warp at a time; with one row per quarter warp it would be a 4-way bank conflict).
             const int h = t & 1;
-            const int rr = (BMODE == B_DECODE_K) ? (t >> 1) : (t >> 3);
-            const int a = (t >> 1) & 3;
+            const int rr = (BMODE == B_DECODE_K) ? (t >> 1) : ((t & 127) >> 1);
+            const int a = t >> 7;
             const int blocks_per_kgroup = p.gs_k / kBK;
             bool ok = true;
             int git = 0;
