@@ -169,6 +169,26 @@ int32_t plz_bwd_dw_hard(const plz_weight_t* w, const void* x, int64_t ldx, const
 int32_t plz_lora_bwd(const void* x, int64_t ldx, const void* dY, int64_t lddy, const void* t, const void* dt,
                      int32_t M, int32_t N, int32_t K, int32_t rank, float* dA, float* dB, void* stream);
 
+/* ---- the steps around the Linear in the distillation loop ------------------------------------
+ * One fused pass of fp32-master AdamW over a flat parameter of n elements:
+ *   g = grad * grad_scale (grad_scale carries the gradient-clipping coefficient and 1/world_size);
+ *   master *= 1 - lr*weight_decay; m, v updated; master -= lr/(1-beta1^step) * m / (sqrt(v)/sqrt(1-beta2^step) + eps);
+ *   param (may be NULL) = master clamped to [clamp_lo, clamp_hi] (no clamp if clamp_lo > clamp_hi), cast to param_dtype;
+ *   clamp_master != 0 also stores the clamped value in the master.
+ * dtype codes: 0 fp32, 1 fp16, 2 bf16. Replaces FP32MasterAdamW.step (scripts/train_qwen.py:154-215, torch.optim.AdamW
+ * with betas/eps of :600), clip_grad_norm_'s in-place scaling (:1303-1319) and the index-logit clamp to +-5 tau
+ * (:1343-1348), which cost eight passes over the state there. */
+int32_t plz_adamw_step(float* master, float* m, float* v, const void* grad, int32_t grad_dtype, float grad_scale, int64_t n,
+                       float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step, float clamp_lo,
+                       float clamp_hi, int32_t clamp_master, void* param, int32_t param_dtype, void* stream);
+
+/* Distillation loss of compute_loss (scripts/train_qwen.py:229-249), type "1-cos+norm_mse", fp32 math on bf16
+ * student / teacher states s, t [M, H]:  loss = w_cos * mean_tokens(1 - cos(s, t)) + w_mse * mean((s-t)^2) / max(mean(t^2), 1e-6),
+ * cosine with each norm clamped at 1e-4. out4 (device, may be NULL) receives {loss, l_cos, l_mse, mean(t^2)}.
+ * ds (may be NULL) receives upstream * dLoss/ds in ds_dtype (0 fp32, 2 bf16). ws: caller workspace of 4 + 3*M floats. */
+int32_t plz_distill_loss(const void* s, int64_t lds, const void* t, int64_t ldt, int32_t M, int32_t H, float w_cos, float w_mse,
+                         float upstream, float* ws, float* out4, void* ds, int64_t ldds, int32_t ds_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -11,6 +11,7 @@ What is executed from the reference (all on CPU):
   * ref_forward                                          scripts/test_triton_hard_forward.py:21-33
   * ref_backward                                         scripts/test_triton_soft_backward.py:45-117
   * pack_idx2                                            scripts/palettize_core.py:31-42
+  * compute_loss, FP32MasterAdamW                        scripts/train_qwen.py:229-249, 154-215
 The soft forward samples its Gumbel noise internally with torch.distributions.Gumbel; the noise is
 recovered by replaying the same torch seed, then stored in the fixture so that the tests need no RNG
 agreement.  Each oracle function is asserted equal (bit-exact for integer/gather work, 1e-6 relative
@@ -149,6 +150,29 @@ def main():
     close(O.from_nk_logits(dlog_o), dlog_r2.float(), 5e-3, "dLogits vs ref_backward (fp16 P)")
     close(dpal_o, dpal_r2.float(), 2e-2, "dPalette vs ref_backward (bf16 output)")
 
+    # ---- distillation loss and the fp32-master AdamW wrapper (scripts/train_qwen.py; importing it runs no training)
+    import train_qwen
+    hs = torch.randn(2, 24, 64, generator=g).to(torch.bfloat16)
+    ht = (hs.float() + 0.3 * torch.randn(2, 24, 64, generator=g)).to(torch.bfloat16)
+    hs[0, 0] = 0          # a zero-norm student row exercises the eps clamp of the cosine
+    hsg = hs.clone().float().requires_grad_(True)
+    loss_ref, info_ref = train_qwen.compute_loss(hsg, ht, {"loss_type": "1-cos+norm_mse", "loss_weights": {"cos": 0.5, "mse": 0.5}})
+    loss_ref.backward()
+    (l_o, lc_o, lm_o, tv_o), ds_o = O.distill_loss(hs, ht, 0.5, 0.5)
+    assert abs(l_o - loss_ref.item()) <= 1e-6 * max(1.0, abs(l_o)) and abs(lc_o - info_ref["cos"]) <= 1e-6
+    close(ds_o, hsg.grad, 1e-6, "distillation loss gradient vs compute_loss autograd")
+    p0 = (torch.randn(300, generator=g) * 2).to(torch.float16)
+    grads = [torch.randn(300, generator=g).to(torch.float16) * 0.1 for _ in range(3)]
+    par = torch.nn.Parameter(p0.clone())
+    ref_opt = train_qwen.FP32MasterAdamW([{"params": [par], "lr": 0.05}], betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0)
+    for gr in grads:
+        par.grad = gr.clone()
+        ref_opt.step()
+        with torch.no_grad():
+            par.data.clamp_(-5.0 * 0.4, 5.0 * 0.4)      # the +-5 tau clamp of the training loop at tau = 0.4
+    ma_o, mo_o, m_o, v_o = O.adamw_reference(p0, grads, 0.05, clamp=(-2.0, 2.0), clamp_master=False)
+    assert torch.equal(mo_o, par.data), "AdamW model copy differs from FP32MasterAdamW + clamp"
+
     # ---- counter-based noise: integer part known answers from the formula itself are pinned by value
     u24 = O.gumbel_hash_u24(5, np.arange(8, dtype=np.uint32))
 
@@ -167,6 +191,8 @@ def main():
         argmax_kn=logits.argmax(dim=0).numpy().astype(np.int8), w_ste_kn=bf16_bits(w_ste_ref), p_4kn=p_ref.numpy(),
         y_soft=bf16_bits(y_soft_ref), dx_soft=bf16_bits(dx_ref), dlogits_4kn=dlog_ref.numpy(), dpal_soft=dpal_ref.numpy(),
         hash_seed=5, hash_u24=u24,
+        loss_s=bf16_bits(hs), loss_t=bf16_bits(ht), loss_vals=np.array([loss_ref.item(), info_ref["cos"]]), loss_ds=hsg.grad.numpy(),
+        adam_p0=p0.numpy(), adam_grads=torch.stack(grads).numpy(), adam_model=par.data.numpy(),
     )
     print(f"oracle pinned against the reference; wrote {out} ({os.path.getsize(out) / 1024:.0f} KiB)")
 

@@ -257,3 +257,46 @@ def cosine(a: torch.Tensor, b: torch.Tensor) -> float:
     a, b = a.double().flatten(), b.double().flatten()
     den = (a.norm() * b.norm()).item()
     return (a @ b).item() / den if den > 0 else 1.0
+
+
+# --------------------------------------------------------------------------------------------
+# the steps around the Linear in the distillation loop
+# --------------------------------------------------------------------------------------------
+
+def distill_loss(s: torch.Tensor, t: torch.Tensor, w_cos: float = 0.5, w_mse: float = 0.5):
+    """compute_loss of the reference, type "1-cos+norm_mse" (scripts/train_qwen.py:229-249): fp32 math,
+    per-token cosine with eps 1e-4, MSE normalised by mean(t^2) clamped at 1e-6.
+    s, t [..., H].  Returns (loss, l_cos, l_mse, t_var) as python floats and dLoss/ds (fp32) by autograd."""
+    sf = s.detach().float().clone().requires_grad_(True)
+    tf = t.detach().float()
+    h = sf.shape[-1]
+    cos_per = torch.nn.functional.cosine_similarity(sf.reshape(-1, h), tf.reshape(-1, h), dim=-1, eps=1e-4)
+    l_cos = (1 - cos_per).mean()
+    t_var = (tf * tf).mean().clamp(min=1e-6)
+    l_mse = ((sf - tf) ** 2).mean() / t_var
+    tot = w_cos + w_mse
+    loss = (w_cos / tot) * l_cos + (w_mse / tot) * l_mse
+    loss.backward()
+    return (loss.item(), l_cos.item(), l_mse.item(), t_var.item()), sf.grad
+
+
+def adamw_reference(param, grads, lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, clamp=None, clamp_master=False,
+                    grad_scale=1.0):
+    """fp32-master AdamW as FP32MasterAdamW runs it (scripts/train_qwen.py:154-215: torch.optim.AdamW on an fp32 master,
+    model copy rewritten after every step; betas/eps :600) followed by the clamp of the model copy (:1343-1348).
+    param: initial model tensor (any float dtype); grads: list of per-step gradients.
+    Returns (master fp32, model copy in param.dtype, m, v)."""
+    master = param.detach().float().clone().requires_grad_(True)
+    opt = torch.optim.AdamW([master], lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+    model = param.detach().clone()
+    for g in grads:
+        master.grad = g.detach().float() * grad_scale
+        opt.step()
+        with torch.no_grad():
+            if clamp is not None and clamp_master:
+                master.clamp_(clamp[0], clamp[1])
+            model.copy_(master)
+            if clamp is not None:
+                model.clamp_(clamp[0], clamp[1])
+    st = opt.state[master]
+    return master.detach(), model, st["exp_avg"], st["exp_avg_sq"]

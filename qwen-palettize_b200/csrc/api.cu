@@ -431,4 +431,30 @@ int32_t plz_lora_bwd(const void* x, int64_t ldx, const void* dY, int64_t lddy, c
     return PLZ_OK;
 }
 
+int32_t plz_adamw_step(float* master, float* m, float* v, const void* grad, int32_t grad_dtype, float grad_scale, int64_t n,
+                       float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step, float clamp_lo,
+                       float clamp_hi, int32_t clamp_master, void* param, int32_t param_dtype, void* stream) {
+    if (n < 0 || step < 1) { set_last_error("adamw: n must be >= 0 and step >= 1"); return PLZ_ERR_BAD_SHAPE; }
+    if (n == 0) return PLZ_OK;
+    if (!master || !m || !v || !grad) { set_last_error("adamw: null state or gradient"); return PLZ_ERR_NULL; }
+    if (grad_dtype < 0 || grad_dtype > 2 || param_dtype < 0 || param_dtype > 2) { set_last_error("adamw: dtype codes are 0 fp32, 1 fp16, 2 bf16"); return PLZ_ERR_UNSUPPORTED; }
+    AdamParams p;
+    p.master = master; p.m = m; p.v = v; p.grad = grad; p.param = param; p.n = n;
+    p.grad_scale = grad_scale; p.lr = lr; p.beta1 = beta1; p.beta2 = beta2; p.eps = eps; p.weight_decay = weight_decay;
+    p.bias_c1 = 1.0f - powf(beta1, (float)step);
+    p.sqrt_bias_c2 = sqrtf(1.0f - powf(beta2, (float)step));
+    p.clamp_lo = clamp_lo; p.clamp_hi = clamp_hi; p.clamp_master = clamp_master;
+    return launch_adamw(p, grad_dtype, param_dtype, (cudaStream_t)stream);
+}
+
+int32_t plz_distill_loss(const void* s, int64_t lds, const void* t, int64_t ldt, int32_t M, int32_t H, float w_cos, float w_mse,
+                         float upstream, float* ws, float* out4, void* ds, int64_t ldds, int32_t ds_dtype, void* stream) {
+    if (M < 0 || H <= 0 || (H & 1)) { set_last_error("distill_loss: H must be even and positive (M=%d, H=%d)", M, H); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!s || !t || !ws) { set_last_error("distill_loss: null input or workspace"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)s & 3) || ((uintptr_t)t & 3) || (lds & 1) || (ldt & 1) || (ds && (ldds & 1))) { set_last_error("distill_loss: rows must be 4-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    if (ds_dtype != 0 && ds_dtype != 2) { set_last_error("distill_loss: gradient dtype must be 0 (fp32) or 2 (bf16)"); return PLZ_ERR_UNSUPPORTED; }
+    return launch_distill_loss(s, lds, t, ldt, M, H, 1e-4f, w_cos, w_mse, upstream, ws, out4, ds, ldds, ds_dtype, (cudaStream_t)stream);
+}
+
 }  // extern "C"

@@ -75,4 +75,19 @@ int launch_unpack_indices(const void* src, long long pitch, int N, int K, void* 
 int launch_dequant(const void* packed, long long pitch, const void* palette, int gs_n, int gs_k, int N, int K,
                    void* dst, long long d_n, long long d_k, cudaStream_t stream);
 
+// ---- train_ops.cu ------------------------------------------------------------------------------
+struct AdamParams {
+    float* master; float* m; float* v;
+    const void* grad; void* param;
+    long long n;
+    float grad_scale, lr, beta1, beta2, eps, weight_decay;
+    float bias_c1, sqrt_bias_c2;  // 1 - beta1^t, sqrt(1 - beta2^t)
+    float clamp_lo, clamp_hi; int clamp_master;
+};
+
+int launch_adamw(const AdamParams& p, int grad_dtype, int param_dtype, cudaStream_t stream);
+int launch_distill_loss(const void* s, long long lds, const void* t, long long ldt, int M, int H, float eps, float w_cos,
+                        float w_mse, float upstream, float* ws, float* out4, void* ds, long long ldds, int ds_dtype,
+                        cudaStream_t stream);
+
 }  // namespace plz

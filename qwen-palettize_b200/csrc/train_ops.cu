@@ -1,0 +1,165 @@
+// The two bandwidth-bound steps on either side of the Linear in the distillation loop:
+//
+//   adamw_clamp   fp32-master AdamW on a flat parameter (index logits, palettes, LoRA factors) with the gradient
+//                 clip coefficient, bias correction, decoupled weight decay and the post-step clamp to +-5 tau
+//                 folded into ONE pass over (grad, master, m, v) that also writes the model-dtype copy.
+//                 Reference: FP32MasterAdamW = torch.optim.AdamW on fp32 masters + copy back
+//                 (scripts/train_qwen.py:154-215, betas/eps :600), clip_grad_norm_ (:1303-1319),
+//                 par.data.clamp_(-5 tau, 5 tau) (:1343-1348) -- eight separate passes there.
+//   distill_loss  per-token 1 - cos plus MSE normalised by mean(t^2), fp32 math, forward and gradient
+//                 (compute_loss, scripts/train_qwen.py:229-249).
+#include "plz_launch.h"
+#include "soft_math.cuh"
+
+namespace plz {
+
+__device__ __forceinline__ float ld_as_f32(const float* p, long long i) { return p[i]; }
+__device__ __forceinline__ float ld_as_f32(const __half* p, long long i) { return __half2float(p[i]); }
+__device__ __forceinline__ float ld_as_f32(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void st_from_f32(float* p, long long i, float v) { p[i] = v; }
+__device__ __forceinline__ void st_from_f32(__half* p, long long i, float v) { p[i] = __float2half_rn(v); }
+__device__ __forceinline__ void st_from_f32(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+template <typename GradT, typename ParamT>
+__global__ void __launch_bounds__(256) adamw_clamp_kernel(const AdamParams p) {
+    const GradT* g = reinterpret_cast<const GradT*>(p.grad);
+    ParamT* out = reinterpret_cast<ParamT*>(p.param);
+    const float step_size = p.lr / p.bias_c1;
+    const bool do_clamp = p.clamp_lo <= p.clamp_hi;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += (long long)gridDim.x * blockDim.x) {
+        const float gr = ld_as_f32(g, i) * p.grad_scale;
+        float w = p.master[i];
+        w *= 1.0f - p.lr * p.weight_decay;                       // decoupled weight decay (torch.optim.AdamW order)
+        const float m = p.beta1 * p.m[i] + (1.0f - p.beta1) * gr;
+        const float v = p.beta2 * p.v[i] + (1.0f - p.beta2) * gr * gr;
+        const float denom = sqrtf(v) / p.sqrt_bias_c2 + p.eps;
+        w -= step_size * (m / denom);
+        float wc = w;
+        if (do_clamp) wc = fminf(fmaxf(w, p.clamp_lo), p.clamp_hi);
+        p.m[i] = m;
+        p.v[i] = v;
+        p.master[i] = p.clamp_master ? wc : w;
+        if (out != nullptr) st_from_f32(out, i, wc);
+    }
+}
+
+int launch_adamw(const AdamParams& p, int grad_dtype, int param_dtype, cudaStream_t stream) {
+    if (p.n <= 0) return PLZ_OK;
+    long long blocks = (p.n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+#define PLZ_ADAM(GT, PT) adamw_clamp_kernel<GT, PT><<<(unsigned)blocks, 256, 0, stream>>>(p)
+    if (grad_dtype == 0) {
+        if (param_dtype == 0) PLZ_ADAM(float, float); else if (param_dtype == 1) PLZ_ADAM(float, __half); else PLZ_ADAM(float, __nv_bfloat16);
+    } else if (grad_dtype == 1) {
+        if (param_dtype == 0) PLZ_ADAM(__half, float); else if (param_dtype == 1) PLZ_ADAM(__half, __half); else PLZ_ADAM(__half, __nv_bfloat16);
+    } else {
+        if (param_dtype == 0) PLZ_ADAM(__nv_bfloat16, float); else if (param_dtype == 1) PLZ_ADAM(__nv_bfloat16, __half); else PLZ_ADAM(__nv_bfloat16, __nv_bfloat16);
+    }
+#undef PLZ_ADAM
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// distillation loss. ws layout (fp32): [0] sum(1 - cos), [1] sum((s-t)^2), [2] sum(t^2), [3] unused,
+// then per token: dot, |s|^2, |t|^2 (3 floats).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+// one warp per token row
+__global__ void __launch_bounds__(256)
+distill_stats_kernel(const __nv_bfloat16* __restrict__ s, long long lds, const __nv_bfloat16* __restrict__ t, long long ldt,
+                     int M, int H, float eps, float* __restrict__ ws) {
+    __shared__ float part[3][8];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    float a_cos = 0.f, a_d2 = 0.f, a_t2 = 0.f;
+    for (int row = blockIdx.x * 8 + wib; row < M; row += gridDim.x * 8) {
+        const __nv_bfloat16* sr = s + (long long)row * lds;
+        const __nv_bfloat16* tr = t + (long long)row * ldt;
+        float dot = 0.f, s2 = 0.f, t2 = 0.f, d2 = 0.f;
+        for (int c = lane * 2; c < H; c += 64) {
+            const float2 sv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sr + c));
+            const float2 tv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(tr + c));
+            dot += sv.x * tv.x + sv.y * tv.y;
+            s2 += sv.x * sv.x + sv.y * sv.y;
+            t2 += tv.x * tv.x + tv.y * tv.y;
+            const float dx = sv.x - tv.x, dy = sv.y - tv.y;
+            d2 += dx * dx + dy * dy;
+        }
+        dot = warp_sum_f(dot); s2 = warp_sum_f(s2); t2 = warp_sum_f(t2); d2 = warp_sum_f(d2);
+        if (lane == 0) {
+            float* st = ws + 4 + 3ll * row;
+            st[0] = dot; st[1] = s2; st[2] = t2;
+            const float cosv = dot / (fmaxf(sqrtf(s2), eps) * fmaxf(sqrtf(t2), eps));
+            a_cos += 1.0f - cosv; a_d2 += d2; a_t2 += t2;
+        }
+    }
+    if (lane == 0) { part[0][wib] = a_cos; part[1][wib] = a_d2; part[2][wib] = a_t2; }
+    __syncthreads();
+    if (threadIdx.x < 3) {
+        float v = 0.f;
+        for (int i = 0; i < 8; ++i) v += part[threadIdx.x][i];
+        atomicAdd(ws + threadIdx.x, v);
+    }
+}
+
+template <typename GradT>
+__global__ void __launch_bounds__(256)
+distill_grad_kernel(const __nv_bfloat16* __restrict__ s, long long lds, const __nv_bfloat16* __restrict__ t, long long ldt,
+                    int M, int H, float eps, float w_cos, float w_mse, float upstream, const float* __restrict__ ws,
+                    float* __restrict__ out4, GradT* __restrict__ ds, long long ldds) {
+    const float inv_m = 1.0f / (float)M, inv_mh = 1.0f / ((float)M * (float)H);
+    const float t_var = fmaxf(ws[2] * inv_mh, 1e-6f);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && out4 != nullptr) {
+        const float l_cos = ws[0] * inv_m, l_mse = ws[1] * inv_mh / t_var;
+        out4[0] = w_cos * l_cos + w_mse * l_mse; out4[1] = l_cos; out4[2] = l_mse; out4[3] = t_var;
+    }
+    if (ds == nullptr) return;
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const float c_mse = upstream * w_mse * 2.0f * inv_mh / t_var;
+    for (int row = blockIdx.x * 8 + wib; row < M; row += gridDim.x * 8) {
+        const float* st = ws + 4 + 3ll * row;
+        const float dot = st[0], s2 = st[1], t2 = st[2];
+        const float ns = sqrtf(s2), nt = sqrtf(t2);
+        const float cs = fmaxf(ns, eps), ct = fmaxf(nt, eps);
+        // cos = dot / (cs * ct); d cos / d s = t / (cs ct) - [ns >= eps] * cos * s / ns^2 (the clamp has no slope below eps)
+        const float a = 1.0f / (cs * ct);
+        const float b = (ns >= eps) ? (dot * a) / s2 : 0.f;
+        const float c_cos = -upstream * w_cos * inv_m;
+        const __nv_bfloat16* sr = s + (long long)row * lds;
+        const __nv_bfloat16* tr = t + (long long)row * ldt;
+        for (int c = lane * 2; c < H; c += 64) {
+            const float2 sv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sr + c));
+            const float2 tv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(tr + c));
+            const float g0 = c_cos * (tv.x * a - sv.x * b) + c_mse * (sv.x - tv.x);
+            const float g1 = c_cos * (tv.y * a - sv.y * b) + c_mse * (sv.y - tv.y);
+            st_from_f32(ds, (long long)row * ldds + c, g0);
+            st_from_f32(ds, (long long)row * ldds + c + 1, g1);
+        }
+    }
+}
+
+int launch_distill_loss(const void* s, long long lds, const void* t, long long ldt, int M, int H, float eps, float w_cos,
+                        float w_mse, float upstream, float* ws, float* out4, void* ds, long long ldds, int ds_dtype,
+                        cudaStream_t stream) {
+    if (M <= 0 || H <= 0) return PLZ_OK;
+    PLZ_CUDA_CHECK(cudaMemsetAsync(ws, 0, 4 * sizeof(float), stream));
+    int blocks = (M + 7) / 8;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    distill_stats_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)s, lds, (const __nv_bfloat16*)t, ldt, M, H, eps, ws);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    if (ds_dtype == 0)
+        distill_grad_kernel<float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)s, lds, (const __nv_bfloat16*)t, ldt, M, H, eps,
+                                                                w_cos, w_mse, upstream, ws, out4, (float*)ds, ldds);
+    else
+        distill_grad_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)s, lds, (const __nv_bfloat16*)t, ldt, M, H,
+                                                                        eps, w_cos, w_mse, upstream, ws, out4, (__nv_bfloat16*)ds, ldds);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
+}  // namespace plz

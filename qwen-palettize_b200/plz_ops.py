@@ -190,3 +190,39 @@ def lora_backward(x: torch.Tensor, dy: torch.Tensor, t: torch.Tensor, dt: torch.
     P.check(P.lib().plz_lora_bwd(x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), t.data_ptr(), dt.data_ptr(),
                                  M, N, K, r, da.data_ptr(), db.data_ptr(), P.stream_ptr()), "plz_lora_bwd")
     return da, db
+
+
+_DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def adamw_step(master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, grad: torch.Tensor, step: int, lr: float,
+               betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0, grad_scale: float = 1.0, clamp=None,
+               clamp_master: bool = False, param: torch.Tensor | None = None):
+    """In-place fused fp32-master AdamW (+ optional clamp) on flat/contiguous tensors; writes `param` (model copy) if given."""
+    P._need_cuda(master, m, v, grad, param)
+    assert master.dtype == m.dtype == v.dtype == torch.float32 and master.is_contiguous() and grad.is_contiguous()
+    assert grad.numel() == master.numel() and (param is None or (param.is_contiguous() and param.numel() == master.numel()))
+    lo, hi = clamp if clamp is not None else (1.0, -1.0)
+    P.check(P.lib().plz_adamw_step(master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(), _DT[grad.dtype], float(grad_scale),
+                                   master.numel(), float(lr), float(betas[0]), float(betas[1]), float(eps), float(weight_decay),
+                                   int(step), float(lo), float(hi), int(clamp_master), param.data_ptr() if param is not None else None,
+                                   _DT[param.dtype] if param is not None else 0, P.stream_ptr()), "plz_adamw_step")
+
+
+def distill_loss(s: torch.Tensor, t: torch.Tensor, w_cos: float = 0.5, w_mse: float = 0.5, want_grad: bool = True,
+                 grad_dtype=torch.bfloat16, upstream: float = 1.0):
+    """s, t bf16 [..., H].  Returns (stats fp32 [4] = loss, l_cos, l_mse, mean(t^2) on the device, dLoss/ds or None)."""
+    H = s.shape[-1]
+    s2, t2 = s.reshape(-1, H), t.reshape(-1, H)
+    _mat(s2, H), _mat(t2, H)
+    M = s2.shape[0]
+    tot = float(w_cos) + float(w_mse)   # the reference normalises the two weights to sum 1 (normalize_weights)
+    if tot > 0:
+        w_cos, w_mse = w_cos / tot, w_mse / tot
+    ws = torch.empty(4 + 3 * M, dtype=torch.float32, device=s.device)
+    out4 = torch.empty(4, dtype=torch.float32, device=s.device)
+    ds = torch.empty(M, H, dtype=grad_dtype, device=s.device) if want_grad else None
+    P.check(P.lib().plz_distill_loss(s2.data_ptr(), s2.stride(0), t2.data_ptr(), t2.stride(0), M, H, float(w_cos), float(w_mse),
+                                     float(upstream), ws.data_ptr(), out4.data_ptr(), ds.data_ptr() if ds is not None else None,
+                                     H, _DT[grad_dtype], P.stream_ptr()), "plz_distill_loss")
+    return out4, (ds.reshape(s.shape) if ds is not None else None)

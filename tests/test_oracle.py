@@ -124,3 +124,15 @@ def test_soft_gradients_by_finite_difference():
         e = torch.zeros_like(lg); e[n, k, q] = eps
         num = (loss(pal, lg + e) - loss(pal, lg - e)) / (2 * eps)
         assert abs(num * tau - dlog[n, k, q]) <= 1e-5 * max(1.0, abs(num))
+
+
+def test_loss_and_optimizer_against_reference(golden):
+    """compute_loss and FP32MasterAdamW + clamp of the reference's training loop (scripts/train_qwen.py:154-249, 1343-1348)."""
+    s, t = bf16_from_bits(golden["loss_s"]), bf16_from_bits(golden["loss_t"])
+    (loss, l_cos, _, _), ds = O.distill_loss(s, t, 0.5, 0.5)
+    assert abs(loss - float(golden["loss_vals"][0])) <= 1e-6 and abs(l_cos - float(golden["loss_vals"][1])) <= 1e-6
+    assert_close(ds, torch.from_numpy(golden["loss_ds"]), "dLoss/ds", rel=1e-6, cos=0.999999)
+    p0 = torch.from_numpy(golden["adam_p0"])
+    grads = list(torch.from_numpy(golden["adam_grads"]))
+    _, model, _, _ = O.adamw_reference(p0, grads, 0.05, clamp=(-2.0, 2.0), clamp_master=False)
+    assert torch.equal(model, torch.from_numpy(golden["adam_model"]))
