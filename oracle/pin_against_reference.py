@@ -173,6 +173,19 @@ def main():
     ma_o, mo_o, m_o, v_o = O.adamw_reference(p0, grads, 0.05, clamp=(-2.0, 2.0), clamp_master=False)
     assert torch.equal(mo_o, par.data), "AdamW model copy differs from FP32MasterAdamW + clamp"
 
+    # ---- on-disk index / palette files: the reference's writer and reader on a small tensor
+    import io
+    fi = torch.randint(0, 4, (64, 96), generator=g, dtype=torch.uint8)           # (out_dim=64, in_dim=96), as palettize_tensor_2bit holds it
+    idx2_bytes = palettize_core.pack_indices_transposed_2bit(fi)                  # writer: transposes to (in, out), packs flat
+    tmp = os.path.join("/tmp", "pin_small.idx2")
+    with open(tmp, "wb") as f:
+        f.write(idx2_bytes)
+    fi_loaded = palettize_core.load_indices(tmp, 64, 96)                          # reader: (in_dim, out_dim)
+    assert torch.equal(fi_loaded, fi.t()), "reference writer/reader disagree"
+    assert O.read_idx2(idx2_bytes, 64, 96).tolist() == fi_loaded.numpy().tolist()
+    lut16 = (torch.randn(8, generator=g) * 0.02).to(torch.float16)
+    lut_bytes = lut16.numpy().tobytes()
+
     # ---- counter-based noise: integer part known answers from the formula itself are pinned by value
     u24 = O.gumbel_hash_u24(5, np.arange(8, dtype=np.uint32))
 
@@ -191,6 +204,7 @@ def main():
         argmax_kn=logits.argmax(dim=0).numpy().astype(np.int8), w_ste_kn=bf16_bits(w_ste_ref), p_4kn=p_ref.numpy(),
         y_soft=bf16_bits(y_soft_ref), dx_soft=bf16_bits(dx_ref), dlogits_4kn=dlog_ref.numpy(), dpal_soft=dpal_ref.numpy(),
         hash_seed=5, hash_u24=u24,
+        idx2_bytes=np.frombuffer(idx2_bytes, np.uint8), idx2_kn=fi_loaded.numpy().astype(np.int8), lut_bytes=np.frombuffer(lut_bytes, np.uint8), lut_vals=lut16.float().numpy(),
         loss_s=bf16_bits(hs), loss_t=bf16_bits(ht), loss_vals=np.array([loss_ref.item(), info_ref["cos"]]), loss_ds=hsg.grad.numpy(),
         adam_p0=p0.numpy(), adam_grads=torch.stack(grads).numpy(), adam_model=par.data.numpy(),
     )

@@ -300,3 +300,19 @@ def adamw_reference(param, grads, lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=
                 model.clamp_(clamp[0], clamp[1])
     st = opt.state[master]
     return master.detach(), model, st["exp_avg"], st["exp_avg_sq"]
+
+
+# --------------------------------------------------------------------------------------------
+# on-disk formats (scripts/palettize_core.py:31-48 writer, :159-178 readers)
+# --------------------------------------------------------------------------------------------
+
+def read_idx2(data: bytes, out_dim: int, in_dim: int) -> np.ndarray:
+    """.idx2 payload -> uint8 indices (in_dim, out_dim): the flat array is in (K, N) row-major order."""
+    n = out_dim * in_dim
+    arr = np.frombuffer(data, dtype=np.uint8)
+    flat = unpack_rows(arr[: (n + 3) // 4].reshape(1, -1), n)[0]
+    return flat.reshape(in_dim, out_dim)
+
+
+def read_lut_scalar(data: bytes) -> np.ndarray:
+    return np.frombuffer(data, dtype=np.float16).astype(np.float32)

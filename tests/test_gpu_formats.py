@@ -81,3 +81,17 @@ def test_soft_weights_match_oracle():
     _, w_soft_h, _, _ = O.soft_weights(lg, O.gumbel_hash(123, N, K), pal, tau, 1, 256)
     assert (got_h - w_soft_h).abs().max() <= 2e-2 * w_soft_h.abs().max()
     check_status()
+
+
+def test_idx2_and_lut_files_load_into_the_native_layout(golden):
+    import formats
+    data = golden["idx2_bytes"].tobytes()
+    packed, idx_kn = formats.load_idx2(data, 64, 96)
+    want_kn = golden["idx2_kn"].astype(np.uint8)                 # (K=96, N=64) as the reference's reader returns it
+    assert np.array_equal(idx_kn.cpu().numpy().astype(np.uint8), want_kn)
+    assert np.array_equal(packed.cpu().numpy(), O.pack_rows(want_kn.T.copy()))
+    assert formats.save_idx2(packed, 96) == data                 # round trip back to the file payload
+    pal = formats.load_lut_scalar(golden["lut_bytes"].tobytes())
+    assert pal.shape == (2, 4) and pal.dtype == torch.bfloat16
+    assert torch.equal(pal.cpu(), torch.from_numpy(golden["lut_vals"]).to(torch.bfloat16).reshape(2, 4))
+    check_status()

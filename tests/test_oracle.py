@@ -136,3 +136,10 @@ def test_loss_and_optimizer_against_reference(golden):
     grads = list(torch.from_numpy(golden["adam_grads"]))
     _, model, _, _ = O.adamw_reference(p0, grads, 0.05, clamp=(-2.0, 2.0), clamp_master=False)
     assert torch.equal(model, torch.from_numpy(golden["adam_model"]))
+
+
+def test_disk_formats_against_reference(golden):
+    """.idx2 / .lut_scalar payloads written by the reference's own writer (scripts/palettize_core.py:31-48)."""
+    data = golden["idx2_bytes"].tobytes()
+    assert np.array_equal(O.read_idx2(data, 64, 96), golden["idx2_kn"].astype(np.uint8))
+    assert np.array_equal(O.read_lut_scalar(golden["lut_bytes"].tobytes()), golden["lut_vals"])
