@@ -36,55 +36,79 @@ def peaks():
     return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
 
 
-class ClockSampler:
-    """SM clock, power and throttle reasons read through NVML (read-only queries) every few milliseconds by a
-    background thread while the timed region runs."""
+_SAMPLER_SRC = r"""
+import sys, time
+import pynvml as nv
+nv.nvmlInit()
+h = nv.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+print("max", nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM), flush=True)
+while True:
+    try:
+        print(time.time(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetPowerUsage(h) / 1000.0,
+              nv.nvmlDeviceGetCurrentClocksEventReasons(h), flush=True)
+    except Exception:
+        pass
+    time.sleep(0.002)
+"""
 
-    def __init__(self, gpu_index, period_s=0.005):
-        self.gpu_index, self.period_s = gpu_index, period_s
-        self.samples, self._stop, self._thr, self._h, self._nv = [], False, None, None, None
+
+class ClockSampler:
+    """SM clock, power and throttle reasons read through NVML (read-only queries) every 2 ms by a helper process
+    for the whole run; stop(t0, t1) keeps the samples taken inside the timed region [t0, t1] (time.time())."""
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.proc, self.path = gpu_index, None, None
 
     def start(self):
+        import subprocess
+        import tempfile
         try:
-            import threading
-            import pynvml as nv
-            nv.nvmlInit()
-            self._nv, self._h = nv, nv.nvmlDeviceGetHandleByIndex(self.gpu_index)
-            self._thr = threading.Thread(target=self._loop, daemon=True)
-            self._thr.start()
+            fd, self.path = tempfile.mkstemp(suffix=".clk")
+            os.close(fd)
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_SRC, str(self.gpu_index)], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
         except Exception:
-            self._thr = None
+            self.proc = None
 
-    def _loop(self):
-        nv, h = self._nv, self._h
-        while not self._stop:
+    def ready(self, timeout=20.0):
+        """Wait until the helper has produced its first sample."""
+        t_end = time.time() + timeout
+        while self.proc is not None and time.time() < t_end:
             try:
-                self.samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetPowerUsage(h) / 1000.0,
-                                     nv.nvmlDeviceGetCurrentClocksEventReasons(h)))
-            except Exception:
+                if sum(1 for _ in open(self.path)) >= 3:
+                    return
+            except OSError:
                 pass
-            time.sleep(self.period_s)
+            time.sleep(0.05)
 
-    def stop(self):
+    def stop(self, t0, t1):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self._thr is None:
+        if self.proc is None:
             return out
-        self._stop = True
-        self._thr.join(timeout=2)
-        nv, h = self._nv, self._h
+        self.proc.terminate()
         try:
-            out["sm_max_mhz"] = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            self.proc.wait(timeout=5)
         except Exception:
-            pass
-        if self.samples:
+            self.proc.kill()
+        rows = []
+        for line in open(self.path):
+            f = line.split()
+            try:
+                if f[0] == "max":
+                    out["sm_max_mhz"] = int(f[1])
+                elif len(f) == 4 and t0 <= float(f[0]) <= t1:
+                    rows.append((int(f[1]), float(f[2]), int(f[3])))
+            except (ValueError, IndexError):
+                continue
+        os.unlink(self.path)
+        if rows:
             bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
                     "hw_power_brake_slowdown": 0x80}
             seen = 0
-            for _, _, r in self.samples:
+            for _, _, r in rows:
                 seen |= r
-            out.update(sm_mhz=statistics.median(s[0] for s in self.samples), samples=len(self.samples),
-                       sm_min_mhz=min(s[0] for s in self.samples), power_w_max=max(s[1] for s in self.samples),
-                       reasons=sorted(k for k, v in bits.items() if seen & v))
+            out.update(sm_mhz=statistics.median(r[0] for r in rows), samples=len(rows), sm_min_mhz=min(r[0] for r in rows),
+                       power_w_max=max(r[1] for r in rows), reasons=sorted(k for k, v in bits.items() if seen & v))
         return out
 
 
@@ -125,7 +149,7 @@ def run_ours(args):
     packed = ops.empty_packed(N_OUT, K_IN, dev)
     w = ops.PackedWeight(packed, palette, N_OUT, K_IN, 1, 256)
     exch = dp.GradExchange()
-    phases = ["select", "fwd", "dw", "lora_bwd", "dx"]
+    phases = ["select", "fwd", "lora_dt", "dw", "dx"]
     ev = {p: [] for p in phases}
 
     def step(record):
@@ -135,20 +159,17 @@ def run_ours(args):
         if record: marks[1].record()
         y, t = ops.hard_forward(w, x, lora)                       # lora_down + LUT GEMM (+ LoRA block)
         if record: marks[2].record()
-        dlog, dpal = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=TAU)
+        dt = ops.lora_dt(lora, dy)                                # skinny product, timed with the dx phase below
         if record: marks[3].record()
-        h1 = exch.start([dlog, dpal])                             # overlaps the dX GEMM below (N > 1 only)
-        dx, dt = ops.backward_dx(w, dy, lora)                     # lora_up_bwd + LUT GEMM (+ LoRA block)
+        dlog, dpal, da, db = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=TAU, lora_ws=(t, dt))
         if record: marks[4].record()
-        da, db = ops.lora_backward(x, dy, t, dt)
+        h1 = exch.start([dlog, dpal, da, db])                     # overlaps the dX GEMM below (N > 1 only)
+        dx = ops.backward_dx_with_dt(w, dy, lora, dt)             # LUT GEMM (+ LoRA block)
         if record: marks[5].record()
-        h2 = exch.start([da, db])
         exch.finish(h1)
-        exch.finish(h2)
         if record:
             ev["select"].append((marks[0], marks[1])); ev["fwd"].append((marks[1], marks[2]))
-            ev["dw"].append((marks[2], marks[3])); ev["dx"].append((marks[3], marks[4]))
-            ev["lora_bwd"].append((marks[4], marks[5]))
+            ev["lora_dt"].append((marks[2], marks[3])); ev["dw"].append((marks[3], marks[4])); ev["dx"].append((marks[4], marks[5]))
         return y, dx, dlog, dpal, da, db
 
     def barrier():
@@ -156,22 +177,26 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local if world > 1 else 0)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step(False)
     barrier()
     plz_native.device_status()
-    sampler = ClockSampler(local if world > 1 else 0)
-    if rank == 0:
-        sampler.start()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if rank == 0:
+        sampler.ready()
     barrier()
+    wall0 = time.time()
     t0.record()
     for _ in range(args.steps):
         step(True)
     t1.record()
     barrier()
+    wall1 = time.time()
     ms = t0.elapsed_time(t1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
     plz_native.device_status()
     if world > 1:
         tt = torch.tensor([ms], device=dev)
@@ -190,8 +215,7 @@ def run_ours(args):
         b.record()
         torch.cuda.synchronize()
         return a.elapsed_time(b) / n
-    skinny = {"fwd": timed(lambda: ops.dense_forward(d["lora_a"], x)), "dx": timed(lambda: ops.dense_backward_dx(d["lora_b"], dy)),
-              "dw": 0.0}
+    skinny = {"fwd": timed(lambda: ops.dense_forward(d["lora_a"], x)), "dx": 0.0, "dw": 0.0}
 
     # ---- end to end: host buffers in, gradients out, through the public step call
     hx, hdy = x.cpu().pin_memory(), dy.cpu().pin_memory()
@@ -268,10 +292,10 @@ def run_ours(args):
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": hx.numel() * 2 + hdy.numel() * 2,
                 "d2h_bytes_per_step": sum(h.numel() * 4 for h in hout), "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": 8 * args.steps,
+        "gpu_launches": 6 * args.steps,
         "phases_ms": phase_ms,
         "tflops_step": 3 * GEMM_FLOPS * world / (ms / args.steps * 1e-3) / 1e12,
-        "roofline": {"bound": "tensor", "kernel": {"fwd": "lut_gemm_kernel<2,B_DECODE_K>", "dw": "tn_gemm_kernel<EPI_SOFT,float>",
+        "roofline": {"bound": "tensor", "kernel": {"fwd": "lut_gemm_kernel<2,B_DECODE_K>", "dw": "tn_gemm_kernel<EPI_SOFT,float,true> (+ dA, dB items)",
                                                     "dx": "lut_gemm_kernel<2,B_DECODE_MN>"}[gemm_phase],
                      "achieved": achieved, "peak": pk["tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / pk["tflops_sustained"],
                      "traffic": traffic[gemm_phase], "traffic_note": "ncu small-case ratio x algorithmic bytes of the full launch", "algorithmic_bytes": alg[gemm_phase], "peak_source": pk["source"] + " (sustained cuBLAS bf16)",

@@ -147,6 +147,12 @@ int32_t plz_dense_fwd(const void* Wd, int64_t ldw, int32_t N, int32_t K, const v
  * grad_x = grad_y @ W.T (scripts/fused_lut_linear_cuda.py:944). */
 int32_t plz_bwd_dx(const plz_weight_t* w, const void* dY, int64_t lddy, int32_t M, const plz_lora_t* lora,
                    void* dt, void* dX, int64_t lddx, void* stream);
+/* The two halves of plz_bwd_dx for callers that want dt early (it is also an input of the LoRA factor gradients, so
+ * computing it first lets plz_bwd_dw_soft_lora run before the dX product and the gradient exchange overlap with dX):
+ * plz_lora_dt: dt[M, rank] = scale * dY B;  plz_bwd_dx_with_dt: dX = dY W + dt A with dt as given. */
+int32_t plz_lora_dt(const plz_lora_t* lora, const void* dY, int64_t lddy, int32_t M, int32_t N, void* dt, void* stream);
+int32_t plz_bwd_dx_with_dt(const plz_weight_t* w, const void* dY, int64_t lddy, int32_t M, const plz_lora_t* lora, const void* dt,
+                           void* dX, int64_t lddx, void* stream);
 int32_t plz_dense_bwd_dx(const void* Wd, int64_t ldw, int32_t N, int32_t K, const void* dY, int64_t lddy,
                          int32_t M, const plz_lora_t* lora, void* dt, void* dX, int64_t lddx, void* stream);
 
@@ -159,6 +165,13 @@ int32_t plz_dense_bwd_dx(const void* Wd, int64_t ldw, int32_t N, int32_t K, cons
 int32_t plz_bwd_dw_soft(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy,
                         int32_t M, const plz_logits_t* logits, const plz_noise_t* noise, float tau,
                         void* dlogits, float* dpalette, void* stream);
+/* plz_bwd_dw_soft plus the LoRA factor gradients in the same launch: dA[rank, K] += dt^T x and dB[N, rank] += dY^T t
+ * (fp32, accumulated) are computed by extra work items that fill the last, partially occupied round of the persistent
+ * weight-gradient kernel, so x and dY are not streamed a second time. t / dt as left by plz_hard_fwd / plz_bwd_dx.
+ * Autograd of scripts/qwen_model.py:300-304 fused with scripts/fused_lut_linear_cuda.py:952-961. */
+int32_t plz_bwd_dw_soft_lora(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M,
+                             const plz_logits_t* logits, const plz_noise_t* noise, float tau, void* dlogits, float* dpalette,
+                             const void* t, const void* dt, int32_t rank, float* dA, float* dB, void* stream);
 /* Hard-mode palette gradient dPalette[group][idx[n,k]] += dW[n,k] (fp32, accumulated):
  * fused_lut_linear_bwd_grad_palette_kernel (scripts/fused_lut_kernel.cu:902-1127). */
 int32_t plz_bwd_dw_hard(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy,

@@ -323,6 +323,35 @@ int32_t plz_bwd_dx(const plz_weight_t* w, const void* dY, int64_t lddy, int32_t 
     return launch_lut_gemm(g, s);
 }
 
+int32_t plz_lora_dt(const plz_lora_t* lora, const void* dY, int64_t lddy, int32_t M, int32_t N, void* dt, void* stream) {
+    if (!lora) { set_last_error("null LoRA descriptor"); return PLZ_ERR_NULL; }
+    if (M < 0 || N <= 0) { set_last_error("lora_dt: bad shape"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!dY) { set_last_error("null gradient pointer"); return PLZ_ERR_NULL; }
+    int rc = check_lora(lora, dt);
+    if (rc) return rc;
+    return lora_up_bwd(lora, dY, lddy, M, N, dt, (cudaStream_t)stream);
+}
+
+int32_t plz_bwd_dx_with_dt(const plz_weight_t* w, const void* dY, int64_t lddy, int32_t M, const plz_lora_t* lora, const void* dt,
+                           void* dX, int64_t lddx, void* stream) {
+    int rc = check_weight(w, true);
+    if (rc) return rc;
+    if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (w->N % 64) { set_last_error("bwd_dx needs N %% 64 == 0 (N=%d)", w->N); return PLZ_ERR_BAD_SHAPE; }
+    if (!dY || !dX) { set_last_error("null gradient pointer"); return PLZ_ERR_NULL; }
+    if ((rc = check_lora(lora, dt))) return rc;
+    LutGemmArgs g = {};
+    g.bmode = B_DECODE_MN; g.M = M; g.J = w->K; g.R = w->N;
+    g.A = dY; g.lda = lddy;
+    g.packed = w->packed; g.packed_pitch = w->packed_pitch; g.palette = w->palette;
+    g.gs_n = w->gs_n; g.gs_k = w->gs_k; g.Wn = w->N; g.Wk = w->K;
+    if (lora) { g.r2 = lora->rank; g.A2 = dt; g.lda2 = lora->rank; g.B2 = lora->A; g.ldb2 = lora->lda; }
+    g.out = dX; g.ld_out = lddx; g.alpha = 1.0f; g.prof = g_prof_buffer;
+    return launch_lut_gemm(g, (cudaStream_t)stream);
+}
+
 int32_t plz_dense_bwd_dx(const void* Wd, int64_t ldw, int32_t N, int32_t K, const void* dY, int64_t lddy, int32_t M,
                          const plz_lora_t* lora, void* dt, void* dX, int64_t lddx, void* stream) {
     if (N <= 0 || K <= 0 || M < 0 || N % 64 || K % 8) { set_last_error("dense_bwd_dx: bad shape M=%d N=%d K=%d", M, N, K); return PLZ_ERR_BAD_SHAPE; }
@@ -342,7 +371,8 @@ int32_t plz_dense_bwd_dx(const void* Wd, int64_t ldw, int32_t N, int32_t K, cons
 
 static int bwd_dw_common(int epi, const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy,
                          int32_t M, const plz_logits_t* logits, const plz_noise_t* noise, float tau, void* dlogits,
-                         float* dpalette, void* stream) {
+                         float* dpalette, void* stream, const void* t = nullptr, const void* dt = nullptr, int rank = 0,
+                         float* dA = nullptr, float* dB = nullptr) {
     int rc = check_weight(w, epi == EPI_HARD);
     if (rc) return rc;
     if (M <= 0) { if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; } return PLZ_OK; }
@@ -375,6 +405,15 @@ static int bwd_dw_common(int epi, const plz_weight_t* w, const void* x, int64_t 
     } else {
         a.tau = 1.0f;
     }
+    if (rank > 0) {
+        // dB[n, r] += sum_m t[m, r] dY[m, n] and dA[r, k] += sum_m dt[m, r] x[m, k] ride as extra items of this launch
+        const bool dy_is_p = !rows_are_k;  // P = dY when rows are n
+        a.side_rank = rank;
+        a.side_S[0] = dB ? t : nullptr; a.side_ld[0] = rank; a.side_q_is_p[0] = dy_is_p ? 1 : 0;
+        a.side_out[0] = dB; a.side_si[0] = 1; a.side_sj[0] = rank;
+        a.side_S[1] = dA ? dt : nullptr; a.side_ld[1] = rank; a.side_q_is_p[1] = dy_is_p ? 0 : 1;
+        a.side_out[1] = dA; a.side_si[1] = w->K; a.side_sj[1] = 1;
+    }
     a.palette = w->palette; a.dpalette = dpalette;
     a.gs_n = w->gs_n; a.gs_k = w->gs_k; a.n_kgroups = w->K / w->gs_k;
     a.packed = w->packed; a.packed_pitch = w->packed_pitch;
@@ -390,6 +429,15 @@ int32_t plz_bwd_dw_soft(const plz_weight_t* w, const void* x, int64_t ldx, const
                         float* dpalette, void* stream) {
     if (!(tau > 0.f)) { set_last_error("tau must be positive"); return PLZ_ERR_BAD_SHAPE; }
     return bwd_dw_common(EPI_SOFT, w, x, ldx, dY, lddy, M, logits, noise, tau, dlogits, dpalette, stream);
+}
+
+int32_t plz_bwd_dw_soft_lora(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M,
+                             const plz_logits_t* logits, const plz_noise_t* noise, float tau, void* dlogits, float* dpalette,
+                             const void* t, const void* dt, int32_t rank, float* dA, float* dB, void* stream) {
+    if (!(tau > 0.f)) { set_last_error("tau must be positive"); return PLZ_ERR_BAD_SHAPE; }
+    if (rank <= 0 || rank > 64 || rank % 8) { set_last_error("LoRA rank %d must be a multiple of 8 in [8, 64]", rank); return PLZ_ERR_BAD_SHAPE; }
+    if ((dA && !dt) || (dB && !t)) { set_last_error("bwd_dw_soft_lora: dA needs dt and dB needs t"); return PLZ_ERR_NULL; }
+    return bwd_dw_common(EPI_SOFT, w, x, ldx, dY, lddy, M, logits, noise, tau, dlogits, dpalette, stream, t, dt, rank, dA, dB);
 }
 
 int32_t plz_bwd_dw_hard(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M,

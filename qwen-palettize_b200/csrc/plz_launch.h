@@ -42,6 +42,9 @@ struct TnArgs {
     const void* palette; float* dpalette; int gs_n, gs_k, n_kgroups;
     const void* packed; long long packed_pitch;
     int sm_count;
+    // optional side jobs appended to a dW launch: out[r, j] += sum_m S[m, r] * (q_is_p ? P : Q)[m, j]
+    const void* side_S[2]; long long side_ld[2]; int side_rank; int side_q_is_p[2];
+    float* side_out[2]; long long side_si[2], side_sj[2];
 };
 int launch_tn_gemm(const TnArgs& a, cudaStream_t stream);
 

@@ -42,6 +42,13 @@ struct TnParams {
     const __nv_bfloat16* palette; float* dpalette;
     int gs_n, gs_k, n_kgroups;
     const uint8_t* packed; long long packed_pitch;  // EPI_HARD
+    // Side jobs (the LoRA factor gradients): extra work items appended to the list, D[r, j] = sum_m S[m, r] * Qs[m, j]
+    // with S a skinny [M, rank] matrix and Qs one of the two main operands; results are atomically added to `out`.
+    struct Side {
+        int tiles_j, splits, m_chunk, q_is_p, out_I, out_J, first_item;
+        float* out; long long out_si, out_sj;
+    } side[2];
+    int n_side_items;
     StatusWord* status;
 };
 
@@ -63,7 +70,7 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;"
 template <int EPI, typename LogitT, bool ROWS_K>
 __global__ void __launch_bounds__(kTnThreads, 1)
 tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-               const TnParams p) {
+               const __grid_constant__ CUtensorMap tmS0, const __grid_constant__ CUtensorMap tmS1, const TnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -82,7 +89,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     const int lane = threadIdx.x & 31;
     const int tiles_i = (p.I + 127) / 128;
     const int tiles_j = (p.J + 255) / 256;
-    const int n_tiles = p.n_items;
+    const int n_tiles = p.n_items + p.n_side_items;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTnStages; ++s) {
@@ -97,6 +104,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         mbar_fence_init();
         tma_prefetch_desc(&tmP);
         tma_prefetch_desc(&tmQ);
+        if (p.n_side_items) { tma_prefetch_desc(&tmS0); tma_prefetch_desc(&tmS1); }
     }
     if (warp == 1) {
         tmem_alloc(smem_u32((const void*)tmem_slot), 512);
@@ -110,9 +118,17 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     // tile -> (split, i tile, j tile); i fastest so that one wave of CTAs covers every i tile
     // item -> (split, i tile, j tile, first column inside the tile, columns); i fastest so that one wave of CTAs
     // covers every i tile. Items past n_whole are the two 128-column halves of a tile.
-    auto tile_coords = [&](int item, int& sp, int& ti, int& tj, int& c_off, int& c_num) {
+    auto tile_coords = [&](int item, int& sp, int& ti, int& tj, int& c_off, int& c_num, int& job) {
+        c_off = 0; c_num = 256; job = -1;
+        if (item >= p.n_items) {
+            job = (p.side[1].splits > 0 && item >= p.side[1].first_item) ? 1 : 0;
+            const int r = item - p.side[job].first_item;
+            ti = 0;
+            tj = r % p.side[job].tiles_j;
+            sp = r / p.side[job].tiles_j;
+            return;
+        }
         int t = item;
-        c_off = 0; c_num = 256;
         if (item >= p.n_whole) {
             t = p.n_whole + ((item - p.n_whole) >> 1);
             c_off = ((item - p.n_whole) & 1) * 128;
@@ -123,9 +139,10 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         tj = r % tiles_j;
         sp = r / tiles_j;
     };
-    auto m_range = [&](int sp, int& m_begin, int& nkb) {
-        m_begin = sp * p.m_chunk;
-        int m_end = m_begin + p.m_chunk;
+    auto m_range = [&](int sp, int job, int& m_begin, int& nkb) {
+        const int chunk = (job < 0) ? p.m_chunk : p.side[job].m_chunk;
+        m_begin = sp * chunk;
+        int m_end = m_begin + chunk;
         if (m_end > p.M) m_end = p.M;
         nkb = (m_end - m_begin + 63) / 64;
         if (nkb < 0) nkb = 0;
@@ -138,9 +155,9 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             bool ok = true;
             int git = 0;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                int sp, ti, tj, c_off, c_num, m_begin, nkb;
-                tile_coords(t, sp, ti, tj, c_off, c_num);
-                m_range(sp, m_begin, nkb);
+                int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
+                tile_coords(t, sp, ti, tj, c_off, c_num, job);
+                m_range(sp, job, m_begin, nkb);
                 for (int it = 0; it < nkb; ++it, ++git) {
                     const int s = git % kTnStages;
                     const uint32_t ph = (git / kTnStages) & 1;
@@ -151,10 +168,13 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                     mbar_arrive_expect_tx(full(s), kTnABytes + (uint32_t)c_num * 128u);
                     const int m = m_begin + it * 64;
 #pragma unroll
-                    for (int q = 0; q < 2; ++q) tma_load_2d(sA + q * 8192u, &tmP, full(s), ti * 128 + q * 64, m);
+                    const CUtensorMap* mp = (job < 0) ? &tmP : (job == 0 ? &tmS0 : &tmS1);
+                    const CUtensorMap* mq = (job < 0) ? &tmQ : (p.side[job].q_is_p ? &tmP : &tmQ);
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) tma_load_2d(sA + q * 8192u, mp, full(s), ti * 128 + q * 64, m);
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
-                        if (q * 64 < c_num) tma_load_2d(sB + q * 8192u, &tmQ, full(s), tj * 256 + c_off + q * 64, m);
+                        if (q * 64 < c_num) tma_load_2d(sB + q * 8192u, mq, full(s), tj * 256 + c_off + q * 64, m);
                     last_fill[s] = git;
                 }
             }
@@ -177,9 +197,9 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             bool ok = true;
             int git = 0, lt = 0;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
-                int sp, ti, tj, c_off, c_num, m_begin, nkb;
-                tile_coords(t, sp, ti, tj, c_off, c_num);
-                m_range(sp, m_begin, nkb);
+                int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
+                tile_coords(t, sp, ti, tj, c_off, c_num, job);
+                m_range(sp, job, m_begin, nkb);
                 const int buf = lt & 1;
                 const uint32_t idesc = make_idesc(128, c_num, 1, 1);
                 ok = mbar_wait(acc_empty(buf), ((lt >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_ACCUM, 1);
@@ -215,9 +235,9 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         bool ok = true;
         int lt = 0;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
-            int sp, ti, tj, c_off, c_num, m_begin, nkb;
-            tile_coords(t, sp, ti, tj, c_off, c_num);
-            m_range(sp, m_begin, nkb);
+            int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
+            tile_coords(t, sp, ti, tj, c_off, c_num, job);
+            m_range(sp, job, m_begin, nkb);
             const int buf = lt & 1;
             ok = mbar_wait(acc_full(buf), (lt >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 2);
             if (!ok) break;
@@ -228,18 +248,21 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             const bool row_ok = row < p.I;
             const int colbase = tj * 256 + c_off + col_half * wcols;
 
-            if (EPI == EPI_STORE) {
+            if (EPI == EPI_STORE || job >= 0) {
+                float* o_ptr = (job < 0) ? p.out : p.side[job].out;
+                const long long o_si = (job < 0) ? p.out_si : p.side[job].out_si, o_sj = (job < 0) ? p.out_sj : p.side[job].out_sj;
+                const int o_I = (job < 0) ? p.out_I : p.side[job].out_I, o_J = (job < 0) ? p.out_J : p.side[job].out_J;
+                const float o_alpha = (job < 0) ? p.alpha : 1.0f;
 #pragma unroll 1
                 for (int c0 = 0; c0 < wcols; c0 += 16) {
                     uint32_t v[16];
                     tmem_ld_32x16(trow + c0, v);
-                    if (nkb > 0 && row < p.out_I) {
+                    if (nkb > 0 && row < o_I) {
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
                             const int col = colbase + c0 + c;
-                            if (col < p.out_J)
-                                atomicAdd(p.out + (long long)row * p.out_si + (long long)col * p.out_sj,
-                                          __uint_as_float(v[c]) * p.alpha);
+                            if (col < o_J)
+                                atomicAdd(o_ptr + (long long)row * o_si + (long long)col * o_sj, __uint_as_float(v[c]) * o_alpha);
                         }
                     }
                 }
@@ -491,7 +514,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 
 template <int EPI, typename LogitT, bool ROWS_K>
 static int launch_tn_t(const TnArgs& a, const TnParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ,
-                       int grid, cudaStream_t stream) {
+                       const CUtensorMap& tmS0, const CUtensorMap& tmS1, int grid, cudaStream_t stream) {
     auto kern = tn_gemm_kernel<EPI, LogitT, ROWS_K>;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -500,7 +523,7 @@ static int launch_tn_t(const TnArgs& a, const TnParams& p, const CUtensorMap& tm
         PLZ_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTnSmemBytes));
         attr_set[dev & 63] = true;
     }
-    kern<<<grid, kTnThreads, kTnSmemBytes, stream>>>(tmP, tmQ, p);
+    kern<<<grid, kTnThreads, kTnSmemBytes, stream>>>(tmP, tmQ, tmS0, tmS1, p);
     PLZ_CUDA_CHECK(cudaGetLastError());
     return PLZ_OK;
 }
@@ -571,20 +594,49 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
     if (g_debug_sm_limit > 0 && g_debug_sm_limit < sms) sms = g_debug_sm_limit;
     const int grid = tiles < sms ? tiles : sms;
     p.n_whole = tiles; p.n_items = tiles;
+    CUtensorMap tmS0 = tmP, tmS1 = tmP;
+    p.n_side_items = 0;
+    p.side[0].splits = p.side[1].splits = 0;
+    for (int b = 0; b < 2; ++b) {
+        if (a.epi == EPI_STORE || !a.side_S[b] || !a.side_out[b] || a.side_rank <= 0) continue;
+        if ((rc = make_tmap_bf16(b == 0 ? &tmS0 : &tmS1, a.side_S[b], a.M, a.side_rank, a.side_ld[b], 64, 64))) return rc;
+        TnParams::Side& sd = p.side[b];
+        sd.q_is_p = a.side_q_is_p[b];
+        const int width = sd.q_is_p ? a.I : a.J;
+        sd.tiles_j = (width + 255) / 256;
+        const int blocks = (a.M + 63) / 64;
+        int sp = blocks >= 32 ? 2 : 1;  // two half-length items cost about as much as the half tiles of the last round
+        sd.m_chunk = ((blocks + sp - 1) / sp) * 64;
+        sd.splits = (a.M + sd.m_chunk - 1) / sd.m_chunk;
+        sd.out = a.side_out[b]; sd.out_si = a.side_si[b]; sd.out_sj = a.side_sj[b];
+        sd.out_I = a.side_rank; sd.out_J = width;
+    }
     if (a.epi != EPI_STORE) {
         // the last, partially filled round of the persistent schedule is cut into half tiles
         const int rem = tiles % grid;
         if (tiles > grid && rem > 0 && 2 * rem <= grid) { p.n_whole = tiles - rem; p.n_items = p.n_whole + 2 * rem; }
     }
+    {
+        int next = p.n_items;
+        for (int b = 0; b < 2; ++b) {
+            p.side[b].first_item = next;
+            next += p.side[b].splits * p.side[b].tiles_j * (p.side[b].splits > 0 ? 1 : 0);
+        }
+        p.n_side_items = next - p.n_items;
+        if (p.side[0].splits == 0 && p.side[1].splits > 0) {
+            // keep job 0 populated so that the item -> job mapping stays a simple threshold
+            p.side[0] = p.side[1]; tmS0 = tmS1; p.side[1].splits = 0; p.side[0].first_item = p.n_items;
+        }
+    }
     switch (a.epi) {
-        case EPI_STORE: return launch_tn_t<EPI_STORE, float, false>(a, p, tmP, tmQ, grid, stream);
+        case EPI_STORE: return launch_tn_t<EPI_STORE, float, false>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream);
         case EPI_HARD:
-            return a.rows_are_k ? launch_tn_t<EPI_HARD, float, true>(a, p, tmP, tmQ, grid, stream)
-                                : launch_tn_t<EPI_HARD, float, false>(a, p, tmP, tmQ, grid, stream);
+            return a.rows_are_k ? launch_tn_t<EPI_HARD, float, true>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream)
+                                : launch_tn_t<EPI_HARD, float, false>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream);
         case EPI_SOFT:
-            if (a.rows_are_k) return launch_tn_t<EPI_SOFT, float, true>(a, p, tmP, tmQ, grid, stream);
-            return a.logits_f16 ? launch_tn_t<EPI_SOFT, __half, false>(a, p, tmP, tmQ, grid, stream)
-                                : launch_tn_t<EPI_SOFT, float, false>(a, p, tmP, tmQ, grid, stream);
+            if (a.rows_are_k) return launch_tn_t<EPI_SOFT, float, true>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream);
+            return a.logits_f16 ? launch_tn_t<EPI_SOFT, __half, false>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream)
+                                : launch_tn_t<EPI_SOFT, float, false>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream);
     }
     set_last_error("tn_gemm: unknown epilogue %d", a.epi);
     return PLZ_ERR_UNSUPPORTED;

@@ -47,6 +47,16 @@ def linear_step(x, dy, palette, logits, noise, tau, lora=None, ste=True, packed=
     out["y"] = y
     if dy is None:
         return out
+    fused_lora = ste and lora is not None and ("da" in want or "db" in want) and ("dlogits" in want or "dpalette" in want)
+    if fused_lora:
+        # dt first, then the weight-gradient launch also produces dA and dB, then dX with the dt already there
+        dt = ops.lora_dt(lora, dy)
+        dlog, dpal, da, db = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=tau, seed=seed,
+                                                  want_dlogits="dlogits" in want, want_dpalette="dpalette" in want, lora_ws=(t, dt))
+        out.update(dlogits=dlog, dpalette=dpal, da=da, db=db)
+        if "dx" in want:
+            out["dx"] = ops.backward_dx_with_dt(w, dy, lora, dt)
+        return out
     if "dx" in want:
         dx, dt = ops.backward_dx(w, dy, lora) if ste else ops.dense_backward_dx(w_soft, dy, lora)
         out["dx"] = dx

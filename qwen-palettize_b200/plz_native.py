@@ -52,8 +52,11 @@ SIGNATURES = {
     "plz_soft_select": [_WP, _GP, _NP, _F, _I32, _P, _I64, _I64, _P],
     "plz_dense_fwd": [_P, _I64, _I32, _I32, _P, _I64, _I32, _LP, _P, _P, _I64, _P],
     "plz_bwd_dx": [_WP, _P, _I64, _I32, _LP, _P, _P, _I64, _P],
+    "plz_lora_dt": [_LP, _P, _I64, _I32, _I32, _P, _P],
+    "plz_bwd_dx_with_dt": [_WP, _P, _I64, _I32, _LP, _P, _P, _I64, _P],
     "plz_dense_bwd_dx": [_P, _I64, _I32, _I32, _P, _I64, _I32, _LP, _P, _P, _I64, _P],
     "plz_bwd_dw_soft": [_WP, _P, _I64, _P, _I64, _I32, _GP, _NP, _F, _P, _P, _P],
+    "plz_bwd_dw_soft_lora": [_WP, _P, _I64, _P, _I64, _I32, _GP, _NP, _F, _P, _P, _P, _P, _I32, _P, _P, _P],
     "plz_bwd_dw_hard": [_WP, _P, _I64, _P, _I64, _I32, _P, _P],
     "plz_lora_bwd": [_P, _I64, _P, _I64, _P, _P, _I32, _I32, _I32, _I32, _P, _P, _P],
     "plz_adamw_step": [_P, _P, _P, _P, _I32, _F, _I64, _F, _F, _F, _F, _F, _I32, _F, _F, _I32, _P, _I32, _P],

@@ -142,6 +142,29 @@ def backward_dx(w: PackedWeight, dy: torch.Tensor, lora=None):
     return dx, dt
 
 
+def lora_dt(lora, dy: torch.Tensor) -> torch.Tensor:
+    """dt = scale * dY B, bf16 [M, rank]."""
+    a, b, scale = lora
+    _mat(dy, b.shape[0])
+    d = P.lora_desc(a, b, scale)
+    dt = torch.empty(dy.shape[0], a.shape[0], dtype=torch.bfloat16, device=dy.device)
+    P.check(P.lib().plz_lora_dt(C.byref(d), dy.data_ptr(), dy.stride(0), dy.shape[0], b.shape[0], dt.data_ptr(), P.stream_ptr()),
+            "plz_lora_dt")
+    return dt
+
+
+def backward_dx_with_dt(w: PackedWeight, dy: torch.Tensor, lora, dt: torch.Tensor) -> torch.Tensor:
+    """dX = dY W + dt A with a precomputed dt."""
+    _mat(dy, w.N)
+    M = dy.shape[0]
+    dx = torch.empty(M, w.K, dtype=torch.bfloat16, device=dy.device)
+    ld = P.lora_desc(*lora)
+    d = w.desc()
+    P.check(P.lib().plz_bwd_dx_with_dt(C.byref(d), dy.data_ptr(), dy.stride(0), M, C.byref(ld), dt.data_ptr(), dx.data_ptr(),
+                                       dx.stride(0), P.stream_ptr()), "plz_bwd_dx_with_dt")
+    return dx
+
+
 def dense_backward_dx(wd: torch.Tensor, dy: torch.Tensor, lora=None):
     N, K = wd.shape
     _mat(dy, N), _mat(wd, K)
@@ -155,8 +178,9 @@ def dense_backward_dx(wd: torch.Tensor, dy: torch.Tensor, lora=None):
 
 
 def backward_dw_soft(w: PackedWeight, x: torch.Tensor, dy: torch.Tensor, logits: torch.Tensor, layout: str, noise=None,
-                     tau: float = 1.0, seed: int = 0, want_dlogits: bool = True, want_dpalette: bool = True):
-    """Returns (dLogits with the dtype/shape of `logits`, dPalette fp32 [groups, 4])."""
+                     tau: float = 1.0, seed: int = 0, want_dlogits: bool = True, want_dpalette: bool = True, lora_ws=None):
+    """Returns (dLogits with the dtype/shape of `logits`, dPalette fp32 [groups, 4]); with lora_ws = (t, dt), the workspaces
+    left by the forward and by backward_dx, also (dA fp32 [r, K], dB fp32 [N, r]) computed in the same launch."""
     _mat(x, w.K), _mat(dy, w.N)
     M = x.shape[0]
     ld, nd = P.logits_desc(logits, layout), P.noise_desc(noise, layout, seed)
@@ -165,6 +189,16 @@ def backward_dw_soft(w: PackedWeight, x: torch.Tensor, dy: torch.Tensor, logits:
         assert dlog.stride() == logits.stride()
     dpal = torch.zeros(w.palette.numel() // 4, 4, dtype=torch.float32, device=x.device) if want_dpalette else None
     d = w.desc()
+    if lora_ws is not None:
+        t, dt = lora_ws
+        r = t.shape[1]
+        da = torch.zeros(r, w.K, dtype=torch.float32, device=x.device)
+        db = torch.zeros(w.N, r, dtype=torch.float32, device=x.device)
+        P.check(P.lib().plz_bwd_dw_soft_lora(C.byref(d), x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), M, C.byref(ld),
+                                             C.byref(nd), float(tau), dlog.data_ptr() if dlog is not None else None,
+                                             dpal.data_ptr() if dpal is not None else None, t.data_ptr(), dt.data_ptr(), r,
+                                             da.data_ptr(), db.data_ptr(), P.stream_ptr()), "plz_bwd_dw_soft_lora")
+        return dlog, dpal, da, db
     P.check(P.lib().plz_bwd_dw_soft(C.byref(d), x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), M, C.byref(ld),
                                     C.byref(nd), float(tau), dlog.data_ptr() if dlog is not None else None,
                                     dpal.data_ptr() if dpal is not None else None, P.stream_ptr()), "plz_bwd_dw_soft")
