@@ -60,5 +60,25 @@ def build(force=False, verbose=False):
     return LIB
 
 
+def spill_report():
+    """{kernel name: (spill store bytes, spill load bytes, registers)} parsed from the ptxas log of the last build."""
+    import re
+    path = os.path.join(HERE, "build", "ptxas.log")
+    out, name = {}, None
+    if not os.path.exists(path):
+        return out
+    for line in open(path):
+        m = re.search(r"Compiling entry function '([^']+)'", line)
+        if m:
+            name = m.group(1)
+        m = re.search(r"(\d+) bytes spill stores, (\d+) bytes spill loads", line)
+        if m and name:
+            out[name] = [int(m.group(1)), int(m.group(2)), None]
+        m = re.search(r"Used (\d+) registers", line)
+        if m and name and name in out:
+            out[name][2] = int(m.group(1))
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

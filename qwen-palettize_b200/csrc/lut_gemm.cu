@@ -57,25 +57,29 @@ constexpr int kBN = 256;            // D columns per tile
 constexpr uint32_t kBBytes = kBN * kBK * 2;
 constexpr uint32_t kEpiStageBytes = 32 * 64 * 2;  // one 32-row x 64-column bf16 box per epilogue warp
 
-template <int MT>
+// NARROW: dense-B products whose output is at most 64 columns wide (the LoRA projections). Their B stage shrinks to
+// one 64 x 64 box, which leaves room for eight stages: these products are bound by streaming A, i.e. by bytes in flight.
+template <int MT, bool NARROW>
 struct Cfg {
-    static constexpr int STAGES = (MT == 2) ? 3 : 4;
+    static constexpr int STAGES = NARROW ? 8 : ((MT == 2) ? 3 : 4);
     static constexpr uint32_t A_BYTES = MT * 128 * kBK * 2;
-    static constexpr uint32_t STAGE_BYTES = A_BYTES + kBBytes;
+    static constexpr uint32_t B_BYTES = NARROW ? 64 * kBK * 2 : kBBytes;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TMEM_COLS = MT * 256;
     static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES;
     static constexpr uint32_t BAR_OFF = EPI_OFF + kEpiWarps * kEpiStageBytes;
     static constexpr uint32_t SMEM_BYTES = BAR_OFF + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int MT, int BMODE>
+template <int MT, int BMODE, bool NARROW>
 __global__ void __launch_bounds__(kThreads, 1)
 lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                 const __grid_constant__ CUtensorMap tmD, const LutGemmParams p) {
-    using C = Cfg<MT>;
+    using C = Cfg<MT, NARROW>;
     constexpr bool kDecode = (BMODE == B_DECODE_K || BMODE == B_DECODE_MN);
     constexpr bool kBMn = (BMODE == B_DECODE_MN || BMODE == B_TMA_MN);
+    constexpr int kIssuers = NARROW ? 4 : 1;  // MMA-issuing warps (see the MMA role below)
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -102,7 +106,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             mbar_init(full_b(s), kDecodeWarps);
             mbar_init(empty(s), 1);
         }
-        mbar_init(accum_full, 1);
+        mbar_init(accum_full, kIssuers);
         mbar_init(tmem_empty, kEpiWarps);
         *abort_flag = 0;
         mbar_fence_init();
@@ -155,7 +159,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const uint32_t sA = base + s * C::STAGE_BYTES;
                     const uint32_t sB = sA + C::A_BYTES;
                     const bool extra = it >= nkb;
-                    const uint32_t bytes = nmt * 16384u + ((extra || !kDecode) ? kBBytes : 0u);
+                    const uint32_t bytes = nmt * 16384u + ((extra || !kDecode) ? C::B_BYTES : 0u);
                     mbar_arrive_expect_tx(full_a(s), bytes);
                     const CUtensorMap* ma = extra ? &tmA2 : &tmA;
                     const CUtensorMap* mb = extra ? &tmB2 : &tmB;
@@ -166,7 +170,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (extra || !kDecode) {
                         if (kBMn) {
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) tma_load_2d(sB + q * 8192u, mb, full_a(s), j0 + q * 64, r0);
+                            for (int q = 0; q < (NARROW ? 1 : 4); ++q) tma_load_2d(sB + q * 8192u, mb, full_a(s), j0 + q * 64, r0);
                         } else {
                             tma_load_2d(sB, mb, full_a(s), r0, j0);
                         }
@@ -189,8 +193,12 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------- MMA issuer
+    } else if (warp == 1 || (kIssuers > 1 && warp < 1 + kIssuers)) {
+        // ------------------------------------------------------------- MMA issuer(s)
+        // A narrow tcgen05.mma (N <= 64) retires in a few tens of cycles but costs its issuing thread several times
+        // that, so for the rank-16/32 products four warps issue in parallel: issuer q takes the blocks q, q + 4, ...
+        // and accumulates into its own 64 TMEM columns; the epilogue adds the four partial tiles.
+        const int q = warp - 1;
         if (lane == 0) {
             const uint32_t idesc_main = make_idesc(128, p.mma_n, 0, kBMn ? 1 : 0);
             bool ok = true;
@@ -209,6 +217,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     tc_fence_after_sync();
                 }
                 for (int it = 0; it < nkb_total; ++it, ++git) {
+                    if (kIssuers > 1 && (it % kIssuers) != q) continue;
                     const int s = git % C::STAGES;
                     const uint32_t ph = (git / C::STAGES) & 1;
                     const bool extra = it >= nkb;
@@ -230,20 +239,21 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         for (int mt = 0; mt < MT; ++mt) {
                             if (mt >= nmt) break;
                             const uint64_t adesc = make_sdesc(sA + mt * 16384u + ks * 32u, 16u, 1024u);
-                            umma_bf16(tmem_base + mt * 256u, adesc, bdesc, idesc_main, (it > 0 || ks > 0) ? 1u : 0u);
+                            umma_bf16(tmem_base + mt * 256u + (kIssuers > 1 ? q * 64u : 0u), adesc, bdesc, idesc_main,
+                                      (it >= kIssuers || ks > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(empty(s));
                 }
                 if (ok) umma_commit(accum_full);
             }
-            if (p.prof) {
+            if (p.prof && q == 0) {
                 unsigned long long* q = p.prof + 8ull * blockIdx.x;
                 q[0] = wait_a; q[1] = wait_b; q[2] = wait_t; q[3] = clock64() - t_begin; q[4] = lt;
             }
         }
     } else if (warp < kFirstEpiWarp) {
-        // ------------------------------------------------------------- decode warps
+        // ------------------------------------------------------------- decode warps (idle in the dense-B modes)
         if (kDecode) {
             // Each of the 512 decode threads produces 32 weights (four 16-byte chunks of one 128-byte operand row)
             // per stage from 8 bytes of packed indices.
@@ -357,6 +367,20 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int c = 0; c < 2; ++c) {
                         uint32_t v[32];
                         tmem_ld_32x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + mt * 256u + col + c * 32, v);
+                        if (NARROW && col == 0) {
+                            // the four issuers' partial tiles sit 64 columns apart
+                            const int used = nkb_total < kIssuers ? nkb_total : kIssuers;
+                            for (int qq = 1; qq < used; ++qq) {
+#pragma unroll
+                                for (int hh = 0; hh < 2; ++hh) {
+                                    uint32_t u[16];
+                                    tmem_ld_32x16(tmem_base + ((uint32_t)(lane_group * 32) << 16) + qq * 64u + c * 32 + hh * 16, u);
+#pragma unroll
+                                    for (int i = 0; i < 16; ++i)
+                                        v[hh * 16 + i] = __float_as_uint(__uint_as_float(v[hh * 16 + i]) + __uint_as_float(u[i]));
+                                }
+                            }
+                        }
                         if (mt == nmt - 1 && b == 1 && c == 1) {
                             // last read of this tile's accumulators: hand TMEM back to the MMA warp
                             tc_fence_before_sync();
@@ -396,16 +420,16 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // host side
 // ---------------------------------------------------------------------------------------------
 
-template <int MT, int BMODE>
+template <int MT, int BMODE, bool NARROW>
 static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
-    using C = Cfg<MT>;
+    using C = Cfg<MT, NARROW>;
     CUtensorMap tmA, tmB, tmA2, tmB2, tmD;
     int rc;
     if ((rc = make_tmap_bf16(&tmA, a.A, a.M, a.R, a.lda, 64, 128))) return rc;
     tmB = tmA; tmA2 = tmA; tmB2 = tmA;
     constexpr bool kMn = (BMODE == B_DECODE_MN || BMODE == B_TMA_MN);
     if (BMODE == B_TMA_K) {
-        if ((rc = make_tmap_bf16(&tmB, a.Bdense, a.J, a.R, a.ldb, 64, 256))) return rc;
+        if ((rc = make_tmap_bf16(&tmB, a.Bdense, a.J, a.R, a.ldb, 64, NARROW ? 64 : 256))) return rc;
     } else if (BMODE == B_TMA_MN) {
         if ((rc = make_tmap_bf16(&tmB, a.Bdense, a.R, a.J, a.ldb, 64, 64))) return rc;
     }
@@ -432,7 +456,7 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
     p.alpha = a.alpha;
     p.status = device_status_ptr();
     p.prof = (unsigned long long*)a.prof;
-    auto kern = lut_gemm_kernel<MT, BMODE>;
+    auto kern = lut_gemm_kernel<MT, BMODE, NARROW>;
     static bool attr_set[64] = {};
     int dev = 0, sms = 0;
     PLZ_CUDA_CHECK(cudaGetDevice(&dev));
@@ -471,11 +495,16 @@ int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream) {
     }
     // narrow outputs (the rank-16/32 LoRA products) are bound by streaming A: 128-row tiles give twice the CTAs
     const bool big = a.M > 128 && a.J > 64;
+    const bool narrow = !decode && a.J <= 64 && a.r2 == 0;
     switch (a.bmode) {
-        case B_DECODE_K: return big ? launch_t<2, B_DECODE_K>(a, stream) : launch_t<1, B_DECODE_K>(a, stream);
-        case B_DECODE_MN: return big ? launch_t<2, B_DECODE_MN>(a, stream) : launch_t<1, B_DECODE_MN>(a, stream);
-        case B_TMA_K: return big ? launch_t<2, B_TMA_K>(a, stream) : launch_t<1, B_TMA_K>(a, stream);
-        case B_TMA_MN: return big ? launch_t<2, B_TMA_MN>(a, stream) : launch_t<1, B_TMA_MN>(a, stream);
+        case B_DECODE_K: return big ? launch_t<2, B_DECODE_K, false>(a, stream) : launch_t<1, B_DECODE_K, false>(a, stream);
+        case B_DECODE_MN: return big ? launch_t<2, B_DECODE_MN, false>(a, stream) : launch_t<1, B_DECODE_MN, false>(a, stream);
+        case B_TMA_K:
+            if (narrow) return launch_t<1, B_TMA_K, true>(a, stream);
+            return big ? launch_t<2, B_TMA_K, false>(a, stream) : launch_t<1, B_TMA_K, false>(a, stream);
+        case B_TMA_MN:
+            if (narrow) return launch_t<1, B_TMA_MN, true>(a, stream);
+            return big ? launch_t<2, B_TMA_MN, false>(a, stream) : launch_t<1, B_TMA_MN, false>(a, stream);
     }
     set_last_error("lut_gemm: unknown B mode %d", a.bmode);
     return PLZ_ERR_UNSUPPORTED;
