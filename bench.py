@@ -25,6 +25,7 @@ M_TOK, N_OUT, K_IN, RANK, TAU = 16384, 9728, 2560, 16, 1.0
 METRIC = "fwd+bwd tokens/s, Qwen-4B-shaped PalettizedLinear (soft forward + full backward + LoRA r16)"
 WORKLOAD = "configs[1]: one Linear N=9728 K=2560, M=32x512=16384 tokens per GPU, soft fwd (STE) + full bwd, LoRA r16, tau=1"
 GEMM_FLOPS = 2.0 * M_TOK * N_OUT * K_IN  # one of the three products
+COMM_SMS = 20  # SMs left free for NCCL during the dX product when the gradient exchange is in flight (N > 1)
 
 
 def peaks():
@@ -136,6 +137,8 @@ def run_ours(args):
     import plz_ops as ops
     import synth
 
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)  # anything a library prints (NCCL's version banner) goes to stderr; the JSON line gets stdout back
     rank, world, local = dist_setup(args.gpus)
     dev = torch.device("cuda", local if world > 1 else 0)
     d = synth.make_linear_inputs_cuda(M_TOK, N_OUT, K_IN, seed=rank, rank=RANK, device=dev)
@@ -149,6 +152,7 @@ def run_ours(args):
     packed = ops.empty_packed(N_OUT, K_IN, dev)
     w = ops.PackedWeight(packed, palette, N_OUT, K_IN, 1, 256)
     exch = dp.GradExchange()
+    sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
     phases = ["select", "fwd", "lora_dt", "dw", "dx"]
     ev = {p: [] for p in phases}
 
@@ -164,7 +168,11 @@ def run_ours(args):
         dlog, dpal, da, db = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=TAU, lora_ws=(t, dt))
         if record: marks[4].record()
         h1 = exch.start([dlog, dpal, da, db])                     # overlaps the dX GEMM below (N > 1 only)
+        if world > 1:
+            plz_native.lib().plz_set_cta_limit(sm_count - COMM_SMS)  # leave SMs to NCCL while the exchange runs
         dx = ops.backward_dx_with_dt(w, dy, lora, dt)             # LUT GEMM (+ LoRA block)
+        if world > 1:
+            plz_native.lib().plz_set_cta_limit(0)
         if record: marks[5].record()
         exch.finish(h1)
         if record:
@@ -304,7 +312,9 @@ def run_ours(args):
     }
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
-    print(json.dumps(line))
+    sys.stdout.flush()
+    os.dup2(saved_stdout, 1)
+    print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -84,6 +84,12 @@ const char* plz_last_error(void);
  * array `out4` (may be NULL) and clears it. Returns PLZ_ERR_DEVICE_WAIT if a kernel gave up. */
 int32_t plz_device_status(uint32_t* out4);
 
+/* The GEMM kernels are persistent: one CTA per SM, holding most of its shared memory for the whole launch, so nothing
+ * else can run beside them. plz_set_cta_limit(n) makes later launches use at most n CTAs (0 = all SMs again), which
+ * leaves the other SMs to a communication library: set it around the dX product while the gradient all-reduce of the
+ * same Linear is in flight. Process-wide. (No counterpart in the reference, which is single-GPU.) */
+int32_t plz_set_cta_limit(int32_t n);
+
 /* ---- formats ---------------------------------------------------------------------------------
  * Pack unpacked int8/uint8 indices, element (n, k) at src[n * s_n + k * s_k], into `dst`.
  * Replaces pack_indices_2bit (scripts/palettize_core.py:31-42) as a device kernel; the reference

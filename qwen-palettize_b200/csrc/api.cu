@@ -142,6 +142,7 @@ void plz_debug_set_profile_buffer(void* dev_ptr) { g_prof_buffer = dev_ptr; }
 // Diagnostics: run the persistent kernels on at most `n` CTAs (0 = one per SM), so that small test problems
 // exercise the multi-tile schedule. Not part of the ABI.
 void plz_debug_set_sm_limit(int n) { g_debug_sm_limit = n; }
+int32_t plz_set_cta_limit(int32_t n) { g_debug_sm_limit = n > 0 ? n : 0; return PLZ_OK; }
 
 int32_t plz_version(void) { return 100; }
 const char* plz_last_error(void) { return g_err; }
