@@ -188,6 +188,23 @@ int32_t plz_bwd_dw_hard(const plz_weight_t* w, const void* x, int64_t ldx, const
 int32_t plz_lora_bwd(const void* x, int64_t ldx, const void* dY, int64_t lddy, const void* t, const void* dt,
                      int32_t M, int32_t N, int32_t K, int32_t rank, float* dA, float* dB, void* stream);
 
+/* ---- the ops around the Linears of a decoder layer, folded into the hard forward -------------------------
+ * The reference has no code for these: it calls the HuggingFace decoder layer (scripts/train_qwen.py:1259-1266), whose
+ * RMSNorm, SwiGLU and Linears are separate eager ops; the fusions were only planned there
+ * (agent-ctx/agent-layer-fusion/TASKS.md). Semantics follow transformers' Qwen3RMSNorm / Qwen3MLP:
+ *   rmsnorm(x)[m, k] = x[m, k] * rstd[m] * g[k],  rstd[m] = 1 / sqrt(mean_k x[m, k]^2 + eps);   mlp = down(silu(gate(h)) * up(h)).
+ * plz_rms_rstd writes rstd (fp32 [M]).
+ * plz_hard_fwd_norm: y = rmsnorm(x) W^T without materialising rmsnorm(x): g[k] is multiplied into the decoded weight tile
+ *   (one bf16 rounding of W*g), rstd[m] scales the accumulator row in the epilogue. Either factor may be NULL.
+ * plz_mlp_gate_up_fwd: act[M, N] = silu(h Wg^T) * (h Wu^T) with h = rmsnorm(x) (factors optional as above): one launch, the
+ *   gate and up tiles share the x tiles and sit side by side in TMEM, the epilogue applies SwiGLU; the two [M, N]
+ *   intermediates never reach HBM. Wg, Wu: same shape / grouping / pitch, N % 128 == 0. */
+int32_t plz_rms_rstd(const void* x, int64_t ldx, int32_t M, int32_t K, float eps, float* rstd, void* stream);
+int32_t plz_hard_fwd_norm(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const float* row_scale,
+                          const void* col_scale, void* y, int64_t ldy, void* stream);
+int32_t plz_mlp_gate_up_fwd(const plz_weight_t* w_gate, const plz_weight_t* w_up, const void* x, int64_t ldx, int32_t M,
+                            const float* row_scale, const void* col_scale, void* act, int64_t ldact, void* stream);
+
 /* ---- the steps around the Linear in the distillation loop ------------------------------------
  * One fused pass of fp32-master AdamW over a flat parameter of n elements:
  *   g = grad * grad_scale (grad_scale carries the gradient-clipping coefficient and 1/world_size);

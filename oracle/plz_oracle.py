@@ -316,3 +316,24 @@ def read_idx2(data: bytes, out_dim: int, in_dim: int) -> np.ndarray:
 
 def read_lut_scalar(data: bytes) -> np.ndarray:
     return np.frombuffer(data, dtype=np.float16).astype(np.float32)
+
+
+# --------------------------------------------------------------------------------------------
+# decoder-layer ops around the Linears (no reference code: the reference calls transformers' Qwen3 modules,
+# scripts/train_qwen.py:1259-1266; these follow Qwen3RMSNorm / Qwen3MLP of transformers 5.5)
+# --------------------------------------------------------------------------------------------
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float = 1e-6) -> torch.Tensor:
+    """fp32 result of x * rsqrt(mean(x^2) + eps) * weight."""
+    xf = x.float()
+    h = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return h if weight is None else h * weight.float()
+
+
+def mlp_gate_up(x: torch.Tensor, w_gate_nk: torch.Tensor, w_up_nk: torch.Tensor, norm_weight=None, eps: float = 1e-6,
+                normalize: bool = True) -> torch.Tensor:
+    """silu(h Wg^T) * (h Wu^T) in fp32, h = rmsnorm(x) if normalize else x."""
+    h = rmsnorm(x, norm_weight, eps) if normalize else x.float()
+    g = h @ w_gate_nk.float().t()
+    u = h @ w_up_nk.float().t()
+    return torch.nn.functional.silu(g) * u

@@ -480,6 +480,51 @@ int32_t plz_lora_bwd(const void* x, int64_t ldx, const void* dY, int64_t lddy, c
     return PLZ_OK;
 }
 
+int32_t plz_rms_rstd(const void* x, int64_t ldx, int32_t M, int32_t K, float eps, float* rstd, void* stream) {
+    if (M < 0 || K <= 0 || (K & 1)) { set_last_error("rms_rstd: K must be even and positive"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !rstd) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)x & 3) || (ldx & 1)) { set_last_error("rms_rstd: rows must be 4-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    return launch_rms_rstd(x, ldx, M, K, eps, rstd, (cudaStream_t)stream);
+}
+
+static int fused_fwd(int fuse, const plz_weight_t* w, const plz_weight_t* w2, const void* x, int64_t ldx, int32_t M,
+                     const float* row_scale, const void* col_scale, void* out, int64_t ldo, void* stream) {
+    int rc = check_weight(w, true);
+    if (rc) return rc;
+    if (fuse == 1) {
+        if ((rc = check_weight(w2, true))) return rc;
+        if (w2->N != w->N || w2->K != w->K || w2->gs_n != w->gs_n || w2->gs_k != w->gs_k || w2->packed_pitch != w->packed_pitch) {
+            set_last_error("gate and up projections must have the same shape, grouping and packed pitch");
+            return PLZ_ERR_BAD_SHAPE;
+        }
+        if (w->N % 128) { set_last_error("the fused gate/up forward needs N %% 128 == 0 (N=%d)", w->N); return PLZ_ERR_BAD_SHAPE; }
+    }
+    if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !out) { set_last_error("null activation pointer"); return PLZ_ERR_NULL; }
+    if (col_scale && ((uintptr_t)col_scale & 15)) { set_last_error("norm weight must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    LutGemmArgs g = {};
+    g.bmode = B_DECODE_K; g.M = M; g.J = (fuse == 1) ? 2 * w->N : w->N; g.R = w->K;
+    g.A = x; g.lda = ldx;
+    g.packed = w->packed; g.packed_pitch = w->packed_pitch; g.palette = w->palette;
+    g.gs_n = w->gs_n; g.gs_k = w->gs_k; g.Wn = w->N; g.Wk = w->K;
+    g.fuse = fuse; g.col_scale = col_scale; g.row_scale = row_scale;
+    if (fuse == 1) { g.packed2 = w2->packed; g.palette2 = w2->palette; }
+    g.out = out; g.ld_out = ldo; g.alpha = 1.0f;
+    return launch_lut_gemm(g, (cudaStream_t)stream);
+}
+
+int32_t plz_hard_fwd_norm(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const float* row_scale,
+                          const void* col_scale, void* y, int64_t ldy, void* stream) {
+    return fused_fwd(2, w, nullptr, x, ldx, M, row_scale, col_scale, y, ldy, stream);
+}
+
+int32_t plz_mlp_gate_up_fwd(const plz_weight_t* w_gate, const plz_weight_t* w_up, const void* x, int64_t ldx, int32_t M,
+                            const float* row_scale, const void* col_scale, void* act, int64_t ldact, void* stream) {
+    return fused_fwd(1, w_gate, w_up, x, ldx, M, row_scale, col_scale, act, ldact, stream);
+}
+
 int32_t plz_adamw_step(float* master, float* m, float* v, const void* grad, int32_t grad_dtype, float grad_scale, int64_t n,
                        float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step, float clamp_lo,
                        float clamp_hi, int32_t clamp_master, void* param, int32_t param_dtype, void* stream) {

@@ -43,6 +43,10 @@ struct LutGemmParams {
     int gs_n_shift;      // log2(gs_n) when gs_n is a power of two, else -1
     int Wn, Wk;          // weight matrix extents (N, K)
     float alpha;
+    // fused MLP front end (FUSE != 0): optional RMSNorm factors and, for FUSE == 1, a second weight matrix
+    const uint8_t* packed2; const __nv_bfloat16* palette2;  // "up" projection, same shape and grouping as the first
+    const __nv_bfloat16* col_scale;  // [K]: norm weight g[k], multiplied into the decoded weights (may be null)
+    const float* row_scale;          // [M]: 1 / rms(x[m, :]), applied to the accumulator rows (may be null)
     StatusWord* status;
     unsigned long long* prof;  // optional [gridDim][8] cycle counters of the MMA thread (diagnostics)
 };
@@ -71,7 +75,7 @@ struct Cfg {
     static constexpr uint32_t SMEM_BYTES = BAR_OFF + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int MT, int BMODE, bool NARROW>
+template <int MT, int BMODE, bool NARROW, int FUSE>
 __global__ void __launch_bounds__(kThreads, 1)
 lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
@@ -273,16 +277,20 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 int m0, j0, nmt;
                 tile_origin(tile, m0, j0, nmt);
                 const int k_fixed = j0 + a * 64 + h * 32;  // backward only
-                auto src_n = [&](int it) { return (BMODE == B_DECODE_K) ? (j0 + rr) : (it * kBK + rr); };
+                // FUSE == 1: the 256 tile rows are 128 rows of the gate matrix followed by the same 128 rows of the up matrix
+                const int n_fused = (j0 >> 1) + (rr & 127);
+                const uint8_t* packed_src = (FUSE == 1 && rr >= 128) ? p.packed2 : p.packed;
+                const __nv_bfloat16* palette_src = (FUSE == 1 && rr >= 128) ? p.palette2 : p.palette;
+                auto src_n = [&](int it) { return (BMODE == B_DECODE_K) ? (FUSE == 1 ? n_fused : (j0 + rr)) : (it * kBK + rr); };
                 auto src_k = [&](int it) { return (BMODE == B_DECODE_K) ? (it * kBK + h * 32) : k_fixed; };
                 auto in_range = [&](int it) { return it < nkb && src_n(it) < p.Wn && src_k(it) < p.Wk; };
                 auto load_idx = [&](int it) -> uint2 {
                     if (!in_range(it)) return make_uint2(0, 0);
-                    return __ldg(reinterpret_cast<const uint2*>(p.packed + (long long)src_n(it) * p.packed_pitch +
+                    return __ldg(reinterpret_cast<const uint2*>(packed_src + (long long)src_n(it) * p.packed_pitch +
                                                                 (src_k(it) >> 2)));
                 };
                 // palette group of the stage: one of (n / gs_n, k / gs_k) is fixed per thread, the other advances
-                const int ng_fixed = (BMODE == B_DECODE_K) ? ((j0 + rr) / p.gs_n) : 0;
+                const int ng_fixed = (BMODE == B_DECODE_K) ? ((FUSE == 1 ? n_fused : (j0 + rr)) / p.gs_n) : 0;
                 const int kg_fixed = (BMODE == B_DECODE_K) ? 0 : (k_fixed / p.gs_k);
                 // kg = k group of stage `it` (forward only), carried incrementally to keep divisions out of the loop
                 auto load_pal = [&](int it, int kg) -> uint2 {
@@ -290,7 +298,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     long long g;
                     if (BMODE == B_DECODE_K) g = (long long)ng_fixed * p.n_kgroups + kg;
                     else g = (long long)((p.gs_n_shift >= 0) ? ((it * kBK + rr) >> p.gs_n_shift) : ((it * kBK + rr) / p.gs_n)) * p.n_kgroups + kg_fixed;
-                    return __ldg(reinterpret_cast<const uint2*>(p.palette + g * 4));
+                    return __ldg(reinterpret_cast<const uint2*>(palette_src + g * 4));
                 };
                 int pf_kg = 0, pf_cnt = 0;  // k group and position inside it of the next stage to prefetch
                 auto advance_kg = [&]() { if (++pf_cnt == blocks_per_kgroup) { pf_cnt = 0; ++pf_kg; } };
@@ -327,6 +335,18 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int i = 0; i < 2; ++i) {
                         uint32_t o[8];
                         decode16(w[i], pal, o);
+                        if (FUSE != 0 && p.col_scale != nullptr) {
+                            // RMSNorm weight folded into the operand: W[n, k] * g[k] (one bf16 rounding)
+                            const uint4* gp = reinterpret_cast<const uint4*>(p.col_scale + it * kBK + h * 32 + i * 16);
+                            const uint4 g0 = __ldg(gp), g1 = __ldg(gp + 1);
+                            const uint32_t gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&o[j]),
+                                                                    *reinterpret_cast<const __nv_bfloat162*>(&gg[j]));
+                                o[j] = *reinterpret_cast<const uint32_t*>(&prod);
+                            }
+                        }
                         // word i covers 16 elements = 16-byte chunks 4h + 2i and 4h + 2i + 1 of the 128-byte row
                         *reinterpret_cast<uint4*>(row + (((4 * h + 2 * i) ^ (rr & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                         *reinterpret_cast<uint4*>(row + (((4 * h + 2 * i + 1) ^ (rr & 7)) << 4)) =
@@ -355,8 +375,55 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             ok = mbar_wait(accum_full, lt & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 4);
             if (!ok) break;
             tc_fence_after_sync();
+            if (FUSE == 1) {
+                // SwiGLU: accumulator columns [0,128) hold the gate product, [128,256) the up product of the same 128
+                // output columns; this warp writes out[:, n0 + 64*col_half .. +64) = silu(s*gate) * (s*up).
+                const int n0 = j0 >> 1;
+#pragma unroll 1
+                for (int mt = 0; mt < nmt; ++mt) {
+                    const int m = m0 + mt * 128 + lane_group * 32 + lane;
+                    const float rs = (p.row_scale != nullptr && m < p.M) ? __ldg(p.row_scale + m) : 1.0f;
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t vg[16], vu[16];
+                        const uint32_t ta = tmem_base + ((uint32_t)(lane_group * 32) << 16) + mt * 256u + col_half * 64 + c * 16;
+                        tmem_ld_32x16(ta, vg);
+                        tmem_ld_32x16(ta + 128u, vu);
+                        if (mt == nmt - 1 && c == 3) {
+                            tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(tmem_empty);
+                        }
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float a0 = __uint_as_float(vg[2 * i]) * rs, a1 = __uint_as_float(vg[2 * i + 1]) * rs;
+                            a0 = __fdividef(a0, 1.0f + __expf(-a0));
+                            a1 = __fdividef(a1, 1.0f + __expf(-a1));
+                            o[i] = pack_bf16x2(a0 * (__uint_as_float(vu[2 * i]) * rs), a1 * (__uint_as_float(vu[2 * i + 1]) * rs));
+                        }
+                        *reinterpret_cast<uint4*>(stage + swz128(lane, c * 2)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4*>(stage + swz128(lane, c * 2 + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && n0 + col_half * 64 < p.J && m0 + mt * 128 + lane_group * 32 < p.M) {
+                        tma_store_2d(&tmD, stage_u32, n0 + col_half * 64, m0 + mt * 128 + lane_group * 32);
+                        tma_store_commit();
+                    }
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int mt = 0; mt < nmt; ++mt) {
+                float rs = 1.0f;
+                if (FUSE == 2 && p.row_scale != nullptr) {
+                    const int m = m0 + mt * 128 + lane_group * 32 + lane;
+                    if (m < p.M) rs = __ldg(p.row_scale + m);
+                }
+                const float scale = p.alpha * rs;
 #pragma unroll 1
                 for (int b = 0; b < 2; ++b) {
                     const int col = col_half * 128 + b * 64;
@@ -390,10 +457,10 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
                             uint4 o;
-                            o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * p.alpha, __uint_as_float(v[g * 8 + 1]) * p.alpha);
-                            o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * p.alpha, __uint_as_float(v[g * 8 + 3]) * p.alpha);
-                            o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * p.alpha, __uint_as_float(v[g * 8 + 5]) * p.alpha);
-                            o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * p.alpha, __uint_as_float(v[g * 8 + 7]) * p.alpha);
+                            o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * scale, __uint_as_float(v[g * 8 + 1]) * scale);
+                            o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * scale, __uint_as_float(v[g * 8 + 3]) * scale);
+                            o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * scale, __uint_as_float(v[g * 8 + 5]) * scale);
+                            o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * scale, __uint_as_float(v[g * 8 + 7]) * scale);
                             *reinterpret_cast<uint4*>(stage + swz128(lane, c * 4 + g)) = o;
                         }
                     }
@@ -420,7 +487,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // host side
 // ---------------------------------------------------------------------------------------------
 
-template <int MT, int BMODE, bool NARROW>
+template <int MT, int BMODE, bool NARROW, int FUSE = 0>
 static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
     using C = Cfg<MT, NARROW>;
     CUtensorMap tmA, tmB, tmA2, tmB2, tmD;
@@ -441,9 +508,10 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
             if ((rc = make_tmap_bf16(&tmB2, a.B2, a.J, a.r2, a.ldb2, 64, 256))) return rc;
         }
     }
-    if ((rc = make_tmap_bf16(&tmD, a.out, a.M, a.J, a.ld_out, 64, 32))) return rc;
+    const int out_cols = (FUSE == 1) ? a.J / 2 : a.J;  // the SwiGLU form writes one column per gate/up pair
+    if ((rc = make_tmap_bf16(&tmD, a.out, a.M, out_cols, a.ld_out, 64, 32))) return rc;
     LutGemmParams p;
-    p.M = a.M; p.J = a.J; p.R = a.R; p.n_extra = a.r2 > 0 ? 1 : 0;
+    p.M = a.M; p.J = out_cols; p.R = a.R; p.n_extra = a.r2 > 0 ? 1 : 0;
     p.tiles_j = (a.J + kBN - 1) / kBN;
     p.tiles_m = (a.M + 128 * MT - 1) / (128 * MT);
     p.packed = (const uint8_t*)a.packed; p.packed_pitch = a.packed_pitch;
@@ -454,9 +522,11 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
     for (int sh = 0; sh < 31; ++sh) if ((1 << sh) == p.gs_n) p.gs_n_shift = sh;
     p.Wn = a.Wn; p.Wk = a.Wk;
     p.alpha = a.alpha;
+    p.packed2 = (const uint8_t*)a.packed2; p.palette2 = (const __nv_bfloat16*)a.palette2;
+    p.col_scale = (const __nv_bfloat16*)a.col_scale; p.row_scale = a.row_scale;
     p.status = device_status_ptr();
     p.prof = (unsigned long long*)a.prof;
-    auto kern = lut_gemm_kernel<MT, BMODE, NARROW>;
+    auto kern = lut_gemm_kernel<MT, BMODE, NARROW, FUSE>;
     static bool attr_set[64] = {};
     int dev = 0, sms = 0;
     PLZ_CUDA_CHECK(cudaGetDevice(&dev));
@@ -497,7 +567,10 @@ int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream) {
     const bool big = a.M > 128 && a.J > 64;
     const bool narrow = !decode && a.J <= 64 && a.r2 == 0;
     switch (a.bmode) {
-        case B_DECODE_K: return big ? launch_t<2, B_DECODE_K, false>(a, stream) : launch_t<1, B_DECODE_K, false>(a, stream);
+        case B_DECODE_K:
+            if (a.fuse == 1) return big ? launch_t<2, B_DECODE_K, false, 1>(a, stream) : launch_t<1, B_DECODE_K, false, 1>(a, stream);
+            if (a.fuse == 2) return big ? launch_t<2, B_DECODE_K, false, 2>(a, stream) : launch_t<1, B_DECODE_K, false, 2>(a, stream);
+            return big ? launch_t<2, B_DECODE_K, false>(a, stream) : launch_t<1, B_DECODE_K, false>(a, stream);
         case B_DECODE_MN: return big ? launch_t<2, B_DECODE_MN, false>(a, stream) : launch_t<1, B_DECODE_MN, false>(a, stream);
         case B_TMA_K:
             if (narrow) return launch_t<1, B_TMA_K, true>(a, stream);

@@ -18,6 +18,9 @@ struct LutGemmArgs {
     // optional extra block: A2 [M, r2] (pitch lda2); B2: K-major modes [J, r2], MN-major modes [r2, J]
     int r2; const void* A2; long long lda2; const void* B2; long long ldb2;
     void* out; long long ld_out; float alpha;
+    // fused MLP front end (forward decode mode only): fuse 1 = gate/up pair + SwiGLU (J = 2 N), 2 = one matrix;
+    // col_scale bf16 [K] and row_scale fp32 [M] are the RMSNorm factors (either may be null)
+    int fuse; const void* packed2; const void* palette2; const void* col_scale; const float* row_scale;
     int sm_limit;  // > 0: use at most this many CTAs (tests of the multi-tile schedule)
     void* prof;  // optional device buffer of cycle counters, 8 x uint64 per CTA (diagnostics)
 };
@@ -89,6 +92,7 @@ struct AdamParams {
 };
 
 int launch_adamw(const AdamParams& p, int grad_dtype, int param_dtype, cudaStream_t stream);
+int launch_rms_rstd(const void* x, long long ldx, int M, int K, float eps, float* rstd, cudaStream_t stream);
 int launch_distill_loss(const void* s, long long lds, const void* t, long long ldt, int M, int H, float eps, float w_cos,
                         float w_mse, float upstream, float* ws, float* out4, void* ds, long long ldds, int ds_dtype,
                         cudaStream_t stream);

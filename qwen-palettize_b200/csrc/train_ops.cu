@@ -162,4 +162,32 @@ int launch_distill_loss(const void* s, long long lds, const void* t, long long l
     return PLZ_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// rstd[m] = 1 / sqrt(mean_k x[m, k]^2 + eps): the per-row factor of RMSNorm. The normalisation itself is folded into
+// the GEMM that consumes x (row factor in its epilogue, norm weight in its decoded operand).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+rms_rstd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int M, int K, float eps, float* __restrict__ rstd) {
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    for (int row = blockIdx.x * 8 + wib; row < M; row += gridDim.x * 8) {
+        const __nv_bfloat16* xr = x + (long long)row * ldx;
+        float s2 = 0.f;
+        for (int c = lane * 2; c < K; c += 64) {
+            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + c));
+            s2 += v.x * v.x + v.y * v.y;
+        }
+        s2 = warp_sum_f(s2);
+        if (lane == 0) rstd[row] = rsqrtf(s2 / (float)K + eps);
+    }
+}
+
+int launch_rms_rstd(const void* x, long long ldx, int M, int K, float eps, float* rstd, cudaStream_t stream) {
+    if (M <= 0) return PLZ_OK;
+    int blocks = (M + 7) / 8;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    rms_rstd_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, M, K, eps, rstd);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
 }  // namespace plz

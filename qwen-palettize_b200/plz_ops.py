@@ -260,3 +260,37 @@ def distill_loss(s: torch.Tensor, t: torch.Tensor, w_cos: float = 0.5, w_mse: fl
                                      float(upstream), ws.data_ptr(), out4.data_ptr(), ds.data_ptr() if ds is not None else None,
                                      H, _DT[grad_dtype], P.stream_ptr()), "plz_distill_loss")
     return out4, (ds.reshape(s.shape) if ds is not None else None)
+
+
+def rms_rstd(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """fp32 [M]: 1 / sqrt(mean(x^2, -1) + eps)."""
+    _mat(x, x.shape[1])
+    out = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+    P.check(P.lib().plz_rms_rstd(x.data_ptr(), x.stride(0), x.shape[0], x.shape[1], float(eps), out.data_ptr(), P.stream_ptr()),
+            "plz_rms_rstd")
+    return out
+
+
+def hard_forward_norm(w: PackedWeight, x: torch.Tensor, rstd: torch.Tensor | None, norm_weight: torch.Tensor | None):
+    """y = rmsnorm(x) W^T with the norm folded into the GEMM (rstd fp32 [M], norm_weight bf16 [K]; either may be None)."""
+    _mat(x, w.K)
+    M = x.shape[0]
+    y = torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device)
+    d = w.desc()
+    P.check(P.lib().plz_hard_fwd_norm(C.byref(d), x.data_ptr(), x.stride(0), M, rstd.data_ptr() if rstd is not None else None,
+                                      norm_weight.data_ptr() if norm_weight is not None else None, y.data_ptr(), y.stride(0),
+                                      P.stream_ptr()), "plz_hard_fwd_norm")
+    return y
+
+
+def mlp_gate_up_forward(w_gate: PackedWeight, w_up: PackedWeight, x: torch.Tensor, rstd=None, norm_weight=None):
+    """act = silu(h Wg^T) * (h Wu^T), h = rmsnorm(x) (optional), in one launch; bf16 [M, N]."""
+    _mat(x, w_gate.K)
+    M = x.shape[0]
+    act = torch.empty(M, w_gate.N, dtype=torch.bfloat16, device=x.device)
+    dg, du = w_gate.desc(), w_up.desc()
+    P.check(P.lib().plz_mlp_gate_up_fwd(C.byref(dg), C.byref(du), x.data_ptr(), x.stride(0), M,
+                                        rstd.data_ptr() if rstd is not None else None,
+                                        norm_weight.data_ptr() if norm_weight is not None else None, act.data_ptr(), act.stride(0),
+                                        P.stream_ptr()), "plz_mlp_gate_up_fwd")
+    return act
