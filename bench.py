@@ -121,6 +121,10 @@ def dist_setup(n_gpus):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # NCCL launches its kernels as 4-CTA clusters by default; a cluster needs its SMs free in ONE GPC, which the few
+        # SMs the persistent dX kernel leaves (scattered over the GPCs) never offer, so the small collectives of the
+        # exchange would wait for dX to end. Without clusters they run on whatever SMs are free.
+        os.environ.setdefault("NCCL_CGA_CLUSTER_SIZE", "0")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     else:
@@ -152,12 +156,24 @@ def run_ours(args):
     packed = ops.empty_packed(N_OUT, K_IN, dev)
     w = ops.PackedWeight(packed, palette, N_OUT, K_IN, 1, 256)
     exch = dp.GradExchange()
+    # N > 1: reduce-scatter of dLogits fused into the weight-gradient kernel over peer memory (--exchange allreduce
+    # selects the plain NCCL all-reduce of the full gradient instead, for comparison)
+    scatter = None
+    if world > 1 and args.exchange in ("fused", "fused-add"):
+        scatter = dp.LogitGradScatter(N_OUT, K_IN, dev, mode="slots" if args.exchange == "fused" else "add")
+    # the fused exchange gathers with the copy engines and needs no SM; the NCCL all-reduce does
+    comm_sms = args.comm_sms if args.comm_sms >= 0 else (COMM_SMS if scatter is None else (0 if scatter.mode == "slots" else 16))
     sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
     phases = ["select", "fwd", "lora_dt", "dw", "dx"]
+    if world > 1:
+        # what the exchange adds to the compute stream: the small all-reduce + slot reduction (fused mode), and the wait for
+        # whatever part of the exchange the dX product did not hide
+        phases = phases[:4] + (["exch_sync", "exch_reduce"] if scatter is not None else []) + ["dx", "exch_wait"]
     ev = {p: [] for p in phases}
 
     def step(record):
-        marks = [torch.cuda.Event(enable_timing=True) for _ in range(len(phases) + 1)] if record else None
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(7)] if record else None
+        xm = [torch.cuda.Event(enable_timing=True) for _ in range(2)] if record else None
         if record: marks[0].record()
         ops.soft_select(w, logits, "nk4", noise=noise, tau=TAU, want_packed=True)
         if record: marks[1].record()
@@ -165,19 +181,43 @@ def run_ours(args):
         if record: marks[2].record()
         dt = ops.lora_dt(lora, dy)                                # skinny product, timed with the dx phase below
         if record: marks[3].record()
-        dlog, dpal, da, db = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=TAU, lora_ws=(t, dt))
-        if record: marks[4].record()
-        h1 = exch.start([dlog, dpal, da, db])                     # overlaps the dX GEMM below (N > 1 only)
+        if scatter is not None:
+            # dLogits partials go straight from the epilogue into the owner ranks' staging buffers (reduce-scatter fused
+            # into the kernel); small all-reduce + slot reduction + all-gather then run beside the dX product
+            dpal, da, db = scatter.dw(w, x, dy, logits, noise, TAU, lora_ws=(t, dt))
+            if record: marks[4].record()
+            if scatter.mode == "add":
+                h1 = scatter.start([dpal, da, db])
+            else:
+                h1 = scatter.sync_small([dpal, da, db])
+            if record: xm[0].record()
+            if scatter.mode != "add":
+                scatter.reduce_and_push()
+            if record: xm[1].record()
+        else:
+            dlog, dpal, da, db = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=TAU, lora_ws=(t, dt))
+            if record: marks[4].record()
+            h1 = exch.start([dlog, dpal, da, db])                 # all-reduce, overlaps the dX GEMM below (N > 1 only)
         if world > 1:
-            plz_native.lib().plz_set_cta_limit(sm_count - COMM_SMS)  # leave SMs to NCCL while the exchange runs
+            plz_native.lib().plz_set_cta_limit(sm_count - comm_sms)  # leave SMs to NCCL while the exchange runs
         dx = ops.backward_dx_with_dt(w, dy, lora, dt)             # LUT GEMM (+ LoRA block)
         if world > 1:
             plz_native.lib().plz_set_cta_limit(0)
         if record: marks[5].record()
-        exch.finish(h1)
+        if scatter is not None:
+            dlog = scatter.finish(h1)
+        else:
+            exch.finish(h1)
+        if record: marks[6].record()
         if record:
             ev["select"].append((marks[0], marks[1])); ev["fwd"].append((marks[1], marks[2]))
-            ev["lora_dt"].append((marks[2], marks[3])); ev["dw"].append((marks[3], marks[4])); ev["dx"].append((marks[4], marks[5]))
+            ev["lora_dt"].append((marks[2], marks[3])); ev["dw"].append((marks[3], marks[4]))
+            if scatter is not None:
+                ev["exch_sync"].append((marks[4], xm[0])); ev["exch_reduce"].append((xm[0], xm[1])); ev["dx"].append((xm[1], marks[5]))
+            else:
+                ev["dx"].append((marks[4], marks[5]))
+            if world > 1:
+                ev["exch_wait"].append((marks[5], marks[6]))
         return y, dx, dlog, dpal, da, db
 
     def barrier():
@@ -251,9 +291,9 @@ def run_ours(args):
             if i + 1 < n:
                 upload(b ^ 1)
             main_s.wait_event(ready[b])
-            out = PL.linear_step(bufs[b][0], bufs[b][1], palette, logits, noise, TAU, lora=lora, packed=packed)
+            out = PL.linear_step(bufs[b][0], bufs[b][1], palette, logits, noise, TAU, lora=lora, packed=packed, dp_scatter=scatter)
             free[b].record(main_s)
-            if world > 1:
+            if world > 1 and scatter is None:
                 exch.finish(exch.start([out["dlogits"], out["dpalette"], out["da"], out["db"]]))
             hout[0].copy_(out["dpalette"].reshape(-1), non_blocking=True)
             hout[1].copy_(out["da"].reshape(-1), non_blocking=True)
@@ -273,6 +313,8 @@ def run_ours(args):
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_ms = tt.item()
     plz_native.device_status()
+    if scatter is not None:
+        scatter.close()
 
     if rank != 0:
         if world > 1:
@@ -296,11 +338,11 @@ def run_ours(args):
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens_per_gpu": M_TOK, "N": N_OUT, "K": K_IN, "lora_rank": RANK,
-                   "parallelism": f"dp{world}", "l2": "inputs larger than L2 (x+dY 403 MB, logits+noise 797 MB per step)"},
+                   "parallelism": f"dp{world}", "exchange": ("none" if world == 1 else (f"reduce-scatter fused into the dW epilogue over peer memory ({scatter.mode}) + copy-engine all-gather" if scatter is not None else "NCCL all-reduce")), "l2": "inputs larger than L2 (x+dY 403 MB, logits+noise 797 MB per step)"},
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": hx.numel() * 2 + hdy.numel() * 2,
                 "d2h_bytes_per_step": sum(h.numel() * 4 for h in hout), "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": 6 * args.steps,
+        "gpu_launches": (7 if scatter is not None else 6) * args.steps,
         "phases_ms": phase_ms,
         "tflops_step": 3 * GEMM_FLOPS * world / (ms / args.steps * 1e-3) / 1e12,
         "roofline": {"bound": "tensor", "kernel": {"fwd": "lut_gemm_kernel<2,B_DECODE_K>", "dw": "tn_gemm_kernel<EPI_SOFT,float,true> (+ dA, dB items)",
@@ -399,6 +441,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--comm-sms", type=int, default=-1, help="N > 1: SMs the dX kernel leaves to the exchange (default: built-in)")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "fused-add", "allreduce"],
+                    help="N > 1: dLogits reduce-scatter fused into the weight-gradient kernel (default) or a plain NCCL all-reduce")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

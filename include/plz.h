@@ -182,6 +182,38 @@ int32_t plz_bwd_dw_soft_lora(const plz_weight_t* w, const void* x, int64_t ldx, 
  * fused_lut_linear_bwd_grad_palette_kernel (scripts/fused_lut_kernel.cu:902-1127). */
 int32_t plz_bwd_dw_hard(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy,
                         int32_t M, float* dpalette, void* stream);
+/* Data-parallel form of plz_bwd_dw_soft_lora: the weight-gradient product fused with the reduce-scatter of dLogits
+ * over peer memory. Rank `my_rank` of `world` (2..8, N % world == 0) owns weight rows [my_rank * N/world, ...).
+ * stage[r] is rank r's staging buffer AS MAPPED IN THIS PROCESS (a peer mapping for r != my_rank; CUDA IPC or any other
+ * peer-accessible allocation), fp32 [world][N/world][K][4]. The epilogue stores this rank's partial dLogits of row n
+ * into stage[n / (N/world)], slot my_rank, with plain coalesced 16-byte stores: the partials cross NVLink while the
+ * tensor cores work on the next tile, nothing is read back, and no dLogits buffer of the full size exists.
+ * After every rank's launch has completed (the caller orders this, e.g. with a small collective on the stream),
+ * plz_reduce_slots sums the `world` slots of a rank's own buffer in a fixed order into its shard,
+ * out[shard_elems] = scale * sum_r stage_own[r][...]  (shard_elems = N/world * K * 4).
+ * accumulate = 1 instead ADDS the partials (16-byte vector reductions, performed by the owner's L2) into ONE fp32
+ * [N/world][K][4] accumulator per rank, stage[r], which its owner zeroes beforehand: no slots (1/world of the memory),
+ * no reduction pass, but the order of the `world` additions per element, and so the last bit, varies from run to run.
+ * Needs the native layout (gs_n = 1, interleaved fp32 logits). dPalette, dA, dB as in plz_bwd_dw_soft_lora
+ * (rank = 0: no LoRA). No reference counterpart: the reference is single-process and leaves the whole gradient in
+ * index_logits.grad (scripts/fused_lut_linear_cuda.py:952-961); this is that step for data-parallel ranks. */
+int32_t plz_bwd_dw_soft_scatter(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M,
+                                const plz_logits_t* logits, const plz_noise_t* noise, float tau, float* const* stage,
+                                int32_t world, int32_t my_rank, int32_t accumulate, float* dpalette, const void* t, const void* dt,
+                                int32_t rank, float* dA, float* dB, void* stream);
+/* Staging memory that the other ranks of the node can map (CUDA IPC): plz_peer_alloc allocates `bytes` of zeroed device
+ * memory on the current device and fills the 64-byte handle to send to the peers (any host channel); plz_peer_open maps
+ * a peer's handle into this process (peer access is enabled on first use); plz_peer_close / plz_peer_free undo them.
+ * plz_peer_copy is one asynchronous copy-engine transfer between two such buffers (either side may be a peer mapping):
+ * the all-gather of the reduced shards is `world - 1` of them per rank and takes no SM from the dX product beside it.
+ * Only plz_peer_alloc / plz_peer_open allocate or map memory. */
+int32_t plz_peer_alloc(int64_t bytes, void** ptr, uint8_t* handle64);
+int32_t plz_peer_copy(void* dst, const void* src, int64_t bytes, void* stream);
+int32_t plz_peer_zero(void* ptr, int64_t bytes, void* stream); /* asynchronous memset to 0 (accumulator of accumulate = 1) */
+int32_t plz_peer_open(const uint8_t* handle64, void** ptr);
+int32_t plz_peer_close(void* ptr);
+int32_t plz_peer_free(void* ptr);
+int32_t plz_reduce_slots(const float* stage, int32_t world, int64_t shard_elems, float* out, float scale, void* stream);
 /* LoRA factor gradients, fp32, ACCUMULATED (zero them first):
  *   dA[rank, K] += dt^T x,   dB[N, rank] += dY^T t     (t, dt as left by plz_hard_fwd / plz_bwd_dx).
  * Autograd of scripts/qwen_model.py:300-304. */

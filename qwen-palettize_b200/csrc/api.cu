@@ -373,7 +373,8 @@ int32_t plz_dense_bwd_dx(const void* Wd, int64_t ldw, int32_t N, int32_t K, cons
 static int bwd_dw_common(int epi, const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy,
                          int32_t M, const plz_logits_t* logits, const plz_noise_t* noise, float tau, void* dlogits,
                          float* dpalette, void* stream, const void* t = nullptr, const void* dt = nullptr, int rank = 0,
-                         float* dA = nullptr, float* dB = nullptr) {
+                         float* dA = nullptr, float* dB = nullptr, float* const* peer_stage = nullptr, int world = 1,
+                         int my_rank = 0, int scatter_add = 0) {
     int rc = check_weight(w, epi == EPI_HARD);
     if (rc) return rc;
     if (M <= 0) { if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; } return PLZ_OK; }
@@ -422,6 +423,10 @@ static int bwd_dw_common(int epi, const plz_weight_t* w, const void* x, int64_t 
     PLZ_CUDA_CHECK(cudaGetDevice(&dev));
     PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     a.sm_count = sms;
+    if (world > 1) {
+        a.world = world; a.rank = my_rank; a.scatter_add = scatter_add;
+        for (int r = 0; r < world && r < 8; ++r) a.peer_stage[r] = peer_stage[r];
+    }
     return launch_tn_gemm(a, (cudaStream_t)stream);
 }
 
@@ -439,6 +444,65 @@ int32_t plz_bwd_dw_soft_lora(const plz_weight_t* w, const void* x, int64_t ldx, 
     if (rank <= 0 || rank > 64 || rank % 8) { set_last_error("LoRA rank %d must be a multiple of 8 in [8, 64]", rank); return PLZ_ERR_BAD_SHAPE; }
     if ((dA && !dt) || (dB && !t)) { set_last_error("bwd_dw_soft_lora: dA needs dt and dB needs t"); return PLZ_ERR_NULL; }
     return bwd_dw_common(EPI_SOFT, w, x, ldx, dY, lddy, M, logits, noise, tau, dlogits, dpalette, stream, t, dt, rank, dA, dB);
+}
+
+int32_t plz_bwd_dw_soft_scatter(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M,
+                                const plz_logits_t* logits, const plz_noise_t* noise, float tau, float* const* stage,
+                                int32_t world, int32_t my_rank, int32_t accumulate, float* dpalette, const void* t, const void* dt,
+                                int32_t rank, float* dA, float* dB, void* stream) {
+    if (!(tau > 0.f)) { set_last_error("tau must be positive"); return PLZ_ERR_BAD_SHAPE; }
+    if (world < 2 || world > 8 || my_rank < 0 || my_rank >= world) { set_last_error("bwd_dw_soft_scatter: world must be in [2, 8] and 0 <= my_rank < world"); return PLZ_ERR_BAD_SHAPE; }
+    if (!stage) { set_last_error("null staging pointer table"); return PLZ_ERR_NULL; }
+    if (rank < 0 || rank > 64 || rank % 8) { set_last_error("LoRA rank %d must be 0 or a multiple of 8 in [8, 64]", rank); return PLZ_ERR_BAD_SHAPE; }
+    if ((dA && !dt) || (dB && !t)) { set_last_error("bwd_dw_soft_scatter: dA needs dt and dB needs t"); return PLZ_ERR_NULL; }
+    return bwd_dw_common(EPI_SOFT, w, x, ldx, dY, lddy, M, logits, noise, tau, nullptr, dpalette, stream, t, dt, rank, dA, dB,
+                         stage, world, my_rank, accumulate ? 1 : 0);
+}
+
+// ---- peer-visible staging memory (CUDA IPC) ------------------------------------------------------------
+int32_t plz_peer_alloc(int64_t bytes, void** ptr, uint8_t* handle64) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (bytes <= 0 || !ptr || !handle64) { set_last_error("peer_alloc: bad arguments"); return PLZ_ERR_NULL; }
+    void* p = nullptr;
+    PLZ_CUDA_CHECK(cudaMalloc(&p, (size_t)bytes));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaMemset(p, 0, (size_t)bytes);
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { cudaFree(p); set_last_error("peer_alloc: %s", cudaGetErrorString(e)); return PLZ_ERR_CUDA; }
+    memcpy(handle64, &h, 64);
+    *ptr = p;
+    return PLZ_OK;
+}
+int32_t plz_peer_open(const uint8_t* handle64, void** ptr) {
+    if (!handle64 || !ptr) { set_last_error("peer_open: null argument"); return PLZ_ERR_NULL; }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    PLZ_CUDA_CHECK(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return PLZ_OK;
+}
+int32_t plz_peer_copy(void* dst, const void* src, int64_t bytes, void* stream) {
+    if (bytes < 0) { set_last_error("peer_copy: negative size"); return PLZ_ERR_BAD_SHAPE; }
+    if (bytes == 0) return PLZ_OK;
+    if (!dst || !src) { set_last_error("peer_copy: null pointer"); return PLZ_ERR_NULL; }
+    PLZ_CUDA_CHECK(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+    return PLZ_OK;
+}
+int32_t plz_peer_zero(void* ptr, int64_t bytes, void* stream) {
+    if (bytes < 0) { set_last_error("peer_zero: negative size"); return PLZ_ERR_BAD_SHAPE; }
+    if (bytes == 0) return PLZ_OK;
+    if (!ptr) { set_last_error("peer_zero: null pointer"); return PLZ_ERR_NULL; }
+    PLZ_CUDA_CHECK(cudaMemsetAsync(ptr, 0, (size_t)bytes, (cudaStream_t)stream));
+    return PLZ_OK;
+}
+int32_t plz_peer_close(void* ptr) { if (ptr) PLZ_CUDA_CHECK(cudaIpcCloseMemHandle(ptr)); return PLZ_OK; }
+int32_t plz_peer_free(void* ptr) { if (ptr) PLZ_CUDA_CHECK(cudaFree(ptr)); return PLZ_OK; }
+
+int32_t plz_reduce_slots(const float* stage, int32_t world, int64_t shard_elems, float* out, float scale, void* stream) {
+    if (world < 1 || world > 8 || shard_elems < 0 || (shard_elems & 3)) { set_last_error("reduce_slots: world in [1, 8], shard_elems a non-negative multiple of 4"); return PLZ_ERR_BAD_SHAPE; }
+    if (shard_elems == 0) return PLZ_OK;
+    if (!stage || !out) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)stage | (uintptr_t)out) & 15) { set_last_error("reduce_slots: 16-byte alignment required"); return PLZ_ERR_BAD_ALIGN; }
+    return launch_reduce_slots(stage, world, shard_elems, out, scale, (cudaStream_t)stream);
 }
 
 int32_t plz_bwd_dw_hard(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M,

@@ -48,6 +48,8 @@ struct TnArgs {
     // optional side jobs appended to a dW launch: out[r, j] += sum_m S[m, r] * (q_is_p ? P : Q)[m, j]
     const void* side_S[2]; long long side_ld[2]; int side_rank; int side_q_is_p[2];
     float* side_out[2]; long long side_si[2], side_sj[2];
+    // fused reduce-scatter of dLogits over peer memory (world > 1): staging base of every rank, as mapped in THIS process
+    int world, rank, scatter_add; float* peer_stage[8];
 };
 int launch_tn_gemm(const TnArgs& a, cudaStream_t stream);
 
@@ -92,6 +94,7 @@ struct AdamParams {
 };
 
 int launch_adamw(const AdamParams& p, int grad_dtype, int param_dtype, cudaStream_t stream);
+int launch_reduce_slots(const float* stage, int world, long long shard_elems, float* out, float scale, cudaStream_t stream);
 int launch_rms_rstd(const void* x, long long ldx, int M, int K, float eps, float* rstd, cudaStream_t stream);
 int launch_distill_loss(const void* s, long long lds, const void* t, long long ldt, int M, int H, float eps, float w_cos,
                         float w_mse, float upstream, float* ws, float* out4, void* ds, long long ldds, int ds_dtype,

@@ -49,6 +49,11 @@ struct TnParams {
         float* out; long long out_si, out_sj;
     } side[2];
     int n_side_items;
+    // Fused reduce-scatter of dLogits over peer memory (rows = k layout only): weight row n belongs to rank
+    // n / rows_per_rank; its gradient is stored into that rank's staging buffer, slot `rank`, instead of into `dlogits`.
+    // scatter_add: the owner's buffer is one fp32 [rows_per_rank][K][4] accumulator (zeroed by its owner) and the partials
+    // are added to it with vector reductions instead of being stored into per-source slots.
+    float* peer_stage[8]; int world, rank, rows_per_rank, scatter_add; long long shard_elems;
     StatusWord* status;
 };
 
@@ -331,7 +336,19 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                                 part[c * 4 + q] = dw * s4.P[q];
                                 dl[q] = part[c * 4 + q] * (cp[q] - s4.w_soft);
                             }
-                            if (valid && dbase != nullptr)
+                            if (valid && p.world > 1) {
+                                // plain (non-atomic) 16-byte store into the owner's staging slot of this rank: the 32 lanes
+                                // of the warp cover 512 contiguous bytes there, peer or local alike
+                                const int owner = n / p.rows_per_rank;
+                                const long long off = ((long long)(n - owner * p.rows_per_rank) * p.I + k) * 4;
+                                if (p.scatter_add) {
+                                    asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                                 :: "l"(p.peer_stage[owner] + off), "f"(dl[0]), "f"(dl[1]), "f"(dl[2]), "f"(dl[3]) : "memory");
+                                } else {
+                                    *reinterpret_cast<float4*>(p.peer_stage[owner] + (long long)p.rank * p.shard_elems + off) =
+                                        make_float4(dl[0], dl[1], dl[2], dl[3]);
+                                }
+                            } else if (valid && dbase != nullptr)
                                 __stcs(reinterpret_cast<float4*>(dbase + (long long)n * p.ls_col), make_float4(dl[0], dl[1], dl[2], dl[3]));
                         } else {
                             const int idx = (hbyte[c] >> (2 * (k & 3))) & 3;
@@ -587,6 +604,20 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
             }
         } else if (!a.packed) { set_last_error("tn_gemm: null packed indices"); return PLZ_ERR_NULL; }
         if ((uintptr_t)a.palette & 7) { set_last_error("tn_gemm: palette must be 8-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    }
+    p.world = 1; p.rank = 0; p.rows_per_rank = 1; p.shard_elems = 0; p.scatter_add = a.scatter_add;
+    for (int r = 0; r < 8; ++r) p.peer_stage[r] = nullptr;
+    if (a.world > 1) {
+        if (a.epi != EPI_SOFT || !a.rows_are_k || a.world > 8 || a.J % a.world) {
+            set_last_error("tn_gemm: the fused reduce-scatter needs interleaved fp32 logits, world <= 8 and N %% world == 0");
+            return PLZ_ERR_UNSUPPORTED;
+        }
+        p.world = a.world; p.rank = a.rank; p.rows_per_rank = a.J / a.world;
+        p.shard_elems = (long long)p.rows_per_rank * a.I * 4;
+        for (int r = 0; r < a.world; ++r) {
+            if (!a.peer_stage[r] || ((uintptr_t)a.peer_stage[r] & 15)) { set_last_error("tn_gemm: null or misaligned peer staging pointer"); return PLZ_ERR_NULL; }
+            p.peer_stage[r] = a.peer_stage[r];
+        }
     }
     p.status = device_status_ptr();
     const int tiles = ((a.I + 127) / 128) * ((a.J + 255) / 256) * p.splits;

@@ -190,4 +190,31 @@ int launch_rms_rstd(const void* x, long long ldx, int M, int K, float eps, float
     return PLZ_OK;
 }
 
+// out[i] = scale * (slot 0 + slot 1 + ... + slot world-1)[i], slots `shard_elems` floats apart: the second half of the
+// reduce-scatter whose first half is the weight-gradient epilogue storing every rank's partial into the owner's slots.
+// Fixed summation order, so every run and every rank count gives the same bits for the same partials.
+__global__ void __launch_bounds__(256)
+reduce_slots_kernel(const float4* __restrict__ stage, int world, long long shard_vec, float4* __restrict__ out, float scale) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < shard_vec; i += stride) {
+        float4 acc = __ldcs(stage + i);
+        for (int r = 1; r < world; ++r) {
+            const float4 v = __ldcs(stage + (long long)r * shard_vec + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+        out[i] = acc;
+    }
+}
+
+int launch_reduce_slots(const float* stage, int world, long long shard_elems, float* out, float scale, cudaStream_t stream) {
+    if (shard_elems <= 0) return PLZ_OK;
+    const long long vec = shard_elems / 4;
+    long long blocks = (vec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    reduce_slots_kernel<<<(int)blocks, 256, 0, stream>>>((const float4*)stage, world, vec, (float4*)out, scale);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
 }  // namespace plz

@@ -99,3 +99,177 @@ class GradExchange:
         if stream is not None:
             torch.cuda.current_stream(tensors[0].device).wait_stream(stream)
         return tensors
+
+
+class _DeviceArray:
+    """Adapter that lets torch view library-allocated device memory (no copy) through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, shape, typestr="<f4"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+
+class LogitGradScatter:
+    """Exchange of the index-logit gradient between data-parallel ranks, built around the weight-gradient kernel:
+
+      1. reduce-scatter inside the kernel: every rank owns N / world weight rows and a peer-visible staging buffer
+         fp32 [world, N/world, K, 4].  The epilogue of rank s stores its partial dLogits for row n straight into slot s of
+         the owner's buffer -- plain coalesced stores over NVLink, tile by tile while the tensor cores work on the next
+         tile.  The partial gradient (398 MB at N x K = 9728 x 2560) is never written locally nor read back by a collective.
+      2. a sum all-reduce of the small gradients (dPalette, dA, dB) on the compute stream: it is needed anyway and it is the
+         point after which every rank's stores have landed.
+      3. reduce_slots: the owner sums its `world` slots in rank order (deterministic) into its rows of `self.full`.
+      4. all-gather by the copy engines on a side stream: each rank pushes its reduced shard into the peers' `full`
+         buffers (world - 1 asynchronous peer copies, staggered so that every round is a permutation of the ranks), then
+         a one-element all-reduce marks "all pushes done".  It uses no SM, so the dX product that runs beside it keeps
+         the whole GPU.
+
+    Hazards: a rank can only pass the all-reduce of step 2 after every rank has launched it, i.e. after every rank has
+    finished consuming the previous step's `full` and staging slots, so the stores and pushes of a step never overtake
+    the readers of the step before.
+
+    mode 'add' replaces the slots and step 3 by vector reductions (red.add.v4.f32, executed by the owner's L2) into one
+    shard-sized accumulator per rank: steps 2 and 4 then run entirely on the side stream and nothing of the exchange sits
+    on the compute stream, at the price of a run-to-run varying order of the `world` additions per element.
+
+    With world == 1 nothing is mapped and `dw` falls through to the single-rank entry point."""
+
+    def __init__(self, N: int, K: int, device, group=None, average: bool = False, mode: str = "slots"):
+        import ctypes as C
+        import plz_native as P
+        if mode not in ("slots", "add"):
+            raise ValueError("mode must be 'slots' or 'add'")
+        if mode == "add" and average:
+            raise ValueError("mode 'add' returns sums: fold 1/world into the optimizer's gradient scale instead")
+        self.N, self.K, self.group, self.device, self.mode = N, K, group, device, mode
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.scale = 1.0 / self.world if average else 1.0
+        self.full = None
+        self.ptrs, self.full_ptrs, self._own, self._opened = [], [], [], []
+        if self.world == 1:
+            return
+        if N % self.world:
+            raise ValueError(f"N={N} must be a multiple of the number of ranks ({self.world})")
+        self._stream = torch.cuda.Stream(device=device)
+        self._done = torch.zeros(1, dtype=torch.float32, device=device)
+        mine = []
+        # staging: `world` slots of a shard each, or one shard-sized accumulator; then the gathered gradient
+        for nbytes in (N * K * 16 if mode == "slots" else N * K * 16 // self.world, N * K * 16):
+            own, handle = C.c_void_p(), C.create_string_buffer(64)
+            P.check(P.lib().plz_peer_alloc(nbytes, C.byref(own), handle), "plz_peer_alloc")
+            self._own.append(own.value)
+            mine.append(handle.raw)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, mine, group=group)
+        for r, hs in enumerate(handles):
+            pair = []
+            for j, h in enumerate(hs):
+                if r == self.rank:
+                    pair.append(self._own[j])
+                    continue
+                p = C.c_void_p()
+                P.check(P.lib().plz_peer_open(C.create_string_buffer(h, 64), C.byref(p)), "plz_peer_open")
+                self._opened.append(p.value)
+                pair.append(p.value)
+            self.ptrs.append(pair[0])
+            self.full_ptrs.append(pair[1])
+        self.full = torch.as_tensor(_DeviceArray(self._own[1], (N, K, 4)), device=device)
+
+    def dw(self, w, x, dy, logits, noise, tau, seed=0, lora_ws=None):
+        """Weight-gradient launch; returns this rank's (dPalette, dA, dB). The dLogits partials are in flight to their owners."""
+        import plz_ops as ops
+        if self.world == 1:
+            r = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=tau, seed=seed, lora_ws=lora_ws)
+            self.full = r[0]
+            return (r[1], r[2], r[3]) if lora_ws is not None else (r[1], None, None)
+        return ops.backward_dw_soft_scatter(w, x, dy, logits, self.ptrs, self.world, self.rank, noise=noise, tau=tau, seed=seed,
+                                            lora_ws=lora_ws, accumulate=self.mode == "add")
+
+    def start(self, small):
+        """Steps 2-4 above. `small` (dPalette, dA, dB ...) are sum-all-reduced in place on the current stream; the pushes
+        of the reduced shard run on the side stream. Returns a handle for finish()."""
+        if self.world == 1:
+            return None
+        if self.mode == "add":
+            return self._start_add(small)
+        handle = self.sync_small(small)
+        self.reduce_and_push()
+        return handle
+
+    def _start_add(self, small):
+        """mode 'add': the owner's accumulator already holds the sum once every rank's kernel has finished, so the whole
+        exchange runs on the side stream beside dX: small all-reduce (= all kernels finished) -> copy-engine pushes of the
+        accumulator into every rank's `full` (this rank's included) -> accumulator zeroed for the next step -> completion
+        all-reduce.  A peer's next additions come after it has passed this step's completion all-reduce, hence after the
+        zeroing here."""
+        import plz_native as P
+        cur = torch.cuda.current_stream(self.device)
+        self._stream.wait_stream(cur)
+        rows = self.N // self.world
+        shard_bytes = rows * self.K * 16
+        off = self.rank * shard_bytes
+        with torch.cuda.stream(self._stream):
+            handle = self.sync_small(small)
+            sp = self._stream.cuda_stream
+            for j in range(self.world):
+                dst = (self.rank + j) % self.world
+                P.check(P.lib().plz_peer_copy(self.full_ptrs[dst] + off, self._own[0], shard_bytes, sp), "plz_peer_copy")
+            P.check(P.lib().plz_peer_zero(self._own[0], shard_bytes, sp), "plz_peer_zero")
+            dist.all_reduce(self._done, group=self.group)
+        return handle
+
+    def sync_small(self, small):
+        """Step 2: sum-all-reduce `small` in place on the current stream (all ranks' staging stores are complete after it)."""
+        small = [t for t in small if t is not None]
+        n = sum(t.numel() for t in small)
+        bucket = torch.empty(max(n, 1), dtype=torch.float32, device=self.device)
+        o = 0
+        for t in small:
+            bucket[o:o + t.numel()].copy_(t.reshape(-1))
+            o += t.numel()
+        dist.all_reduce(bucket, op=dist.ReduceOp.SUM, group=self.group)
+        o = 0
+        for t in small:
+            t.copy_(bucket[o:o + t.numel()].reshape(t.shape))
+            if self.scale != 1.0:
+                t.mul_(self.scale)
+            o += t.numel()
+        return (small, bucket)
+
+    def reduce_and_push(self):
+        """Steps 3 and 4: reduce this rank's slots on the current stream, push the shard to the peers on the side stream."""
+        import plz_native as P
+        import plz_ops as ops
+        rows = self.N // self.world
+        shard = self.full[self.rank * rows:(self.rank + 1) * rows]
+        ops.reduce_slots(self.ptrs[self.rank], self.world, shard, self.scale)
+        cur = torch.cuda.current_stream(self.device)
+        self._stream.wait_stream(cur)
+        shard_bytes = rows * self.K * 16
+        off = self.rank * shard_bytes
+        with torch.cuda.stream(self._stream):
+            for j in range(1, self.world):
+                dst = (self.rank + j) % self.world
+                P.check(P.lib().plz_peer_copy(self.full_ptrs[dst] + off, self._own[1] + off, shard_bytes, self._stream.cuda_stream),
+                        "plz_peer_copy")
+            dist.all_reduce(self._done, group=self.group)  # leaves only when every rank has issued and finished its pushes
+
+    def finish(self, handle):
+        """The compute stream waits for the pushes; afterwards `self.full` holds the reduced dLogits on every rank."""
+        if handle is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._stream)
+        return self.full
+
+    def close(self):
+        import plz_native as P
+        if self.world > 1 and self._own:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)  # nobody unmaps while a peer may still store
+            self.full = None
+            for p in self._opened:
+                P.check(P.lib().plz_peer_close(p), "plz_peer_close")
+            self._opened = []
+            dist.barrier(group=self.group)
+            for p in self._own:
+                P.check(P.lib().plz_peer_free(p), "plz_peer_free")
+            self._own = []

@@ -28,12 +28,15 @@ import plz_ops as ops  # noqa: E402
 
 
 def linear_step(x, dy, palette, logits, noise, tau, lora=None, ste=True, packed=None, seed=0, gs_n=1, gs_k=256,
-                want=("y", "dx", "dlogits", "dpalette", "da", "db")):
+                want=("y", "dx", "dlogits", "dpalette", "da", "db"), dp_scatter=None):
     """x bf16 [M, K]; dy bf16 [M, N] or None (forward only); palette bf16 [N/gs_n, K/gs_k, 4];
     logits fp32 [N, K, 4]; noise: fp32 [N, K, 4], None or 'hash'; lora = (A [r, K], B [N, r], scale) or None.
     `packed` is an optional preallocated uint8 [N, K/4] buffer for the hard indices.
     Returns a dict with the requested outputs (dlogits fp32 [N, K, 4], dpalette fp32 [groups, 4],
-    da fp32 [r, K], db fp32 [N, r]) plus 'packed'."""
+    da fp32 [r, K], db fp32 [N, r]) plus 'packed'.
+    dp_scatter: a dp.LogitGradScatter (data-parallel ranks, straight-through path with LoRA): the weight-gradient launch
+    stores its dLogits partials into the owners' staging buffers, the exchange runs beside the dX product, and the
+    returned gradients are already summed over the ranks."""
     N, K, _ = logits.shape
     if packed is None:
         packed = ops.empty_packed(N, K, x.device)
@@ -48,6 +51,14 @@ def linear_step(x, dy, palette, logits, noise, tau, lora=None, ste=True, packed=
     if dy is None:
         return out
     fused_lora = ste and lora is not None and ("da" in want or "db" in want) and ("dlogits" in want or "dpalette" in want)
+    if fused_lora and dp_scatter is not None and dp_scatter.world > 1:
+        dt = ops.lora_dt(lora, dy)
+        dpal, da, db = dp_scatter.dw(w, x, dy, logits, noise, tau, seed=seed, lora_ws=(t, dt))
+        handle = dp_scatter.start([dpal, da, db])
+        if "dx" in want:
+            out["dx"] = ops.backward_dx_with_dt(w, dy, lora, dt)
+        out.update(dlogits=dp_scatter.finish(handle), dpalette=dpal, da=da, db=db)
+        return out
     if fused_lora:
         # dt first, then the weight-gradient launch also produces dA and dB, then dX with the dt already there
         dt = ops.lora_dt(lora, dy)

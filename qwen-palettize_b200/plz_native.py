@@ -58,6 +58,15 @@ SIGNATURES = {
     "plz_dense_bwd_dx": [_P, _I64, _I32, _I32, _P, _I64, _I32, _LP, _P, _P, _I64, _P],
     "plz_bwd_dw_soft": [_WP, _P, _I64, _P, _I64, _I32, _GP, _NP, _F, _P, _P, _P],
     "plz_bwd_dw_soft_lora": [_WP, _P, _I64, _P, _I64, _I32, _GP, _NP, _F, _P, _P, _P, _P, _I32, _P, _P, _P],
+    "plz_bwd_dw_soft_scatter": [_WP, _P, _I64, _P, _I64, _I32, _GP, _NP, _F, C.POINTER(C.c_void_p), _I32, _I32, _I32, _P, _P, _P, _I32,
+                                _P, _P, _P],
+    "plz_peer_alloc": [_I64, C.POINTER(C.c_void_p), C.c_char_p],
+    "plz_peer_open": [C.c_char_p, C.POINTER(C.c_void_p)],
+    "plz_peer_copy": [_P, _P, _I64, _P],
+    "plz_peer_zero": [_P, _I64, _P],
+    "plz_peer_close": [_P],
+    "plz_peer_free": [_P],
+    "plz_reduce_slots": [_P, _I32, _I64, _P, _F, _P],
     "plz_bwd_dw_hard": [_WP, _P, _I64, _P, _I64, _I32, _P, _P],
     "plz_lora_bwd": [_P, _I64, _P, _I64, _P, _P, _I32, _I32, _I32, _I32, _P, _P, _P],
     "plz_rms_rstd": [_P, _I64, _I32, _I32, _F, _P, _P],
