@@ -327,12 +327,15 @@ def run_ours(args):
     achieved = GEMM_FLOPS / (kern_ms[gemm_phase] * 1e-3) / 1e12
     # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum): one ncu capture of each kernel at 4096
     # tokens (profiles/*.md) gave measured / algorithmic = 0.51 (fwd: most of y was still in L2 when the capture
-    # ended), 0.91 (dx) and 1.005 (dw); the figures below are those ratios times the algorithmic bytes of the full
-    # 16384-token launch (the M-proportional part scales, the 1.2 GB of logits / noise / dLogits does not).
+    # ended) and 0.87 (dx). The dW launch measured 1391.8 MB there: 1195.4 MB of logits / noise / dLogits that do not
+    # depend on the token count, plus x and dY streamed twice (once for dW, once more by the dA / dB side items in
+    # the last round); the figure below scales that token-proportional part to the full 16384-token launch.
     alg = {"fwd": M_TOK * K_IN * 2 + N_OUT * K_IN // 4 + N_OUT * (K_IN // 256) * 8 + M_TOK * N_OUT * 2,
            "dx": M_TOK * N_OUT * 2 + N_OUT * K_IN // 4 + N_OUT * (K_IN // 256) * 8 + M_TOK * K_IN * 2,
            "dw": 3 * N_OUT * K_IN * 16 + M_TOK * (N_OUT + K_IN) * 2}
-    traffic = {"fwd": 0.51 * alg["fwd"], "dx": 0.91 * alg["dx"], "dw": 1.005 * alg["dw"]}
+    xdy_small = 4096 * (N_OUT + K_IN) * 2
+    traffic = {"fwd": 0.51 * alg["fwd"], "dx": 0.87 * alg["dx"],
+               "dw": (1391.8e6 - 2 * xdy_small) + 2 * M_TOK * (N_OUT + K_IN) * 2}
     line = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",

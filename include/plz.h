@@ -183,7 +183,7 @@ int32_t plz_bwd_dw_soft_lora(const plz_weight_t* w, const void* x, int64_t ldx, 
 int32_t plz_bwd_dw_hard(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy,
                         int32_t M, float* dpalette, void* stream);
 /* Data-parallel form of plz_bwd_dw_soft_lora: the weight-gradient product fused with the reduce-scatter of dLogits
- * over peer memory. Rank `my_rank` of `world` (2..8, N % world == 0) owns weight rows [my_rank * N/world, ...).
+ * over peer memory. Rank `my_rank` of `world` (2..8, N % (8 * world) == 0) owns weight rows [my_rank * N/world, ...).
  * stage[r] is rank r's staging buffer AS MAPPED IN THIS PROCESS (a peer mapping for r != my_rank; CUDA IPC or any other
  * peer-accessible allocation), fp32 [world][N/world][K][4]. The epilogue stores this rank's partial dLogits of row n
  * into stage[n / (N/world)], slot my_rank, with plain coalesced 16-byte stores: the partials cross NVLink while the

@@ -286,6 +286,14 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                     uint32_t v[8];
                     tmem_ld_32x8(trow + c0, v);
                     const int nb = colbase + c0;  // first n of the batch
+                    // fused reduce-scatter: the 8 rows of a batch have one owner (rows_per_rank % 8 == 0); its buffer, this
+                    // rank's slot (or the accumulator) and this thread's k folded into one base pointer per batch
+                    float* sbase = nullptr;
+                    if (p.world > 1 && nb < p.J) {
+                        const int owner = nb / p.rows_per_rank;
+                        sbase = p.peer_stage[owner] + (p.scatter_add ? 0ll : (long long)p.rank * p.shard_elems) +
+                                ((long long)(nb - owner * p.rows_per_rank) * p.I + k) * 4;
+                    }
                     float4 lv[8], gv[8];
                     uint2 praw[8];
                     uint32_t hbyte[8];
@@ -339,14 +347,12 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                             if (valid && p.world > 1) {
                                 // plain (non-atomic) 16-byte store into the owner's staging slot of this rank: the 32 lanes
                                 // of the warp cover 512 contiguous bytes there, peer or local alike
-                                const int owner = n / p.rows_per_rank;
-                                const long long off = ((long long)(n - owner * p.rows_per_rank) * p.I + k) * 4;
+                                float* dst = sbase + (long long)c * p.I * 4;
                                 if (p.scatter_add) {
                                     asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
-                                                 :: "l"(p.peer_stage[owner] + off), "f"(dl[0]), "f"(dl[1]), "f"(dl[2]), "f"(dl[3]) : "memory");
+                                                 :: "l"(dst), "f"(dl[0]), "f"(dl[1]), "f"(dl[2]), "f"(dl[3]) : "memory");
                                 } else {
-                                    *reinterpret_cast<float4*>(p.peer_stage[owner] + (long long)p.rank * p.shard_elems + off) =
-                                        make_float4(dl[0], dl[1], dl[2], dl[3]);
+                                    *reinterpret_cast<float4*>(dst) = make_float4(dl[0], dl[1], dl[2], dl[3]);
                                 }
                             } else if (valid && dbase != nullptr)
                                 __stcs(reinterpret_cast<float4*>(dbase + (long long)n * p.ls_col), make_float4(dl[0], dl[1], dl[2], dl[3]));
@@ -608,8 +614,8 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
     p.world = 1; p.rank = 0; p.rows_per_rank = 1; p.shard_elems = 0; p.scatter_add = a.scatter_add;
     for (int r = 0; r < 8; ++r) p.peer_stage[r] = nullptr;
     if (a.world > 1) {
-        if (a.epi != EPI_SOFT || !a.rows_are_k || a.world > 8 || a.J % a.world) {
-            set_last_error("tn_gemm: the fused reduce-scatter needs interleaved fp32 logits, world <= 8 and N %% world == 0");
+        if (a.epi != EPI_SOFT || !a.rows_are_k || a.world > 8 || a.J % (8 * a.world)) {
+            set_last_error("tn_gemm: the fused reduce-scatter needs interleaved fp32 logits, world <= 8 and N %% (8 * world) == 0");
             return PLZ_ERR_UNSUPPORTED;
         }
         p.world = a.world; p.rank = a.rank; p.rows_per_rank = a.J / a.world;

@@ -1,6 +1,6 @@
 """Run one kernel of the hot path a few times on a small case, for `ncu` captures.
 
-    python qwen-palettize_b200/profile_case.py --case fwd|dx|dw|smallm|select [--M 4096] [--N 9728] [--K 2560] [--iters 3]
+    python qwen-palettize_b200/profile_case.py --case fwd|dx|dw|smallm|select|gateup [--M 4096] [--N 9728] [--K 2560] [--iters 3]
 
 The shapes keep the full weight matrix of the benchmark Linear (so per-tile behaviour is the benchmark's) and cut
 the token count; everything held on the device stays under 2 GB.
@@ -19,7 +19,7 @@ import synth  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["fwd", "dx", "dw", "smallm", "select"])
+    ap.add_argument("--case", required=True, choices=["fwd", "dx", "dw", "smallm", "select", "gateup"])
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--N", type=int, default=9728)
     ap.add_argument("--K", type=int, default=2560)
@@ -29,13 +29,23 @@ def main():
     pal = d["palette"].reshape(-1, 4).contiguous()
     w = ops.PackedWeight(ops.pack_indices(d["idx"].view(torch.int8), n_major=True), pal, a.N, a.K, 1, 256)
     lora = (d["lora_a"], d["lora_b"], 1.0)
+    t = dt = w2 = rstd = g = None
+    if a.case == "dw":  # the workspaces the weight-gradient launch takes its dA / dB side items from
+        t = ops.hard_forward(w, d["x"], lora)[1]
+        dt = ops.lora_dt(lora, d["dy"])
+    if a.case == "gateup":  # second matrix of the fused gate/up launch and the RMSNorm factors
+        w2 = ops.PackedWeight(ops.pack_indices(((d["idx"].view(torch.uint8) + 1) & 3).view(torch.int8), n_major=True), pal, a.N, a.K, 1, 256)
+        rstd = ops.rms_rstd(d["x"], 1e-6)
+        g = torch.ones(a.K, dtype=torch.bfloat16, device=d["x"].device)
     for _ in range(a.iters):
-        if a.case == "fwd":
+        if a.case == "gateup":
+            ops.mlp_gate_up_forward(w, w2, d["x"], rstd, g)
+        elif a.case == "fwd":
             ops.hard_forward(w, d["x"], lora)
         elif a.case == "dx":
             ops.backward_dx(w, d["dy"], lora)
         elif a.case == "dw":
-            ops.backward_dw_soft(w, d["x"], d["dy"], d["logits"], "nk4", noise=d["noise"], tau=1.0)
+            ops.backward_dw_soft(w, d["x"], d["dy"], d["logits"], "nk4", noise=d["noise"], tau=1.0, lora_ws=(t, dt))
         elif a.case == "smallm":
             ops.hard_forward_smallm(w, d["x"][: min(a.M, 64)].contiguous())
         else:
