@@ -133,6 +133,20 @@ int32_t plz_hard_fwd_lora_static(const plz_weight_t* w, const void* x, int64_t l
  * scripts/fused_lut_kernel.cu:309) serves every batch size and reads one byte per weight. */
 int32_t plz_hard_fwd_smallm(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, void* y, int64_t ldy,
                             void* stream);
+/* The same for 1 to 4 weight matrices that multiply the SAME x (gate_proj and up_proj of the MLP; q, k and v projections of the
+ * attention: separate Linears of the same input in the reference's model, listed with their shapes in
+ * scripts/bench_triton_kernels.py:9 and :141-142, each wrapped on its own by scripts/qwen_model.py:769-794):
+ * one launch streams all of them, ys[i] = x W_i^T (bf16 [M, N_i], pitch ldys[i]). M <= 16; all matrices share K and
+ * the palette grouping. A decode step is bound by launch latency, not bandwidth, at 7 MB per Linear. */
+int32_t plz_hard_fwd_smallm_multi(const plz_weight_t* const* ws, int32_t count, const void* x, int64_t ldx, int32_t M,
+                                  void* const* ys, const int64_t* ldys, void* stream);
+/* on = 1: small-M launches (M <= 16) carry the programmatic-stream-serialization attribute, so a launch may start while the
+ * previous kernel of the stream is still running: it issues the loads of its weights and builds its tables at once, and
+ * waits for the previous kernel to finish (griddepcontrol.wait) only before it reads x or writes y. This hides the
+ * launch latency between the Linears of a decode step. Only valid when the kernel that precedes a small-M call in its
+ * stream does not write that call's packed indices or palettes (true in inference; not right after plz_soft_select or
+ * plz_pack_indices). Process-wide, default 0. */
+int32_t plz_set_smallm_overlap(int32_t on);
 
 /* One pass over the index logits: packed hard indices (argmax over the plain logits, first maximum
  * wins: scripts/triton_soft_forward.py:160-168) into w->packed (written!), and/or the soft weights

@@ -88,10 +88,43 @@ def main():
             ys = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
             ms = timed(lambda i: ops.hard_forward_smallm(ws[i % copies], x, out=ys[i & 1]), a.iters, graph_batch=copies)
             gbs = wbytes / (ms * 1e-3) / 1e9
-            print(json.dumps({"kernel": "lut_gemv_kernel", "case": "smallm", "M": M, "N": N, "K": K, "us": ms * 1e3,
+            print(json.dumps({"kernel": "lut_smallm_mma_kernel" if M <= 16 else "lut_gemv_kernel (tcgen05 swap-AB)", "case": "smallm", "M": M, "N": N, "K": K, "us": ms * 1e3,
                               "weight_bytes": wbytes, "GBps": gbs, "hbm_peak_GBps": hbm, "frac": gbs / hbm,
                               "peak_source": src, "weight_copies_rotated": copies, "timing": "CUDA graph of one launch per weight copy"}))
         if (N, K) == (9728, 2560):
+            # gate_proj + up_proj share x: one launch streams both matrices (pairs of consecutive weight copies)
+            for M in (1, 8, 16):
+                x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+                pairs = copies // 2
+                ms = timed(lambda i: ops.hard_forward_smallm_multi([ws[2 * (i % pairs)], ws[2 * (i % pairs) + 1]], x), a.iters,
+                           graph_batch=pairs)
+                gbs = 2 * wbytes / (ms * 1e-3) / 1e9
+                print(json.dumps({"kernel": "lut_smallm_mma_kernel", "case": "smallm gate+up in one launch", "M": M, "N": [N, N], "K": K,
+                                  "us": ms * 1e3, "weight_bytes": 2 * wbytes, "GBps": gbs, "hbm_peak_GBps": hbm, "frac": gbs / hbm,
+                                  "peak_source": src, "timing": "CUDA graph of one launch per pair of weight copies"}))
+            # launches allowed to start under the tail of the previous one (programmatic stream serialization)
+            plz_native.lib().plz_set_smallm_overlap(1)
+            for M in (1, 8):
+                x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+                ms = timed(lambda i: ops.hard_forward_smallm(ws[i % copies], x, out=ys[i & 1][:M]), a.iters, graph_batch=copies)
+                gbs = wbytes / (ms * 1e-3) / 1e9
+                print(json.dumps({"kernel": "lut_smallm_mma_kernel", "case": "smallm, overlapped launches", "M": M, "N": N, "K": K,
+                                  "us": ms * 1e3, "GBps": gbs, "frac": gbs / hbm}))
+                pairs = copies // 2
+                ms = timed(lambda i: ops.hard_forward_smallm_multi([ws[2 * (i % pairs)], ws[2 * (i % pairs) + 1]], x), a.iters,
+                           graph_batch=pairs)
+                gbs = 2 * wbytes / (ms * 1e-3) / 1e9
+                print(json.dumps({"kernel": "lut_smallm_mma_kernel", "case": "smallm gate+up in one launch, overlapped launches", "M": M,
+                                  "us": ms * 1e3, "GBps": gbs, "frac": gbs / hbm}))
+            plz_native.lib().plz_set_smallm_overlap(0)
+            # the kernels that served M <= 16 before the mma.sync one, for comparison
+            plz_native.lib().plz_debug_set_smallm_variant(1)
+            for M in (1, 8):
+                x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+                ms = timed(lambda i: ops.hard_forward_smallm(ws[i % copies], x, out=ys[i & 1][:M]), a.iters, graph_batch=copies)
+                print(json.dumps({"kernel": "lut_gemv_rows_kernel" if M <= 4 else "lut_gemv_kernel (tcgen05 swap-AB)", "case": "smallm, previous kernel",
+                                  "M": M, "N": N, "K": K, "us": ms * 1e3, "GBps": wbytes / (ms * 1e-3) / 1e9}))
+            plz_native.lib().plz_debug_set_smallm_variant(0)
             x = torch.randn(512, K, device=dev).to(torch.bfloat16)
             ms = timed(lambda i: ops.hard_forward(ws[i % copies], x), a.iters)
             fl = 2.0 * 512 * N * K

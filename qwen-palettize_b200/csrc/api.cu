@@ -142,7 +142,11 @@ void plz_debug_set_profile_buffer(void* dev_ptr) { g_prof_buffer = dev_ptr; }
 // Diagnostics: run the persistent kernels on at most `n` CTAs (0 = one per SM), so that small test problems
 // exercise the multi-tile schedule. Not part of the ABI.
 void plz_debug_set_sm_limit(int n) { g_debug_sm_limit = n; }
+// Diagnostics: 1 = keep the small-M forward off the mma.sync kernel (to time the other kernels). Not part of the ABI.
+void plz_debug_set_smallm_variant(int v) { g_debug_smallm_variant = v; }
 int32_t plz_set_cta_limit(int32_t n) { g_debug_sm_limit = n > 0 ? n : 0; return PLZ_OK; }
+
+int32_t plz_set_smallm_overlap(int32_t on) { g_smallm_overlap = on ? 1 : 0; return PLZ_OK; }
 
 int32_t plz_version(void) { return 100; }
 const char* plz_last_error(void) { return g_err; }
@@ -266,6 +270,35 @@ int32_t plz_hard_fwd_smallm(const plz_weight_t* w, const void* x, int64_t ldx, i
     PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     g.sm_count = sms; g.prof = g_prof_buffer;
     return launch_lut_gemv(g, (cudaStream_t)stream);
+}
+
+int32_t plz_hard_fwd_smallm_multi(const plz_weight_t* const* ws, int32_t count, const void* x, int64_t ldx, int32_t M,
+                                  void* const* ys, const int64_t* ldys, void* stream) {
+    if (count < 1 || count > 4 || !ws || !ys || !ldys) { set_last_error("smallm_multi: 1 to 4 weight matrices"); return PLZ_ERR_BAD_SHAPE; }
+    if (M < 0 || M > 16) { set_last_error("plz_hard_fwd_smallm_multi handles 0 <= M <= 16 (M=%d)", M); return PLZ_ERR_BAD_SHAPE; }
+    GemvArgs g[4] = {};
+    int dev = 0, sms = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    for (int i = 0; i < count; ++i) {
+        int rc = check_weight(ws[i], true);
+        if (rc) return rc;
+        if (!ys[i]) { set_last_error("null output pointer"); return PLZ_ERR_NULL; }
+        if (ws[i]->K != ws[0]->K || ws[i]->gs_n != ws[0]->gs_n || ws[i]->gs_k != ws[0]->gs_k) {
+            set_last_error("smallm_multi: all matrices must share K and the palette grouping"); return PLZ_ERR_BAD_SHAPE;
+        }
+        g[i].M = M; g[i].N = ws[i]->N; g[i].K = ws[i]->K; g[i].x = x; g[i].ldx = ldx;
+        g[i].packed = ws[i]->packed; g[i].packed_pitch = ws[i]->packed_pitch; g[i].palette = ws[i]->palette;
+        g[i].gs_n = ws[i]->gs_n; g[i].gs_k = ws[i]->gs_k; g[i].out = ys[i]; g[i].ld_out = ldys[i];
+        g[i].sm_count = sms;
+    }
+    if (M == 0) return PLZ_OK;
+    if (!x) { set_last_error("null activation pointer"); return PLZ_ERR_NULL; }
+    int rc = launch_lut_smallm_mma_multi(g, count, (cudaStream_t)stream);
+    if (rc == PLZ_ERR_UNSUPPORTED)
+        set_last_error("smallm_multi: needs K %% 256 == 0, palette groups of a multiple of 256 columns, 16-byte aligned x rows "
+                       "and M * K small enough for shared memory; call plz_hard_fwd_smallm per matrix instead");
+    return rc;
 }
 
 int32_t plz_dense_fwd(const void* Wd, int64_t ldw, int32_t N, int32_t K, const void* x, int64_t ldx, int32_t M,

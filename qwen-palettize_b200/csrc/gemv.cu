@@ -394,8 +394,15 @@ static int launch_rows(const GemvArgs& a, cudaStream_t stream) {
     return PLZ_OK;
 }
 
+int g_debug_smallm_variant = 0;
+
 int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream) {
     if (a.M <= 0 || a.M > 64) { set_last_error("small-M forward handles 1 <= M <= 64 (M=%d)", a.M); return PLZ_ERR_BAD_SHAPE; }
+    // up to 16 rows: weights go from registers straight into mma.sync fragments, all loads in flight at once
+    if (a.M <= 16 && g_debug_smallm_variant != 1) {
+        const int rc = launch_lut_smallm_mma(a, stream);
+        if (rc != PLZ_ERR_UNSUPPORTED) return rc;
+    }
     // one to four rows, activations fit in shared memory as fp32: the barrier-free CUDA-core kernel is faster
     if (a.M <= 4 && (size_t)a.K * 4 * (a.M <= 1 ? 1 : (a.M <= 2 ? 2 : 4)) <= 160 * 1024 && a.K % 16 == 0 && (a.packed_pitch % 4) == 0) {
         if (a.M <= 1) return launch_rows<1>(a, stream);

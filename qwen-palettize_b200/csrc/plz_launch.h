@@ -64,6 +64,11 @@ struct GemvArgs {
     void* prof;  // optional device buffer of cycle counters (diagnostics)
 };
 int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream);
+// smallm_mma.cu: M <= 16 on mma.sync fragments; PLZ_ERR_UNSUPPORTED = shape outside its domain, use launch_lut_gemv's kernels
+int launch_lut_smallm_mma(const GemvArgs& a, cudaStream_t stream);
+int launch_lut_smallm_mma_multi(const GemvArgs* mats, int count, cudaStream_t stream);  // 1..4 matrices sharing x
+extern int g_smallm_overlap;        // 1: launch the mma.sync small-M kernel with programmatic stream serialization
+extern int g_debug_smallm_variant;  // 0 = automatic choice, 1 = never use the mma.sync kernel (comparisons)
 
 // ---- elementwise.cu ---------------------------------------------------------------------------
 struct SelectParams {

@@ -50,6 +50,8 @@ SIGNATURES = {
     "plz_hard_fwd": [_WP, _P, _I64, _I32, _LP, _P, _P, _I64, _P],
     "plz_hard_fwd_lora_static": [_WP, _P, _I64, _I32, _LP, _P, _I64, _P],
     "plz_hard_fwd_smallm": [_WP, _P, _I64, _I32, _P, _I64, _P],
+    "plz_hard_fwd_smallm_multi": [C.POINTER(_WP), _I32, _P, _I64, _I32, C.POINTER(C.c_void_p), C.POINTER(C.c_int64), _P],
+    "plz_set_smallm_overlap": [_I32],
     "plz_soft_select": [_WP, _GP, _NP, _F, _I32, _P, _I64, _I64, _P],
     "plz_dense_fwd": [_P, _I64, _I32, _I32, _P, _I64, _I32, _LP, _P, _P, _I64, _P],
     "plz_bwd_dx": [_WP, _P, _I64, _I32, _LP, _P, _P, _I64, _P],

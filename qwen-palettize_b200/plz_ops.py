@@ -107,6 +107,20 @@ def hard_forward_smallm(w: PackedWeight, x: torch.Tensor, out: torch.Tensor | No
     return y
 
 
+def hard_forward_smallm_multi(ws, x: torch.Tensor):
+    """[x W_i^T for W_i in ws] in ONE launch (1..4 matrices sharing K and the palette grouping, M <= 16)."""
+    _mat(x, ws[0].K)
+    M, n = x.shape[0], len(ws)
+    ys = [torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device) for w in ws]
+    descs = [w.desc() for w in ws]
+    wp = (C.POINTER(P.Weight) * n)(*[C.pointer(d) for d in descs])
+    yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    ld = (C.c_int64 * n)(*[y.stride(0) for y in ys])
+    P.check(P.lib().plz_hard_fwd_smallm_multi(wp, n, x.data_ptr(), x.stride(0), M, yp, ld, P.stream_ptr()),
+            "plz_hard_fwd_smallm_multi")
+    return ys
+
+
 def soft_select(w: PackedWeight, logits: torch.Tensor, layout: str, noise=None, tau: float = 1.0, seed: int = 0,
                 want_packed: bool = True, want_soft: bool = False):
     """Writes argmax indices into w.packed (if want_packed) and returns W_soft bf16 [N, K] (if want_soft)."""

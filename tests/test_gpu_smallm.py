@@ -9,6 +9,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("M,N,K,gs_n,gs_k", [(1, 256, 256, 1, 256), (1, 9728, 2560, 1, 256), (2, 1000, 2560, 1, 256), (3, 2560, 9728, 1, 256), (8, 1024, 2560, 1, 256), (16, 9728, 2560, 1, 256),
+                                             (12, 4096, 4096, 1, 256), (7, 72, 768, 1, 256), (16, 2560, 9728, 1, 256), (9, 151936 // 16, 2560, 1, 256),
                                              (33, 1000, 512, 1, 64), (64, 2560, 9728, 1, 256), (4, 1024, 1024, 256, 1024)])
 def test_small_m_forward(M, N, K, gs_n, gs_k):
     import plz_ops as ops
@@ -23,3 +24,23 @@ def test_small_m_forward(M, N, K, gs_n, gs_k):
     if N % 8 == 0:
         y_big, _ = ops.hard_forward(w, x.cuda())
         assert_close(y, y_big, "small-M kernel vs tiled kernel", rel=4e-3)
+
+
+@pytest.mark.parametrize("M,Ns,K", [(1, (9728, 9728), 2560), (8, (4096, 1024, 1024), 2560), (16, (264, 72, 1000, 8), 512), (5, (2560,), 9728)])
+def test_small_m_multi(M, Ns, K):
+    """Several matrices that share x in one launch against the oracle and the single-matrix calls (same arithmetic; the
+    order in which the partial sums of the ten 256-column groups meet in shared memory is not fixed, so not bit for bit)."""
+    import plz_ops as ops
+    g = torch.Generator().manual_seed(M + sum(Ns))
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    ws, refs = [], []
+    for N in Ns:
+        idx = torch.randint(0, 4, (N, K), generator=g, dtype=torch.uint8)
+        pal = (torch.randn(N * (K // 256), 4, generator=g) * 0.02).sort(-1).values.to(torch.bfloat16)
+        ws.append(ops.PackedWeight(torch.from_numpy(O.pack_rows(idx.numpy())).cuda(), pal.cuda(), N, K, 1, 256))
+        refs.append(O.hard_forward(x.cpu(), O.dequantize(idx.long(), pal, 1, 256)))
+    ys = ops.hard_forward_smallm_multi(ws, x)
+    check_status()
+    for y, w, ref in zip(ys, ws, refs):
+        assert_close(y, ref, "y of one matrix of the group")
+        assert_close(y, ops.hard_forward_smallm(w, x), "multi vs single launch", rel=4e-3)
