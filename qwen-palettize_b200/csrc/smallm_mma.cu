@@ -5,10 +5,11 @@
 // allocation, no tensor map, no producer / consumer hand-over between warps):
 //
 //   * one CTA per SM owns a contiguous range of weight rows; warp 0 starts one bulk copy (cp.async.bulk, mbarrier
-//     complete_tx) per row into shared memory before anything else happens.  Loading the rows into registers with
+//     complete_tx) per 16-row strip into shared memory before anything else happens, each strip with its own
+//     mbarrier so that its items start as soon as its 16 rows have landed.  Loading the rows into registers with
 //     ordinary 16-byte loads instead was measured to take 4400 cycles just to ISSUE (the SM's outstanding-load
-//     capacity, not HBM, was the limit); the bulk copies are queued outside the load/store path;
-//   * while the rows are in flight all warps stage x in shared memory, in the permuted order below (cp.async);
+//     capacity, not HBM, was the limit), and one bulk copy per row 50 cycles of issue each;
+//   * while the rows are in flight all warps stage x in shared memory, in the permuted order below;
 //   * a work item is 16 rows x 256 input columns (one palette group per row); the items are dealt round-robin to the
 //     16 warps.  Weights go from shared memory straight into mma.sync.m16n8k16 A fragments (the 128-row tcgen05 tile
 //     would be 7/8 padding here): the reduction dimension may be permuted freely as long as x is permuted alike, so

@@ -1,6 +1,6 @@
 """Run one kernel of the hot path a few times on a small case, for `ncu` captures.
 
-    python qwen-palettize_b200/profile_case.py --case fwd|dx|dw|smallm|select|gateup [--M 4096] [--N 9728] [--K 2560] [--iters 3]
+    python qwen-palettize_b200/profile_case.py --case fwd|dx|dw|smallm|smallm8|select|gateup [--M 4096] [--N 9728] [--K 2560] [--iters 3]
 
 The shapes keep the full weight matrix of the benchmark Linear (so per-tile behaviour is the benchmark's) and cut
 the token count; everything held on the device stays under 2 GB.
@@ -19,7 +19,7 @@ import synth  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["fwd", "dx", "dw", "smallm", "select", "gateup"])
+    ap.add_argument("--case", required=True, choices=["fwd", "dx", "dw", "smallm", "smallm8", "select", "gateup"])
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--N", type=int, default=9728)
     ap.add_argument("--K", type=int, default=2560)
@@ -46,6 +46,8 @@ def main():
             ops.backward_dx(w, d["dy"], lora)
         elif a.case == "dw":
             ops.backward_dw_soft(w, d["x"], d["dy"], d["logits"], "nk4", noise=d["noise"], tau=1.0, lora_ws=(t, dt))
+        elif a.case == "smallm8":  # eight rows: the mma.sync kernel (up to 16 rows)
+            ops.hard_forward_smallm(w, d["x"][:8].contiguous())
         elif a.case == "smallm":
             ops.hard_forward_smallm(w, d["x"][: min(a.M, 64)].contiguous())
         else:
