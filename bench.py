@@ -160,7 +160,11 @@ def run_ours(args):
     # selects the plain NCCL all-reduce of the full gradient instead, for comparison)
     scatter = None
     if world > 1 and args.exchange in ("fused", "fused-add"):
-        scatter = dp.LogitGradScatter(N_OUT, K_IN, dev, mode="slots" if args.exchange == "fused" else "add")
+        try:
+            scatter = dp.LogitGradScatter(N_OUT, K_IN, dev, mode="slots" if args.exchange == "fused" else "add")
+        except RuntimeError as e:  # raised on every rank together: peer mappings unavailable, use the NCCL exchange
+            print(f"[bench] fused exchange unavailable ({e}); using the NCCL all-reduce", file=sys.stderr)
+            scatter = None
     # the fused exchange gathers with the copy engines and needs no SM; the NCCL all-reduce does
     comm_sms = args.comm_sms if args.comm_sms >= 0 else (COMM_SMS if scatter is None else (0 if scatter.mode == "slots" else 16))
     sm_count = torch.cuda.get_device_properties(dev).multi_processor_count

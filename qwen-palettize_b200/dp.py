@@ -152,27 +152,43 @@ class LogitGradScatter:
             raise ValueError(f"N={N} must be a multiple of the number of ranks ({self.world})")
         self._stream = torch.cuda.Stream(device=device)
         self._done = torch.zeros(1, dtype=torch.float32, device=device)
-        mine = []
-        # staging: `world` slots of a shard each, or one shard-sized accumulator; then the gathered gradient
-        for nbytes in (N * K * 16 if mode == "slots" else N * K * 16 // self.world, N * K * 16):
-            own, handle = C.c_void_p(), C.create_string_buffer(64)
-            P.check(P.lib().plz_peer_alloc(nbytes, C.byref(own), handle), "plz_peer_alloc")
-            self._own.append(own.value)
-            mine.append(handle.raw)
+        # Every rank reaches every collective below whatever fails locally, and all ranks raise together: a rank that
+        # raised alone would leave the others waiting in the next collective.
+        mine, err = [], None
+        try:
+            # staging: `world` slots of a shard each, or one shard-sized accumulator; then the gathered gradient
+            for nbytes in (N * K * 16 if mode == "slots" else N * K * 16 // self.world, N * K * 16):
+                own, handle = C.c_void_p(), C.create_string_buffer(64)
+                P.check(P.lib().plz_peer_alloc(nbytes, C.byref(own), handle), "plz_peer_alloc")
+                self._own.append(own.value)
+                mine.append(handle.raw)
+        except Exception as e:  # noqa: BLE001
+            err = repr(e)
         handles = [None] * self.world
-        dist.all_gather_object(handles, mine, group=group)
-        for r, hs in enumerate(handles):
-            pair = []
-            for j, h in enumerate(hs):
-                if r == self.rank:
-                    pair.append(self._own[j])
-                    continue
-                p = C.c_void_p()
-                P.check(P.lib().plz_peer_open(C.create_string_buffer(h, 64), C.byref(p)), "plz_peer_open")
-                self._opened.append(p.value)
-                pair.append(p.value)
-            self.ptrs.append(pair[0])
-            self.full_ptrs.append(pair[1])
+        dist.all_gather_object(handles, (mine, err), group=group)
+        errs = [f"rank {r}: {h[1]}" for r, h in enumerate(handles) if h[1]]
+        if not errs:
+            try:
+                for r, (hs, _) in enumerate(handles):
+                    pair = []
+                    for j, h in enumerate(hs):
+                        if r == self.rank:
+                            pair.append(self._own[j])
+                            continue
+                        p = C.c_void_p()
+                        P.check(P.lib().plz_peer_open(C.create_string_buffer(h, 64), C.byref(p)), "plz_peer_open")
+                        self._opened.append(p.value)
+                        pair.append(p.value)
+                    self.ptrs.append(pair[0])
+                    self.full_ptrs.append(pair[1])
+            except Exception as e:  # noqa: BLE001
+                err = repr(e)
+            opened = [None] * self.world
+            dist.all_gather_object(opened, err, group=group)
+            errs = [f"rank {r}: {e}" for r, e in enumerate(opened) if e]
+        if errs:
+            self._release()
+            raise RuntimeError("peer staging memory could not be set up on every rank: " + "; ".join(errs))
         self.full = torch.as_tensor(_DeviceArray(self._own[1], (N, K, 4)), device=device)
 
     def dw(self, w, x, dy, logits, noise, tau, seed=0, lora_ws=None):
@@ -260,16 +276,20 @@ class LogitGradScatter:
             torch.cuda.current_stream(self.device).wait_stream(self._stream)
         return self.full
 
-    def close(self):
+    def _release(self):
         import plz_native as P
+        self.full = None
+        for p in self._opened:
+            P.lib().plz_peer_close(p)
+        self._opened = []
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(group=self.group)  # nobody frees while a peer still has the memory mapped
+        for p in self._own:
+            P.lib().plz_peer_free(p)
+        self._own = []
+
+    def close(self):
         if self.world > 1 and self._own:
             torch.cuda.synchronize(self.device)
             dist.barrier(group=self.group)  # nobody unmaps while a peer may still store
-            self.full = None
-            for p in self._opened:
-                P.check(P.lib().plz_peer_close(p), "plz_peer_close")
-            self._opened = []
-            dist.barrier(group=self.group)
-            for p in self._own:
-                P.check(P.lib().plz_peer_free(p), "plz_peer_free")
-            self._own = []
+            self._release()
