@@ -125,3 +125,29 @@ def test_two_ranks_over_peer_memory(mode):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "SCATTER_OK" in r.stdout
+
+
+def test_peer_memory_helpers_single_process():
+    """plz_peer_alloc gives zeroed device memory and a 64-byte handle; plz_peer_copy / plz_peer_zero are asynchronous on the
+    given stream; plz_peer_free releases it. (Mapping a handle needs a second process: covered by the two-rank test.)"""
+    import ctypes as C
+    import plz_native as P
+    from dp import _DeviceArray
+    n = 1 << 16
+    ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+    P.check(P.lib().plz_peer_alloc(n * 4, C.byref(ptr), handle), "plz_peer_alloc")
+    try:
+        assert any(handle.raw), "handle must be filled"
+        t = torch.as_tensor(_DeviceArray(ptr.value, (n,)), device="cuda:0")
+        assert t.data_ptr() == ptr.value and float(t.abs().sum()) == 0.0
+        src = torch.arange(n, dtype=torch.float32, device="cuda:0")
+        P.check(P.lib().plz_peer_copy(ptr.value, src.data_ptr(), n * 4, P.stream_ptr()), "plz_peer_copy")
+        assert torch.equal(t, src)
+        P.check(P.lib().plz_peer_zero(ptr.value + 4 * 16, (n - 16) * 4, P.stream_ptr()), "plz_peer_zero")
+        assert torch.equal(t[:16], src[:16]) and float(t[16:].abs().sum()) == 0.0
+        assert P.lib().plz_peer_copy(None, src.data_ptr(), 16, P.stream_ptr()) != 0
+        assert P.lib().plz_peer_alloc(0, C.byref(ptr), handle) != 0
+        del t
+    finally:
+        torch.cuda.synchronize()
+        P.check(P.lib().plz_peer_free(ptr.value), "plz_peer_free")

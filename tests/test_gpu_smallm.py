@@ -44,3 +44,44 @@ def test_small_m_multi(M, Ns, K):
     for y, w, ref in zip(ys, ws, refs):
         assert_close(y, ref, "y of one matrix of the group")
         assert_close(y, ops.hard_forward_smallm(w, x), "multi vs single launch", rel=4e-3)
+
+
+def test_small_m_overlapped_launches():
+    """Programmatic dependent launch on: a chain y1 = x W1^T, y2 = y1[:, :K] W2^T ... whose every launch may start under the
+    tail of the previous one must give what the serialized chain gives (the kernel waits for its predecessor before it
+    reads x or writes y)."""
+    import plz_native as P
+    import plz_ops as ops
+    N = K = 2560
+    g = torch.Generator().manual_seed(7)
+    ws = []
+    for _ in range(6):
+        idx = torch.randint(0, 4, (N, K), generator=g, dtype=torch.uint8)
+        pal = (torch.randn(N * (K // 256), 4, generator=g) * 0.02).sort(-1).values.to(torch.bfloat16)
+        ws.append(ops.PackedWeight(torch.from_numpy(O.pack_rows(idx.numpy())).cuda(), pal.cuda(), N, K, 1, 256))
+    x0 = torch.randn(8, K, generator=g).to(torch.bfloat16).cuda()
+
+    def chain():
+        h = x0
+        for w in ws:
+            h = ops.hard_forward_smallm(w, h)
+            h = (h * 16.0).to(torch.bfloat16)  # keep the magnitude; a torch kernel between the launches
+        return h
+
+    want = chain()
+    P.check(P.lib().plz_set_smallm_overlap(1), "plz_set_smallm_overlap")
+    try:
+        outs = [chain() for _ in range(5)]
+        h = x0
+        for w in ws:  # and back to back, without anything in between
+            h = ops.hard_forward_smallm(w, h)
+        torch.cuda.synchronize()
+    finally:
+        P.check(P.lib().plz_set_smallm_overlap(0), "plz_set_smallm_overlap")
+    check_status()
+    for o in outs:
+        assert_close(o, want, "overlapped chain", rel=8e-3)
+    h2 = x0
+    for w in ws:
+        h2 = ops.hard_forward_smallm(w, h2)
+    assert_close(h, h2, "back-to-back overlapped chain", rel=8e-3)
