@@ -198,8 +198,15 @@ class LogitGradScatter:
             r = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=tau, seed=seed, lora_ws=lora_ws)
             self.full = r[0]
             return (r[1], r[2], r[3]) if lora_ws is not None else (r[1], None, None)
-        return ops.backward_dw_soft_scatter(w, x, dy, logits, self.ptrs, self.world, self.rank, noise=noise, tau=tau, seed=seed,
-                                            lora_ws=lora_ws, accumulate=self.mode == "add")
+        # the small gradients are produced as views of ONE flat buffer, which sync_small all-reduces in place: no packing
+        n_pal = w.palette.numel()
+        r = lora_ws[0].shape[1] if lora_ws is not None else 0
+        flat = torch.zeros(n_pal + r * w.K + w.N * r, dtype=torch.float32, device=x.device)
+        outs = (flat[:n_pal].view(-1, 4), flat[n_pal:n_pal + r * w.K].view(r, w.K), flat[n_pal + r * w.K:].view(w.N, r))
+        res = ops.backward_dw_soft_scatter(w, x, dy, logits, self.ptrs, self.world, self.rank, noise=noise, tau=tau, seed=seed,
+                                           lora_ws=lora_ws, accumulate=self.mode == "add", outs=outs)
+        self._flat = (flat, [t for t in res if t is not None])
+        return res
 
     def start(self, small):
         """Steps 2-4 above. `small` (dPalette, dA, dB ...) are sum-all-reduced in place on the current stream; the pushes
@@ -237,6 +244,14 @@ class LogitGradScatter:
     def sync_small(self, small):
         """Step 2: sum-all-reduce `small` in place on the current stream (all ranks' staging stores are complete after it)."""
         small = [t for t in small if t is not None]
+        flat = getattr(self, "_flat", None)
+        if flat is not None and len(flat[1]) == len(small) and all(a is b for a, b in zip(flat[1], small)):
+            # exactly the views handed out by dw(): reduce the flat buffer they live in
+            self._flat = None
+            dist.all_reduce(flat[0], op=dist.ReduceOp.SUM, group=self.group)
+            if self.scale != 1.0:
+                flat[0].mul_(self.scale)
+            return (small, flat[0])
         n = sum(t.numel() for t in small)
         bucket = torch.empty(max(n, 1), dtype=torch.float32, device=self.device)
         o = 0

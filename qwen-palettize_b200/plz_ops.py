@@ -220,15 +220,17 @@ def backward_dw_soft(w: PackedWeight, x: torch.Tensor, dy: torch.Tensor, logits:
 
 
 def backward_dw_soft_scatter(w: PackedWeight, x: torch.Tensor, dy: torch.Tensor, logits: torch.Tensor, stage_ptrs, world: int,
-                             rank: int, noise=None, tau: float = 1.0, seed: int = 0, lora_ws=None, accumulate: bool = False):
+                             rank: int, noise=None, tau: float = 1.0, seed: int = 0, lora_ws=None, accumulate: bool = False,
+                             outs=None):
     """Weight-gradient launch whose epilogue stores this rank's partial dLogits into the owners' staging buffers
     (`stage_ptrs`: the `world` device addresses, as mapped in this process, of the fp32 [world, N/world, K, 4] buffers; with
     accumulate=True of the zeroed fp32 [N/world, K, 4] accumulators that the partials are added to).
-    Returns (dPalette, dA, dB) of THIS rank (fp32, not reduced; dA = dB = None without lora_ws = (t, dt))."""
+    Returns (dPalette, dA, dB) of THIS rank (fp32, not reduced; dA = dB = None without lora_ws = (t, dt)).
+    outs = (dPalette, dA, dB): ZEROED fp32 tensors to accumulate into (e.g. views of one flat all-reduce bucket)."""
     _mat(x, w.K), _mat(dy, w.N)
     M = x.shape[0]
     ld, nd = P.logits_desc(logits, "nk4"), P.noise_desc(noise, "nk4", seed)
-    dpal = torch.zeros(w.palette.numel() // 4, 4, dtype=torch.float32, device=x.device)
+    dpal = outs[0] if outs is not None else torch.zeros(w.palette.numel() // 4, 4, dtype=torch.float32, device=x.device)
     table = (C.c_void_p * world)(*[int(p) for p in stage_ptrs])
     d = w.desc()
     t = dt = da = db = None
@@ -236,8 +238,8 @@ def backward_dw_soft_scatter(w: PackedWeight, x: torch.Tensor, dy: torch.Tensor,
     if lora_ws is not None:
         t, dt = lora_ws
         r = t.shape[1]
-        da = torch.zeros(r, w.K, dtype=torch.float32, device=x.device)
-        db = torch.zeros(w.N, r, dtype=torch.float32, device=x.device)
+        da = outs[1] if outs is not None else torch.zeros(r, w.K, dtype=torch.float32, device=x.device)
+        db = outs[2] if outs is not None else torch.zeros(w.N, r, dtype=torch.float32, device=x.device)
     P.check(P.lib().plz_bwd_dw_soft_scatter(C.byref(d), x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), M, C.byref(ld),
                                             C.byref(nd), float(tau), table, world, rank, 1 if accumulate else 0, dpal.data_ptr(),
                                             t.data_ptr() if t is not None else None, dt.data_ptr() if dt is not None else None, r,
