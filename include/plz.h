@@ -251,6 +251,18 @@ int32_t plz_hard_fwd_norm(const plz_weight_t* w, const void* x, int64_t ldx, int
 int32_t plz_mlp_gate_up_fwd(const plz_weight_t* w_gate, const plz_weight_t* w_up, const void* x, int64_t ldx, int32_t M,
                             const float* row_scale, const void* col_scale, void* act, int64_t ldact, void* stream);
 
+/* Backward of the two element-wise ops above (the Linears between them use plz_bwd_dx / plz_bwd_dw_*):
+ * plz_swiglu_bwd: from the pre-activations gate = h Wg^T, up = h Wu^T (bf16 [M, N], recomputed with plz_hard_fwd_norm
+ *   or kept from an unfused forward) and dAct: dGate = dAct * up * silu'(gate), dUp = dAct * silu(gate)  (bf16 [M, N]).
+ * plz_rmsnorm_bwd: from dH, the gradient with respect to h = rmsnorm(x): dX (bf16 [M, K]) and dG[K] += sum_m dH * x * rstd
+ *   (fp32, ACCUMULATED: zero it first; NULL to skip). g may be NULL (no norm weight).
+ * Semantics: autograd of transformers' Qwen3MLP / Qwen3RMSNorm, which the reference trains through
+ * (scripts/train_qwen.py:1259-1266); no reference kernel exists for them. */
+int32_t plz_swiglu_bwd(const void* gate, int64_t ldg, const void* up, int64_t ldu, const void* dact, int64_t ldd, int32_t M,
+                       int32_t N, void* dgate, int64_t lddg, void* dup, int64_t lddu, void* stream);
+int32_t plz_rmsnorm_bwd(const void* x, int64_t ldx, const void* dh, int64_t lddh, const float* rstd, const void* g, int32_t M,
+                        int32_t K, void* dx, int64_t lddx, float* dg, void* stream);
+
 /* ---- the steps around the Linear in the distillation loop ------------------------------------
  * One fused pass of fp32-master AdamW over a flat parameter of n elements:
  *   g = grad * grad_scale (grad_scale carries the gradient-clipping coefficient and 1/world_size);

@@ -337,3 +337,22 @@ def mlp_gate_up(x: torch.Tensor, w_gate_nk: torch.Tensor, w_up_nk: torch.Tensor,
     g = h @ w_gate_nk.float().t()
     u = h @ w_up_nk.float().t()
     return torch.nn.functional.silu(g) * u
+
+
+def swiglu_backward(gate: torch.Tensor, up: torch.Tensor, dact: torch.Tensor):
+    """fp32 (dGate, dUp) of act = silu(gate) * up. Autograd of transformers' Qwen3MLP activation (no reference kernel:
+    the reference trains through the HuggingFace module, scripts/train_qwen.py:1259-1266)."""
+    g, u, d = gate.float(), up.float(), dact.float()
+    sg = torch.sigmoid(g)
+    return d * u * sg * (1.0 + g * (1.0 - sg)), d * g * sg
+
+
+def rmsnorm_backward(x: torch.Tensor, weight, dh: torch.Tensor, eps: float = 1e-6):
+    """fp32 (dX, dWeight) of h = x * rsqrt(mean(x^2) + eps) * weight given dH (autograd of Qwen3RMSNorm)."""
+    xf, d = x.float(), dh.float()
+    K = xf.shape[-1]
+    rs = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    gd = d if weight is None else d * weight.float()
+    dx = rs * gd - xf * rs.pow(3) * (xf * gd).sum(-1, keepdim=True) / K
+    dw = None if weight is None else (d * xf * rs).sum(0)
+    return dx, dw

@@ -5,6 +5,7 @@
            The weights rotate over enough copies to exceed the 126 MB L2, so every launch reads HBM.
   config0  hard forward at M = 512 (BASELINE config 0): time and TFLOP/s of the tiled tcgen05 kernel.
   select   logits -> packed argmax indices: GB/s on the 16 bytes per weight it reads.
+  swiglu / rmsnorm backward: GB/s on the bytes they read and write.
 
     python qwen-palettize_b200/bench_kernels.py [--iters 200]
 Prints one JSON object per measurement.  Timing: CUDA events on the launching stream around `iters` back-to-back
@@ -140,6 +141,22 @@ def main():
     print(json.dumps({"kernel": "soft_select_kfast_kernel", "case": "select", "N": N, "K": K, "us": ms * 1e3, "bytes": rb,
                       "GBps": rb / (ms * 1e-3) / 1e9, "hbm_peak_GBps": hbm, "frac": rb / (ms * 1e-3) / 1e9 / hbm,
                       "peak_source": src}))
+    # element-wise backward ops around the MLP Linears at the benchmark's token count (inputs larger than L2)
+    M = 16384
+    gate, up, dact = (torch.randn(M, N, device=dev).to(torch.bfloat16) for _ in range(3))
+    ms = timed(lambda i: ops.swiglu_backward(gate, up, dact), 30)
+    rb = 5 * M * N * 2
+    print(json.dumps({"kernel": "swiglu_bwd_kernel", "case": "swiglu backward", "M": M, "N": N, "us": ms * 1e3, "bytes": rb,
+                      "GBps": rb / (ms * 1e-3) / 1e9, "hbm_peak_GBps": hbm, "frac": rb / (ms * 1e-3) / 1e9 / hbm, "peak_source": src}))
+    del gate, up, dact
+    Mx = 65536  # 335 MB per tensor, so that x + dH exceed L2
+    xx, dh = (torch.randn(Mx, K, device=dev).to(torch.bfloat16) for _ in range(2))
+    nw = torch.ones(K, dtype=torch.bfloat16, device=dev)
+    rstd = ops.rms_rstd(xx, 1e-6)
+    ms = timed(lambda i: ops.rmsnorm_backward(xx, dh, rstd, nw), 30)
+    rb = 3 * Mx * K * 2
+    print(json.dumps({"kernel": "rmsnorm_bwd_kernel<5>", "case": "rmsnorm backward", "M": Mx, "K": K, "us": ms * 1e3, "bytes": rb,
+                      "GBps": rb / (ms * 1e-3) / 1e9, "hbm_peak_GBps": hbm, "frac": rb / (ms * 1e-3) / 1e9 / hbm, "peak_source": src}))
     print(json.dumps({"status": list(plz_native.device_status())}))
 
 

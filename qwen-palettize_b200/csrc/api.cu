@@ -612,6 +612,29 @@ static int fused_fwd(int fuse, const plz_weight_t* w, const plz_weight_t* w2, co
     return launch_lut_gemm(g, (cudaStream_t)stream);
 }
 
+int32_t plz_swiglu_bwd(const void* gate, int64_t ldg, const void* up, int64_t ldu, const void* dact, int64_t ldd, int32_t M,
+                       int32_t N, void* dgate, int64_t lddg, void* dup, int64_t lddu, void* stream) {
+    if (M < 0 || N <= 0 || (N & 7)) { set_last_error("swiglu_bwd: N must be a positive multiple of 8"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!gate || !up || !dact || !dgate || !dup) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if ((((uintptr_t)gate | (uintptr_t)up | (uintptr_t)dact | (uintptr_t)dgate | (uintptr_t)dup) & 15) ||
+        ((ldg | ldu | ldd | lddg | lddu) & 7)) {
+        set_last_error("swiglu_bwd: rows must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN;
+    }
+    return launch_swiglu_bwd(gate, ldg, up, ldu, dact, ldd, M, N, dgate, lddg, dup, lddu, (cudaStream_t)stream);
+}
+
+int32_t plz_rmsnorm_bwd(const void* x, int64_t ldx, const void* dh, int64_t lddh, const float* rstd, const void* g, int32_t M,
+                        int32_t K, void* dx, int64_t lddx, float* dg, void* stream) {
+    if (M < 0 || K <= 0 || (K & 1)) { set_last_error("rmsnorm_bwd: K must be even and positive"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !dh || !rstd || !dx) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if ((((uintptr_t)x | (uintptr_t)dh | (uintptr_t)dx | (uintptr_t)g) & 3) || ((ldx | lddh | lddx) & 1)) {
+        set_last_error("rmsnorm_bwd: rows must be 4-byte aligned"); return PLZ_ERR_BAD_ALIGN;
+    }
+    return launch_rmsnorm_bwd(x, ldx, dh, lddh, rstd, g, M, K, dx, lddx, dg, (cudaStream_t)stream);
+}
+
 int32_t plz_hard_fwd_norm(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const float* row_scale,
                           const void* col_scale, void* y, int64_t ldy, void* stream) {
     return fused_fwd(2, w, nullptr, x, ldx, M, row_scale, col_scale, y, ldy, stream);

@@ -100,6 +100,10 @@ struct AdamParams {
 
 int launch_adamw(const AdamParams& p, int grad_dtype, int param_dtype, cudaStream_t stream);
 int launch_reduce_slots(const float* stage, int world, long long shard_elems, float* out, float scale, cudaStream_t stream);
+int launch_swiglu_bwd(const void* gate, long long ldg, const void* up, long long ldu, const void* dact, long long ldd, int M, int N,
+                      void* dgate, long long lddg, void* dup, long long lddu, cudaStream_t stream);
+int launch_rmsnorm_bwd(const void* x, long long ldx, const void* dh, long long lddh, const float* rstd, const void* g, int M, int K,
+                       void* dx, long long lddx, float* dg, cudaStream_t stream);
 int launch_rms_rstd(const void* x, long long ldx, int M, int K, float eps, float* rstd, cudaStream_t stream);
 int launch_distill_loss(const void* s, long long lds, const void* t, long long ldt, int M, int H, float eps, float w_cos,
                         float w_mse, float upstream, float* ws, float* out4, void* ds, long long ldds, int ds_dtype,

@@ -190,6 +190,135 @@ int launch_rms_rstd(const void* x, long long ldx, int M, int K, float eps, float
     return PLZ_OK;
 }
 
+// Backward of act = silu(gate) * up, elementwise, fp32 arithmetic on bf16 operands:
+//   dGate = dAct * up * sigma(gate) * (1 + gate * (1 - sigma(gate))),   dUp = dAct * silu(gate).
+// Eight elements (16 bytes) per thread and step; rows may be pitched.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gate, long long ldg, const __nv_bfloat16* __restrict__ up, long long ldu,
+                  const __nv_bfloat16* __restrict__ dact, long long ldd, int M, int N, __nv_bfloat16* __restrict__ dgate,
+                  long long lddg, __nv_bfloat16* __restrict__ dup, long long lddu) {
+    const int vec_per_row = N >> 3;
+    const long long total = (long long)M * vec_per_row;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int m = (int)(i / vec_per_row), c = (int)(i - (long long)m * vec_per_row) << 3;
+        const uint4 gv = __ldcs(reinterpret_cast<const uint4*>(gate + (long long)m * ldg + c));
+        const uint4 uv = __ldcs(reinterpret_cast<const uint4*>(up + (long long)m * ldu + c));
+        const uint4 dv = __ldcs(reinterpret_cast<const uint4*>(dact + (long long)m * ldd + c));
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+        uint32_t og[4], ou[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float r[2][2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float g = __uint_as_float(h ? (gw[q] & 0xFFFF0000u) : (gw[q] << 16));
+                const float u = __uint_as_float(h ? (uw[q] & 0xFFFF0000u) : (uw[q] << 16));
+                const float d = __uint_as_float(h ? (dw[q] & 0xFFFF0000u) : (dw[q] << 16));
+                const float sg = 1.0f / (1.0f + __expf(-g));
+                r[0][h] = d * u * sg * (1.0f + g * (1.0f - sg));
+                r[1][h] = d * g * sg;
+            }
+            const __nv_bfloat162 a = __floats2bfloat162_rn(r[0][0], r[0][1]), b = __floats2bfloat162_rn(r[1][0], r[1][1]);
+            og[q] = *reinterpret_cast<const uint32_t*>(&a);
+            ou[q] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        __stcs(reinterpret_cast<uint4*>(dgate + (long long)m * lddg + c), make_uint4(og[0], og[1], og[2], og[3]));
+        __stcs(reinterpret_cast<uint4*>(dup + (long long)m * lddu + c), make_uint4(ou[0], ou[1], ou[2], ou[3]));
+    }
+}
+
+int launch_swiglu_bwd(const void* gate, long long ldg, const void* up, long long ldu, const void* dact, long long ldd, int M, int N,
+                      void* dgate, long long lddg, void* dup, long long lddu, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return PLZ_OK;
+    long long blocks = ((long long)M * (N >> 3) + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    swiglu_bwd_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate, ldg, (const __nv_bfloat16*)up, ldu,
+                                                        (const __nv_bfloat16*)dact, ldd, M, N, (__nv_bfloat16*)dgate, lddg,
+                                                        (__nv_bfloat16*)dup, lddu);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
+// Backward of h = x * rstd[m] * g[k] (RMSNorm) given dh:
+//   dx[m, k] = rstd * g[k] * dh[m, k] - x[m, k] * rstd^3 / K * sum_k (x * g * dh)[m, k]
+//   dg[k]   += sum_m dh[m, k] * x[m, k] * rstd[m]                       (fp32, accumulated with atomics)
+// A block of 256 threads walks rows; thread t owns the column pairs 2t + 512 i, keeps its dg partial sums in registers over
+// all its rows and adds them to memory once at the end.
+constexpr int kNormPairsMax = 20;  // K <= 512 * 20
+template <int kNormPairs>  // column pairs per thread: K <= 512 * kNormPairs
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ dh, long long lddh,
+                   const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ g, int M, int K,
+                   __nv_bfloat16* __restrict__ dx, long long lddx, float* __restrict__ dg) {
+    __shared__ float red[8];
+    const int t = threadIdx.x, lane = t & 31, wib = t >> 5;
+    float gk[kNormPairs][2], acc[kNormPairs][2];
+#pragma unroll
+    for (int i = 0; i < kNormPairs; ++i) {
+        const int c = 2 * t + 512 * i;
+        acc[i][0] = acc[i][1] = 0.f;
+        gk[i][0] = gk[i][1] = 0.f;
+        if (c < K) {
+            const float2 v = g ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + c)) : make_float2(1.f, 1.f);
+            gk[i][0] = v.x; gk[i][1] = v.y;
+        }
+    }
+    for (int row = blockIdx.x; row < M; row += gridDim.x) {
+        const float rs = rstd[row];
+        float xv[kNormPairs][2], dv[kNormPairs][2];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < kNormPairs; ++i) {
+            const int c = 2 * t + 512 * i;
+            xv[i][0] = xv[i][1] = dv[i][0] = dv[i][1] = 0.f;
+            if (c < K) {
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + (long long)row * ldx + c));
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dh + (long long)row * lddh + c));
+                xv[i][0] = a.x; xv[i][1] = a.y; dv[i][0] = b.x; dv[i][1] = b.y;
+                s += a.x * gk[i][0] * b.x + a.y * gk[i][1] * b.y;
+                acc[i][0] += b.x * a.x * rs; acc[i][1] += b.y * a.y * rs;
+            }
+        }
+        s = warp_sum_f(s);
+        __syncthreads();  // red is free again (previous row's readers are done)
+        if (lane == 0) red[wib] = s;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += red[w];
+        const float coef = tot * rs * rs * rs / (float)K;
+#pragma unroll
+        for (int i = 0; i < kNormPairs; ++i) {
+            const int c = 2 * t + 512 * i;
+            if (c < K) {
+                const __nv_bfloat162 o = __floats2bfloat162_rn(rs * gk[i][0] * dv[i][0] - xv[i][0] * coef,
+                                                               rs * gk[i][1] * dv[i][1] - xv[i][1] * coef);
+                *reinterpret_cast<__nv_bfloat162*>(dx + (long long)row * lddx + c) = o;
+            }
+        }
+    }
+    if (dg) {
+#pragma unroll
+        for (int i = 0; i < kNormPairs; ++i) {
+            const int c = 2 * t + 512 * i;
+            if (c < K) { atomicAdd(dg + c, acc[i][0]); atomicAdd(dg + c + 1, acc[i][1]); }
+        }
+    }
+}
+
+int launch_rmsnorm_bwd(const void* x, long long ldx, const void* dh, long long lddh, const float* rstd, const void* g, int M, int K,
+                       void* dx, long long lddx, float* dg, cudaStream_t stream) {
+    if (M <= 0) return PLZ_OK;
+    if (K > 512 * kNormPairsMax) { set_last_error("rmsnorm_bwd: K=%d exceeds %d", K, 512 * kNormPairsMax); return PLZ_ERR_TOO_LARGE; }
+    int blocks = M < 148 * 8 ? M : 148 * 8;
+    const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *dp = (const __nv_bfloat16*)dh, *gp = (const __nv_bfloat16*)g;
+    if (K <= 512 * 5) rmsnorm_bwd_kernel<5><<<blocks, 256, 0, stream>>>(xp, ldx, dp, lddh, rstd, gp, M, K, (__nv_bfloat16*)dx, lddx, dg);
+    else if (K <= 512 * 10) rmsnorm_bwd_kernel<10><<<blocks, 256, 0, stream>>>(xp, ldx, dp, lddh, rstd, gp, M, K, (__nv_bfloat16*)dx, lddx, dg);
+    else rmsnorm_bwd_kernel<20><<<blocks, 256, 0, stream>>>(xp, ldx, dp, lddh, rstd, gp, M, K, (__nv_bfloat16*)dx, lddx, dg);
+    PLZ_CUDA_CHECK(cudaGetLastError());
+    return PLZ_OK;
+}
+
 // out[i] = scale * (slot 0 + slot 1 + ... + slot world-1)[i], slots `shard_elems` floats apart: the second half of the
 // reduce-scatter whose first half is the weight-gradient epilogue storing every rank's partial into the owner's slots.
 // Fixed summation order, so every run and every rank count gives the same bits for the same partials.

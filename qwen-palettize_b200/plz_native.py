@@ -72,6 +72,8 @@ SIGNATURES = {
     "plz_bwd_dw_hard": [_WP, _P, _I64, _P, _I64, _I32, _P, _P],
     "plz_lora_bwd": [_P, _I64, _P, _I64, _P, _P, _I32, _I32, _I32, _I32, _P, _P, _P],
     "plz_rms_rstd": [_P, _I64, _I32, _I32, _F, _P, _P],
+    "plz_swiglu_bwd": [_P, _I64, _P, _I64, _P, _I64, _I32, _I32, _P, _I64, _P, _I64, _P],
+    "plz_rmsnorm_bwd": [_P, _I64, _P, _I64, _P, _P, _I32, _I32, _P, _I64, _P, _P],
     "plz_hard_fwd_norm": [_WP, _P, _I64, _I32, _P, _P, _P, _I64, _P],
     "plz_mlp_gate_up_fwd": [_WP, _WP, _P, _I64, _I32, _P, _P, _P, _I64, _P],
     "plz_adamw_step": [_P, _P, _P, _P, _I32, _F, _I64, _F, _F, _F, _F, _F, _I32, _F, _F, _I32, _P, _I32, _P],

@@ -345,3 +345,41 @@ def mlp_gate_up_forward(w_gate: PackedWeight, w_up: PackedWeight, x: torch.Tenso
                                         norm_weight.data_ptr() if norm_weight is not None else None, act.data_ptr(), act.stride(0),
                                         P.stream_ptr()), "plz_mlp_gate_up_fwd")
     return act
+
+
+def swiglu_backward(gate: torch.Tensor, up: torch.Tensor, dact: torch.Tensor):
+    """(dGate, dUp) of act = silu(gate) * up; all bf16 [M, N]."""
+    M, N = gate.shape
+    _mat(gate, N), _mat(up, N), _mat(dact, N)
+    dgate, dup = torch.empty_like(gate), torch.empty_like(up)
+    P.check(P.lib().plz_swiglu_bwd(gate.data_ptr(), gate.stride(0), up.data_ptr(), up.stride(0), dact.data_ptr(), dact.stride(0), M, N,
+                                   dgate.data_ptr(), dgate.stride(0), dup.data_ptr(), dup.stride(0), P.stream_ptr()), "plz_swiglu_bwd")
+    return dgate, dup
+
+
+def rmsnorm_backward(x: torch.Tensor, dh: torch.Tensor, rstd: torch.Tensor, norm_weight: torch.Tensor | None, want_dg: bool = True):
+    """(dX bf16 [M, K], dG fp32 [K] or None) from dH, the gradient with respect to rmsnorm(x)."""
+    M, K = x.shape
+    _mat(x, K), _mat(dh, K)
+    dx = torch.empty_like(x)
+    dg = torch.zeros(K, dtype=torch.float32, device=x.device) if (want_dg and norm_weight is not None) else None
+    P.check(P.lib().plz_rmsnorm_bwd(x.data_ptr(), x.stride(0), dh.data_ptr(), dh.stride(0), rstd.data_ptr(),
+                                    norm_weight.data_ptr() if norm_weight is not None else None, M, K, dx.data_ptr(), dx.stride(0),
+                                    dg.data_ptr() if dg is not None else None, P.stream_ptr()), "plz_rmsnorm_bwd")
+    return dx, dg
+
+
+def mlp_front_backward(w_gate: PackedWeight, w_up: PackedWeight, x: torch.Tensor, rstd, norm_weight, dact: torch.Tensor):
+    """Backward of act = silu(h Wg^T) * (h Wu^T), h = rmsnorm(x), by recomputation: the fused forward keeps neither
+    pre-activation, so gate and up are recomputed (two LUT GEMMs with the norm folded in), then
+    swiglu_backward -> two dX products -> rmsnorm_backward.  Returns (dX, dG, dGate, dUp); dGate / dUp are what the
+    weight-gradient launches of the two Linears take as dY (with h as their x)."""
+    gate = hard_forward_norm(w_gate, x, rstd, norm_weight)
+    up = hard_forward_norm(w_up, x, rstd, norm_weight)
+    dgate, dup = swiglu_backward(gate, up, dact)
+    dh = backward_dx(w_gate, dgate)[0]
+    dh += backward_dx(w_up, dup)[0]
+    if rstd is None:
+        return dh, None, dgate, dup
+    dx, dg = rmsnorm_backward(x, dh, rstd, norm_weight)
+    return dx, dg, dgate, dup
