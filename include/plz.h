@@ -250,6 +250,11 @@ int32_t plz_hard_fwd_norm(const plz_weight_t* w, const void* x, int64_t ldx, int
                           const void* col_scale, void* y, int64_t ldy, void* stream);
 int32_t plz_mlp_gate_up_fwd(const plz_weight_t* w_gate, const plz_weight_t* w_up, const void* x, int64_t ldx, int32_t M,
                             const float* row_scale, const void* col_scale, void* act, int64_t ldact, void* stream);
+/* plz_mlp_gate_up_fwd that also writes the two pre-activations gate = h Wg^T and up = h Wu^T (bf16 [M, N], common pitch
+ * ldgu) from the same accumulators, for a backward that does not recompute them (plz_swiglu_bwd). */
+int32_t plz_mlp_gate_up_fwd_keep(const plz_weight_t* w_gate, const plz_weight_t* w_up, const void* x, int64_t ldx, int32_t M,
+                                 const float* row_scale, const void* col_scale, void* act, int64_t ldact, void* gate, void* up,
+                                 int64_t ldgu, void* stream);
 
 /* Backward of the two element-wise ops above (the Linears between them use plz_bwd_dx / plz_bwd_dw_*):
  * plz_swiglu_bwd: from the pre-activations gate = h Wg^T, up = h Wu^T (bf16 [M, N], recomputed with plz_hard_fwd_norm

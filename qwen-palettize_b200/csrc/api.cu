@@ -586,7 +586,8 @@ int32_t plz_rms_rstd(const void* x, int64_t ldx, int32_t M, int32_t K, float eps
 }
 
 static int fused_fwd(int fuse, const plz_weight_t* w, const plz_weight_t* w2, const void* x, int64_t ldx, int32_t M,
-                     const float* row_scale, const void* col_scale, void* out, int64_t ldo, void* stream) {
+                     const float* row_scale, const void* col_scale, void* out, int64_t ldo, void* stream,
+                     void* gate_out = nullptr, void* up_out = nullptr, int64_t ld_gu = 0) {
     int rc = check_weight(w, true);
     if (rc) return rc;
     if (fuse == 1) {
@@ -608,6 +609,13 @@ static int fused_fwd(int fuse, const plz_weight_t* w, const plz_weight_t* w2, co
     g.gs_n = w->gs_n; g.gs_k = w->gs_k; g.Wn = w->N; g.Wk = w->K;
     g.fuse = fuse; g.col_scale = col_scale; g.row_scale = row_scale;
     if (fuse == 1) { g.packed2 = w2->packed; g.palette2 = w2->palette; }
+    if (gate_out || up_out) {
+        if (!gate_out || !up_out) { set_last_error("gate and up outputs come together"); return PLZ_ERR_NULL; }
+        if ((((uintptr_t)gate_out | (uintptr_t)up_out) & 15) || (ld_gu & 7) || ld_gu < w->N) {
+            set_last_error("gate / up outputs: rows must be 16-byte aligned, pitch >= N"); return PLZ_ERR_BAD_ALIGN;
+        }
+        g.gate_out = gate_out; g.up_out = up_out; g.ld_gu = ld_gu;
+    }
     g.out = out; g.ld_out = ldo; g.alpha = 1.0f;
     return launch_lut_gemm(g, (cudaStream_t)stream);
 }
@@ -643,6 +651,12 @@ int32_t plz_hard_fwd_norm(const plz_weight_t* w, const void* x, int64_t ldx, int
 int32_t plz_mlp_gate_up_fwd(const plz_weight_t* w_gate, const plz_weight_t* w_up, const void* x, int64_t ldx, int32_t M,
                             const float* row_scale, const void* col_scale, void* act, int64_t ldact, void* stream) {
     return fused_fwd(1, w_gate, w_up, x, ldx, M, row_scale, col_scale, act, ldact, stream);
+}
+
+int32_t plz_mlp_gate_up_fwd_keep(const plz_weight_t* w_gate, const plz_weight_t* w_up, const void* x, int64_t ldx, int32_t M,
+                                 const float* row_scale, const void* col_scale, void* act, int64_t ldact, void* gate, void* up,
+                                 int64_t ldgu, void* stream) {
+    return fused_fwd(1, w_gate, w_up, x, ldx, M, row_scale, col_scale, act, ldact, stream, gate, up, ldgu);
 }
 
 int32_t plz_adamw_step(float* master, float* m, float* v, const void* grad, int32_t grad_dtype, float grad_scale, int64_t n,

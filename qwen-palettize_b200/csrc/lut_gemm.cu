@@ -45,6 +45,7 @@ struct LutGemmParams {
     float alpha;
     // fused MLP front end (FUSE != 0): optional RMSNorm factors and, for FUSE == 1, a second weight matrix
     const uint8_t* packed2; const __nv_bfloat16* palette2;  // "up" projection, same shape and grouping as the first
+    __nv_bfloat16* gate_out; __nv_bfloat16* up_out; long long ld_gu;  // FUSE == 1: optional copies of the two pre-activations
     const __nv_bfloat16* col_scale;  // [K]: norm weight g[k], multiplied into the decoded weights (may be null)
     const float* row_scale;          // [M]: 1 / rms(x[m, :]), applied to the accumulator rows (may be null)
     StatusWord* status;
@@ -397,6 +398,22 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             if (lane == 0) mbar_arrive(tmem_empty);
                         }
                         uint32_t o[8];
+                        if (p.gate_out != nullptr && m < p.M) {
+                            // keep rs * gate and rs * up (bf16) for the backward: 32 contiguous bytes of this thread's row each
+                            const int n = n0 + col_half * 64 + c * 16;
+                            if (n < p.Wn) {
+                                uint32_t kg[8], ku[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    kg[i] = pack_bf16x2(__uint_as_float(vg[2 * i]) * rs, __uint_as_float(vg[2 * i + 1]) * rs);
+                                    ku[i] = pack_bf16x2(__uint_as_float(vu[2 * i]) * rs, __uint_as_float(vu[2 * i + 1]) * rs);
+                                }
+                                uint4* dg = reinterpret_cast<uint4*>(p.gate_out + (long long)m * p.ld_gu + n);
+                                uint4* du = reinterpret_cast<uint4*>(p.up_out + (long long)m * p.ld_gu + n);
+                                dg[0] = make_uint4(kg[0], kg[1], kg[2], kg[3]); dg[1] = make_uint4(kg[4], kg[5], kg[6], kg[7]);
+                                du[0] = make_uint4(ku[0], ku[1], ku[2], ku[3]); du[1] = make_uint4(ku[4], ku[5], ku[6], ku[7]);
+                            }
+                        }
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             float a0 = __uint_as_float(vg[2 * i]) * rs, a1 = __uint_as_float(vg[2 * i + 1]) * rs;
@@ -523,6 +540,7 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
     p.Wn = a.Wn; p.Wk = a.Wk;
     p.alpha = a.alpha;
     p.packed2 = (const uint8_t*)a.packed2; p.palette2 = (const __nv_bfloat16*)a.palette2;
+    p.gate_out = (__nv_bfloat16*)a.gate_out; p.up_out = (__nv_bfloat16*)a.up_out; p.ld_gu = a.ld_gu;
     p.col_scale = (const __nv_bfloat16*)a.col_scale; p.row_scale = a.row_scale;
     p.status = device_status_ptr();
     p.prof = (unsigned long long*)a.prof;

@@ -21,6 +21,7 @@ struct LutGemmArgs {
     // fused MLP front end (forward decode mode only): fuse 1 = gate/up pair + SwiGLU (J = 2 N), 2 = one matrix;
     // col_scale bf16 [K] and row_scale fp32 [M] are the RMSNorm factors (either may be null)
     int fuse; const void* packed2; const void* palette2; const void* col_scale; const float* row_scale;
+    void* gate_out; void* up_out; long long ld_gu;  // fuse == 1: optional bf16 copies of the two pre-activations
     int sm_limit;  // > 0: use at most this many CTAs (tests of the multi-tile schedule)
     void* prof;  // optional device buffer of cycle counters, 8 x uint64 per CTA (diagnostics)
 };

@@ -76,6 +76,7 @@ SIGNATURES = {
     "plz_rmsnorm_bwd": [_P, _I64, _P, _I64, _P, _P, _I32, _I32, _P, _I64, _P, _P],
     "plz_hard_fwd_norm": [_WP, _P, _I64, _I32, _P, _P, _P, _I64, _P],
     "plz_mlp_gate_up_fwd": [_WP, _WP, _P, _I64, _I32, _P, _P, _P, _I64, _P],
+    "plz_mlp_gate_up_fwd_keep": [_WP, _WP, _P, _I64, _I32, _P, _P, _P, _I64, _P, _P, _I64, _P],
     "plz_adamw_step": [_P, _P, _P, _P, _I32, _F, _I64, _F, _F, _F, _F, _F, _I32, _F, _F, _I32, _P, _I32, _P],
     "plz_distill_loss": [_P, _I64, _P, _I64, _I32, _I32, _F, _F, _F, _P, _P, _P, _I64, _I32, _P],
 }

@@ -334,12 +334,21 @@ def hard_forward_norm(w: PackedWeight, x: torch.Tensor, rstd: torch.Tensor | Non
     return y
 
 
-def mlp_gate_up_forward(w_gate: PackedWeight, w_up: PackedWeight, x: torch.Tensor, rstd=None, norm_weight=None):
-    """act = silu(h Wg^T) * (h Wu^T), h = rmsnorm(x) (optional), in one launch; bf16 [M, N]."""
+def mlp_gate_up_forward(w_gate: PackedWeight, w_up: PackedWeight, x: torch.Tensor, rstd=None, norm_weight=None, keep: bool = False):
+    """act = silu(h Wg^T) * (h Wu^T), h = rmsnorm(x) (optional), in one launch; bf16 [M, N].
+    keep=True: returns (act, gate, up) with the two pre-activations written by the same launch (for swiglu_backward)."""
     _mat(x, w_gate.K)
     M = x.shape[0]
     act = torch.empty(M, w_gate.N, dtype=torch.bfloat16, device=x.device)
     dg, du = w_gate.desc(), w_up.desc()
+    if keep:
+        gate, up = torch.empty_like(act), torch.empty_like(act)
+        P.check(P.lib().plz_mlp_gate_up_fwd_keep(C.byref(dg), C.byref(du), x.data_ptr(), x.stride(0), M,
+                                                 rstd.data_ptr() if rstd is not None else None,
+                                                 norm_weight.data_ptr() if norm_weight is not None else None, act.data_ptr(),
+                                                 act.stride(0), gate.data_ptr(), up.data_ptr(), gate.stride(0), P.stream_ptr()),
+                "plz_mlp_gate_up_fwd_keep")
+        return act, gate, up
     P.check(P.lib().plz_mlp_gate_up_fwd(C.byref(dg), C.byref(du), x.data_ptr(), x.stride(0), M,
                                         rstd.data_ptr() if rstd is not None else None,
                                         norm_weight.data_ptr() if norm_weight is not None else None, act.data_ptr(), act.stride(0),
@@ -369,13 +378,15 @@ def rmsnorm_backward(x: torch.Tensor, dh: torch.Tensor, rstd: torch.Tensor, norm
     return dx, dg
 
 
-def mlp_front_backward(w_gate: PackedWeight, w_up: PackedWeight, x: torch.Tensor, rstd, norm_weight, dact: torch.Tensor):
-    """Backward of act = silu(h Wg^T) * (h Wu^T), h = rmsnorm(x), by recomputation: the fused forward keeps neither
-    pre-activation, so gate and up are recomputed (two LUT GEMMs with the norm folded in), then
-    swiglu_backward -> two dX products -> rmsnorm_backward.  Returns (dX, dG, dGate, dUp); dGate / dUp are what the
-    weight-gradient launches of the two Linears take as dY (with h as their x)."""
-    gate = hard_forward_norm(w_gate, x, rstd, norm_weight)
-    up = hard_forward_norm(w_up, x, rstd, norm_weight)
+def mlp_front_backward(w_gate: PackedWeight, w_up: PackedWeight, x: torch.Tensor, rstd, norm_weight, dact: torch.Tensor,
+                       gate: torch.Tensor | None = None, up: torch.Tensor | None = None):
+    """Backward of act = silu(h Wg^T) * (h Wu^T), h = rmsnorm(x): swiglu_backward -> two dX products -> rmsnorm_backward.
+    gate / up: the pre-activations kept by mlp_gate_up_forward(keep=True); without them they are recomputed (two LUT
+    GEMMs with the norm folded in).  Returns (dX, dG, dGate, dUp); dGate / dUp are what the weight-gradient launches
+    of the two Linears take as dY (with h as their x)."""
+    if gate is None or up is None:
+        gate = hard_forward_norm(w_gate, x, rstd, norm_weight)
+        up = hard_forward_norm(w_up, x, rstd, norm_weight)
     dgate, dup = swiglu_backward(gate, up, dact)
     dh = backward_dx(w_gate, dgate)[0]
     dh += backward_dx(w_up, dup)[0]

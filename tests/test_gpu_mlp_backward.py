@@ -77,3 +77,30 @@ def test_mlp_front_backward_against_autograd():
     wg, wu = O.swiglu_backward(h @ dense[0].t(), h @ dense[1].t(), dact)
     assert_close(dgate, wg, "dGate", rel=1e-2)
     assert_close(dup, wu, "dUp", rel=1e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 384, 512), (1000, 1280, 768)])
+def test_gate_up_forward_keeps_preactivations(M, N, K):
+    """keep=True: same act as the plain fused launch bit for bit, gate / up equal to the single-matrix norm-folded forward,
+    and the backward from the kept tensors equals the recomputing backward."""
+    import plz_ops as ops
+    g = torch.Generator().manual_seed(M)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    nw = (1.0 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16).cuda()
+    dact = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    ws = []
+    for _ in range(2):
+        idx = torch.randint(0, 4, (N, K), generator=g, dtype=torch.uint8)
+        pal = (torch.randn(N * (K // 256), 4, generator=g) * 0.05).sort(-1).values.to(torch.bfloat16)
+        ws.append(ops.PackedWeight(torch.from_numpy(O.pack_rows(idx.numpy())).cuda(), pal.cuda(), N, K, 1, 256))
+    rstd = ops.rms_rstd(x, 1e-6)
+    act0 = ops.mlp_gate_up_forward(ws[0], ws[1], x, rstd, nw)
+    act, gate, up = ops.mlp_gate_up_forward(ws[0], ws[1], x, rstd, nw, keep=True)
+    check_status()
+    assert torch.equal(act, act0)
+    assert_close(gate, ops.hard_forward_norm(ws[0], x, rstd, nw), "kept gate", rel=4e-3)
+    assert_close(up, ops.hard_forward_norm(ws[1], x, rstd, nw), "kept up", rel=4e-3)
+    a = ops.mlp_front_backward(ws[0], ws[1], x, rstd, nw, dact, gate=gate, up=up)
+    b = ops.mlp_front_backward(ws[0], ws[1], x, rstd, nw, dact)
+    for u, v, name in zip(a, b, ("dX", "dG", "dGate", "dUp")):
+        assert_close(u, v, name + " kept vs recomputed", rel=1e-2)
