@@ -133,7 +133,8 @@ class LogitGradScatter:
 
     With world == 1 nothing is mapped and `dw` falls through to the single-rank entry point."""
 
-    def __init__(self, N: int, K: int, device, group=None, average: bool = False, mode: str = "slots"):
+    def __init__(self, N: int, K: int, device, group=None, average: bool = False, mode: str = "slots",
+                 shard_optimizer: bool = False):
         import ctypes as C
         import plz_native as P
         if mode not in ("slots", "add"):
@@ -145,7 +146,9 @@ class LogitGradScatter:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.scale = 1.0 / self.world if average else 1.0
         self.full = None
-        self.ptrs, self.full_ptrs, self._own, self._opened = [], [], [], []
+        self.ptrs, self.full_ptrs, self.param_ptrs, self._own, self._opened = [], [], [], [], []
+        self.param = None          # shard_optimizer: the peer-visible fp32 [N, K, 4] parameter (index logits)
+        self.shard_optimizer = shard_optimizer
         if self.world == 1:
             return
         if N % self.world:
@@ -157,7 +160,10 @@ class LogitGradScatter:
         mine, err = [], None
         try:
             # staging: `world` slots of a shard each, or one shard-sized accumulator; then the gathered gradient
-            for nbytes in (N * K * 16 if mode == "slots" else N * K * 16 // self.world, N * K * 16):
+            sizes = [N * K * 16 if mode == "slots" else N * K * 16 // self.world, N * K * 16]
+            if shard_optimizer:
+                sizes.append(N * K * 16)  # the parameter itself, so that updated rows can be pushed straight into it
+            for nbytes in sizes:
                 own, handle = C.c_void_p(), C.create_string_buffer(64)
                 P.check(P.lib().plz_peer_alloc(nbytes, C.byref(own), handle), "plz_peer_alloc")
                 self._own.append(own.value)
@@ -181,6 +187,8 @@ class LogitGradScatter:
                         pair.append(p.value)
                     self.ptrs.append(pair[0])
                     self.full_ptrs.append(pair[1])
+                    if shard_optimizer:
+                        self.param_ptrs.append(pair[2])
             except Exception as e:  # noqa: BLE001
                 err = repr(e)
             opened = [None] * self.world
@@ -190,6 +198,13 @@ class LogitGradScatter:
             self._release()
             raise RuntimeError("peer staging memory could not be set up on every rank: " + "; ".join(errs))
         self.full = torch.as_tensor(_DeviceArray(self._own[1], (N, K, 4)), device=device)
+        if shard_optimizer:
+            self.param = torch.as_tensor(_DeviceArray(self._own[2], (N, K, 4)), device=device)
+
+    def shard_rows(self):
+        """[begin, end) of the weight rows this rank owns (reduces, and with shard_optimizer updates)."""
+        rows = self.N // self.world
+        return self.rank * rows, (self.rank + 1) * rows
 
     def dw(self, w, x, dy, logits, noise, tau, seed=0, lora_ws=None):
         """Weight-gradient launch; returns this rank's (dPalette, dA, dB). The dLogits partials are in flight to their owners."""
@@ -208,18 +223,20 @@ class LogitGradScatter:
         self._flat = (flat, [t for t in res if t is not None])
         return res
 
-    def start(self, small):
+    def start(self, small, step_fn=None):
         """Steps 2-4 above. `small` (dPalette, dA, dB ...) are sum-all-reduced in place on the current stream; the pushes
         of the reduced shard run on the side stream. Returns a handle for finish()."""
         if self.world == 1:
             return None
+        if step_fn is not None and self.param is None:
+            raise ValueError("step_fn needs shard_optimizer=True (the parameter must live in peer-visible memory)")
         if self.mode == "add":
-            return self._start_add(small)
+            return self._start_add(small, step_fn)
         handle = self.sync_small(small)
-        self.reduce_and_push()
+        self.reduce_and_push(step_fn)
         return handle
 
-    def _start_add(self, small):
+    def _start_add(self, small, step_fn=None):
         """mode 'add': the owner's accumulator already holds the sum once every rank's kernel has finished, so the whole
         exchange runs on the side stream beside dX: small all-reduce (= all kernels finished) -> copy-engine pushes of the
         accumulator into every rank's `full` (this rank's included) -> accumulator zeroed for the next step -> completion
@@ -234,9 +251,17 @@ class LogitGradScatter:
         with torch.cuda.stream(self._stream):
             handle = self.sync_small(small)
             sp = self._stream.cuda_stream
-            for j in range(self.world):
-                dst = (self.rank + j) % self.world
-                P.check(P.lib().plz_peer_copy(self.full_ptrs[dst] + off, self._own[0], shard_bytes, sp), "plz_peer_copy")
+            if step_fn is not None:
+                # sharded optimizer: update this rank's parameter rows from its accumulator, gather the PARAMETER
+                acc = torch.as_tensor(_DeviceArray(self._own[0], (rows, self.K, 4)), device=self.device)
+                step_fn(self.param[self.rank * rows:(self.rank + 1) * rows], acc)
+                for j in range(1, self.world):
+                    dst = (self.rank + j) % self.world
+                    P.check(P.lib().plz_peer_copy(self.param_ptrs[dst] + off, self._own[2] + off, shard_bytes, sp), "plz_peer_copy")
+            else:
+                for j in range(self.world):
+                    dst = (self.rank + j) % self.world
+                    P.check(P.lib().plz_peer_copy(self.full_ptrs[dst] + off, self._own[0], shard_bytes, sp), "plz_peer_copy")
             P.check(P.lib().plz_peer_zero(self._own[0], shard_bytes, sp), "plz_peer_zero")
             dist.all_reduce(self._done, group=self.group)
         return handle
@@ -267,13 +292,20 @@ class LogitGradScatter:
             o += t.numel()
         return (small, bucket)
 
-    def reduce_and_push(self):
-        """Steps 3 and 4: reduce this rank's slots on the current stream, push the shard to the peers on the side stream."""
+    def reduce_and_push(self, step_fn=None):
+        """Steps 3 and 4: reduce this rank's slots on the current stream, push the shard to the peers on the side stream.
+        step_fn(param_rows, grad_rows) (shard_optimizer): the optimizer step of this rank's rows runs right after the
+        reduction, and the updated PARAMETER rows are gathered instead of the gradient: same bytes on the wire, 1 / world
+        of the optimizer state and work per rank, and `self.full` holds only this rank's rows of the gradient."""
         import plz_native as P
         import plz_ops as ops
         rows = self.N // self.world
         shard = self.full[self.rank * rows:(self.rank + 1) * rows]
         ops.reduce_slots(self.ptrs[self.rank], self.world, shard, self.scale)
+        src_base, dst_ptrs = self._own[1], self.full_ptrs
+        if step_fn is not None:
+            step_fn(self.param[self.rank * rows:(self.rank + 1) * rows], shard)
+            src_base, dst_ptrs = self._own[2], self.param_ptrs
         cur = torch.cuda.current_stream(self.device)
         self._stream.wait_stream(cur)
         shard_bytes = rows * self.K * 16
@@ -281,7 +313,7 @@ class LogitGradScatter:
         with torch.cuda.stream(self._stream):
             for j in range(1, self.world):
                 dst = (self.rank + j) % self.world
-                P.check(P.lib().plz_peer_copy(self.full_ptrs[dst] + off, self._own[1] + off, shard_bytes, self._stream.cuda_stream),
+                P.check(P.lib().plz_peer_copy(dst_ptrs[dst] + off, src_base + off, shard_bytes, self._stream.cuda_stream),
                         "plz_peer_copy")
             dist.all_reduce(self._done, group=self.group)  # leaves only when every rank has issued and finished its pushes
 
@@ -294,6 +326,7 @@ class LogitGradScatter:
     def _release(self):
         import plz_native as P
         self.full = None
+        self.param = None
         for p in self._opened:
             P.lib().plz_peer_close(p)
         self._opened = []

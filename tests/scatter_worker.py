@@ -30,6 +30,10 @@ def main():
     w = ops.PackedWeight(ops.empty_packed(N, K, dev), palette, N, K, 1, 256)
     ops.soft_select(w, logits, "nk4", noise=noise, tau=1.0, want_packed=True)
     mode = sys.argv[1] if len(sys.argv) > 1 else "slots"
+    if mode.endswith("-opt"):
+        ok = sharded_optimizer_check(mode.split("-")[0], dp, ops, w, mine, logits, noise, lora, N, K, dev, rank, world)
+        finish(ok, plz_native, dist, dev, rank)
+        return
     sc = dp.LogitGradScatter(N, K, dev, mode=mode)
     ok = True
     for step in range(4):
@@ -50,9 +54,13 @@ def main():
         small = max(((a - b).abs().max() / b.abs().max()).item() for a, b in ((dpal2, dpal), (da2, da), (db2, db)))
         print(f"rank {rank} step {step}: dLogits rel err {err:.2e} bit-exact {exact}; small grads rel err {small:.2e}", flush=True)
         ok = ok and err < 1e-5 and small < 1e-4 and (exact or world > 2 or mode == "add")
+    sc.close()
+    finish(ok, plz_native, dist, dev, rank)
+
+
+def finish(ok, plz_native, dist, dev, rank):
     st = plz_native.device_status()
     ok = ok and st[0] == 0
-    sc.close()
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()
@@ -60,6 +68,38 @@ def main():
         sys.exit(1)
     if rank == 0:
         print("SCATTER_OK", flush=True)
+
+
+def sharded_optimizer_check(mode, dp, ops, w, mine, logits, noise, lora, N, K, dev, rank, world):
+    """Each rank runs AdamW on its own rows only (state of 1 / world of the size) and the updated parameter rows are
+    gathered; the result must follow a replicated AdamW on the all-reduced gradient of the unfused kernel."""
+    sc = dp.LogitGradScatter(N, K, dev, mode=mode, shard_optimizer=True)
+    sc.param.copy_(logits)
+    r0, r1 = sc.shard_rows()
+    m_s = torch.zeros((r1 - r0) * K * 4, device=dev)
+    v_s = torch.zeros_like(m_s)
+    ref = logits.clone()
+    ref_m, ref_v = torch.zeros(N * K * 4, device=dev), torch.zeros(N * K * 4, device=dev)
+    hp = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-3)
+    ok = True
+    for step in range(4):
+        x = (mine["x"] * (1.0 + 0.25 * step)).to(torch.bfloat16).to(dev)
+        dy = mine["dy"].to(dev)
+        _, t = ops.hard_forward(w, x, lora)
+        dt = ops.lora_dt(lora, dy)
+        dlog = ops.backward_dw_soft(w, x, dy, ref, "nk4", noise=noise, tau=1.0)[0]
+        dist.all_reduce(dlog)
+        ops.adamw_step(ref.view(-1), ref_m, ref_v, dlog.view(-1), step + 1, **hp)
+        small = sc.dw(w, x, dy, sc.param, noise, 1.0, lora_ws=(t, dt))
+        h = sc.start(list(small), step_fn=lambda p, g: ops.adamw_step(p.reshape(-1), m_s, v_s, g.reshape(-1), step + 1, **hp))
+        sc.finish(h)
+        torch.cuda.synchronize()
+        err = (sc.param - ref).abs().max().item()
+        moved = (ref - logits).abs().max().item()
+        print(f"rank {rank} step {step}: sharded-optimizer parameter max abs diff {err:.2e} (moved {moved:.2e})", flush=True)
+        ok = ok and err < 2e-5 and moved > 1e-3
+    sc.close()
+    return ok
 
 
 if __name__ == "__main__":

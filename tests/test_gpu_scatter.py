@@ -117,7 +117,7 @@ def test_scale_and_argument_checks():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["slots", "add"])
+@pytest.mark.parametrize("mode", ["slots", "add", "slots-opt", "add-opt"])
 def test_two_ranks_over_peer_memory(mode):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
