@@ -151,3 +151,25 @@ def test_peer_memory_helpers_single_process():
     finally:
         torch.cuda.synchronize()
         P.check(P.lib().plz_peer_free(ptr.value), "plz_peer_free")
+
+
+def test_single_rank_falls_through():
+    """Without a process group the exchange object maps nothing and dw() is the plain single-rank launch."""
+    import dp
+    import plz_ops as ops
+    base, shards = _rank_inputs(1, 128, 256, 256)
+    dev = torch.device("cuda", 0)
+    logits, noise = base["logits"].to(dev), base["noise"].to(dev)
+    w = ops.PackedWeight(ops.empty_packed(256, 256, dev), base["palette"].reshape(-1, 4).to(dev), 256, 256, 1, 256)
+    ops.soft_select(w, logits, "nk4", noise=noise, tau=1.0, want_packed=True)
+    x, dy = shards[0][0].to(dev), shards[0][1].to(dev)
+    sc = dp.LogitGradScatter(256, 256, dev)
+    assert sc.world == 1 and sc.full is None
+    dpal, da, db = sc.dw(w, x, dy, logits, noise, 1.0)
+    h = sc.start([dpal, da, db])
+    full = sc.finish(h)
+    want, wpal = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=1.0)
+    check_status()
+    assert torch.equal(full, want) and da is None and db is None
+    assert_close(dpal, wpal, "dPalette", rel=1e-5)
+    sc.close()
