@@ -30,7 +30,7 @@ def _rank_inputs(world, M, N, K):
     return base, shards
 
 
-@pytest.mark.parametrize("world,M,N,K", [(2, 256, 512, 512), (4, 200, 1024, 256), (8, 128, 1024, 768)])
+@pytest.mark.parametrize("world,M,N,K", [(2, 256, 512, 512), (4, 200, 1024, 256), (8, 128, 1024, 768), (5, 96, 960, 768)])
 def test_emulated_ranks_bit_exact_and_oracle(world, M, N, K):
     import plz_ops as ops
     base, shards = _rank_inputs(world, M, N, K)
