@@ -1,6 +1,6 @@
 """Run one kernel of the hot path a few times on a small case, for `ncu` captures.
 
-    python qwen-palettize_b200/profile_case.py --case fwd|dx|dw|smallm|smallm8|select|gateup [--M 4096] [--N 9728] [--K 2560] [--iters 3]
+    python qwen-palettize_b200/profile_case.py --case fwd|dx|dw|dwscatter|smallm|smallm8|select|gateup [--M 4096] [--N 9728] [--K 2560] [--iters 3]
 
 The shapes keep the full weight matrix of the benchmark Linear (so per-tile behaviour is the benchmark's) and cut
 the token count; everything held on the device stays under 2 GB.
@@ -19,7 +19,7 @@ import synth  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["fwd", "dx", "dw", "smallm", "smallm8", "select", "gateup"])
+    ap.add_argument("--case", required=True, choices=["fwd", "dx", "dw", "dwscatter", "smallm", "smallm8", "select", "gateup"])
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--N", type=int, default=9728)
     ap.add_argument("--K", type=int, default=2560)
@@ -30,7 +30,12 @@ def main():
     w = ops.PackedWeight(ops.pack_indices(d["idx"].view(torch.int8), n_major=True), pal, a.N, a.K, 1, 256)
     lora = (d["lora_a"], d["lora_b"], 1.0)
     t = dt = w2 = rstd = g = None
-    if a.case == "dw":  # the workspaces the weight-gradient launch takes its dA / dB side items from
+    stage = None
+    if a.case == "dwscatter":
+        # the data-parallel form of the dW launch as rank 0 of 2, both owners' staging buffers in this GPU's memory (ncu
+        # profiles one process; the peer stores become local stores, everything else is the multi-GPU kernel)
+        stage = torch.empty(2, a.N // 2, a.K, 4, dtype=torch.float32, device=d["x"].device)
+    if a.case in ("dw", "dwscatter"):  # the workspaces the weight-gradient launch takes its dA / dB side items from
         t = ops.hard_forward(w, d["x"], lora)[1]
         dt = ops.lora_dt(lora, d["dy"])
     if a.case == "gateup":  # second matrix of the fused gate/up launch and the RMSNorm factors
@@ -44,6 +49,9 @@ def main():
             ops.hard_forward(w, d["x"], lora)
         elif a.case == "dx":
             ops.backward_dx(w, d["dy"], lora)
+        elif a.case == "dwscatter":
+            ops.backward_dw_soft_scatter(w, d["x"], d["dy"], d["logits"], [stage[0].data_ptr(), stage[1].data_ptr()], 2, 0,
+                                         noise=d["noise"], tau=1.0, lora_ws=(t, dt))
         elif a.case == "dw":
             ops.backward_dw_soft(w, d["x"], d["dy"], d["logits"], "nk4", noise=d["noise"], tau=1.0, lora_ws=(t, dt))
         elif a.case == "smallm8":  # eight rows: the mma.sync kernel (up to 16 rows)
