@@ -4,8 +4,10 @@ parameter gradients (index logits, palettes, LoRA factors), which are all sums o
 row-local and never cross ranks.  The reference is single-GPU (no torch.distributed anywhere), so this has no
 counterpart there; correctness is "P ranks on P shards == 1 rank on the whole batch".
 
-The exchange is issued on a side stream right after the weight-gradient kernel, so that it overlaps the dX
-GEMM that follows on the compute stream.
+Two exchanges: GradExchange, a plain NCCL all-reduce issued on a side stream right after the weight-gradient kernel so
+that it overlaps the dX GEMM that follows on the compute stream; and LogitGradScatter, where the weight-gradient
+kernel itself stores its dLogits partials into the owner ranks' memory (reduce-scatter fused into the kernel) and the
+reduced shards, or the parameter rows updated from them, are gathered by the copy engines.
 """
 from __future__ import annotations
 
@@ -130,6 +132,13 @@ class LogitGradScatter:
     mode 'add' replaces the slots and step 3 by vector reductions (red.add.v4.f32, executed by the owner's L2) into one
     shard-sized accumulator per rank: steps 2 and 4 then run entirely on the side stream and nothing of the exchange sits
     on the compute stream, at the price of a run-to-run varying order of the `world` additions per element.
+
+    shard_optimizer=True keeps the parameter itself (`self.param`, fp32 [N, K, 4]) in peer-visible memory; start(small,
+    step_fn=...) then runs step_fn(param_rows, grad_rows) on this rank's rows right after the reduction and gathers the
+    updated PARAMETER rows instead of the gradient (optimizer state and work of 1 / world of the size per rank).
+
+    Every rank starts the column sweep of its weight-gradient kernel at a different owner (a rotation by rank * tiles /
+    world, applied by the launcher), so that at any moment the ranks store into different GPUs.
 
     With world == 1 nothing is mapped and `dw` falls through to the single-rank entry point."""
 
