@@ -166,6 +166,9 @@ def run_ours(args):
             print(f"[bench] fused exchange unavailable ({e}); using the NCCL all-reduce", file=sys.stderr)
             scatter = None
     # the fused exchange gathers with the copy engines and needs no SM; the NCCL all-reduce does
+    # fused slot mode: dX in two row blocks, the first (two rounds of 256-row tiles on 140 SMs) beside the small all-reduce
+    split_rows = args.split_dx if (scatter is not None and scatter.mode == "slots") else 0
+    dx_buf = torch.empty(M_TOK, K_IN, dtype=torch.bfloat16, device=dev) if split_rows > 0 else None
     comm_sms = args.comm_sms if args.comm_sms >= 0 else (COMM_SMS if scatter is None else (0 if scatter.mode == "slots" else 16))
     sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
     phases = ["select", "fwd", "lora_dt", "dw", "dx"]
@@ -192,19 +195,33 @@ def run_ours(args):
             if record: marks[4].record()
             if scatter.mode == "add":
                 h1 = scatter.start([dpal, da, db])
+                if record: xm[0].record(); xm[1].record()
+            elif split_rows > 0:
+                # the first rows of dX run while the small all-reduce (and the wait for the slowest rank's dW behind it)
+                # happens on the side stream; then the slot reduction, then the rest of dX beside the all-gather
+                h1 = scatter.sync_small_beside([dpal, da, db])
+                plz_native.lib().plz_set_cta_limit(sm_count - 8)  # a few SMs for the small collective
+                ops.backward_dx_with_dt(w, dy[:split_rows], lora, dt[:split_rows], out=dx_buf[:split_rows])
+                plz_native.lib().plz_set_cta_limit(0)
+                if record: xm[0].record()
+                scatter.reduce_and_push()
+                if record: xm[1].record()
             else:
                 h1 = scatter.sync_small([dpal, da, db])
-            if record: xm[0].record()
-            if scatter.mode != "add":
+                if record: xm[0].record()
                 scatter.reduce_and_push()
-            if record: xm[1].record()
+                if record: xm[1].record()
         else:
             dlog, dpal, da, db = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=TAU, lora_ws=(t, dt))
             if record: marks[4].record()
             h1 = exch.start([dlog, dpal, da, db])                 # all-reduce, overlaps the dX GEMM below (N > 1 only)
         if world > 1:
             plz_native.lib().plz_set_cta_limit(sm_count - comm_sms)  # leave SMs to NCCL while the exchange runs
-        dx = ops.backward_dx_with_dt(w, dy, lora, dt)             # LUT GEMM (+ LoRA block)
+        if scatter is not None and scatter.mode == "slots" and split_rows > 0:
+            dx = ops.backward_dx_with_dt(w, dy[split_rows:], lora, dt[split_rows:], out=dx_buf[split_rows:])
+            dx = dx_buf
+        else:
+            dx = ops.backward_dx_with_dt(w, dy, lora, dt)         # LUT GEMM (+ LoRA block)
         if world > 1:
             plz_native.lib().plz_set_cta_limit(0)
         if record: marks[5].record()
@@ -345,7 +362,7 @@ def run_ours(args):
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens_per_gpu": M_TOK, "N": N_OUT, "K": K_IN, "lora_rank": RANK,
-                   "parallelism": f"dp{world}", "exchange": ("none" if world == 1 else (f"reduce-scatter fused into the dW epilogue over peer memory ({scatter.mode}) + copy-engine all-gather" if scatter is not None else "NCCL all-reduce")), "l2": "inputs larger than L2 (x+dY 403 MB, logits+noise 797 MB per step)"},
+                   "parallelism": f"dp{world}", "split_dx_rows": split_rows, "exchange": ("none" if world == 1 else (f"reduce-scatter fused into the dW epilogue over peer memory ({scatter.mode}) + copy-engine all-gather" if scatter is not None else "NCCL all-reduce")), "l2": "inputs larger than L2 (x+dY 403 MB, logits+noise 797 MB per step)"},
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": hx.numel() * 2 + hdy.numel() * 2,
                 "d2h_bytes_per_step": sum(h.numel() * 4 for h in hout), "ms_per_step": e2e_ms / args.steps},
@@ -448,6 +465,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--split-dx", type=int, default=0, help="N > 1, fused slot mode: rows of dX computed beside the small all-reduce (0 = off; with it the exch_sync phase "
+                         "contains that first block of dX)")
     ap.add_argument("--comm-sms", type=int, default=-1, help="N > 1: SMs the dX kernel leaves to the exchange (default: built-in)")
     ap.add_argument("--exchange", default="fused", choices=["fused", "fused-add", "allreduce"],
                     help="N > 1: dLogits reduce-scatter fused into the weight-gradient kernel (default) or a plain NCCL all-reduce")

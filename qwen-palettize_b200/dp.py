@@ -275,6 +275,18 @@ class LogitGradScatter:
             dist.all_reduce(self._done, group=self.group)
         return handle
 
+    def sync_small_beside(self, small):
+        """Step 2 on the side stream: the caller puts independent work (part of the dX product) on the compute stream
+        meanwhile, so that neither the collective nor the wait for the slowest rank's kernel is exposed;
+        reduce_and_push() then waits for it."""
+        cur = torch.cuda.current_stream(self.device)
+        self._stream.wait_stream(cur)
+        with torch.cuda.stream(self._stream):
+            handle = self.sync_small(small)
+            self._sync_event = torch.cuda.Event()
+            self._sync_event.record(self._stream)
+        return handle
+
     def sync_small(self, small):
         """Step 2: sum-all-reduce `small` in place on the current stream (all ranks' staging stores are complete after it)."""
         small = [t for t in small if t is not None]
@@ -308,6 +320,10 @@ class LogitGradScatter:
         of the optimizer state and work per rank, and `self.full` holds only this rank's rows of the gradient."""
         import plz_native as P
         import plz_ops as ops
+        ev = getattr(self, "_sync_event", None)
+        if ev is not None:  # step 2 ran on the side stream (sync_small_beside)
+            torch.cuda.current_stream(self.device).wait_event(ev)
+            self._sync_event = None
         rows = self.N // self.world
         shard = self.full[self.rank * rows:(self.rank + 1) * rows]
         ops.reduce_slots(self.ptrs[self.rank], self.world, shard, self.scale)

@@ -167,11 +167,15 @@ def lora_dt(lora, dy: torch.Tensor) -> torch.Tensor:
     return dt
 
 
-def backward_dx_with_dt(w: PackedWeight, dy: torch.Tensor, lora, dt: torch.Tensor) -> torch.Tensor:
-    """dX = dY W + dt A with a precomputed dt."""
+def backward_dx_with_dt(w: PackedWeight, dy: torch.Tensor, lora, dt: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """dX = dY W + dt A with a precomputed dt. Rows are independent, so a caller may compute dX in row blocks (slices of
+    dy, dt and `out`), e.g. to put other work between them."""
     _mat(dy, w.N)
     M = dy.shape[0]
-    dx = torch.empty(M, w.K, dtype=torch.bfloat16, device=dy.device)
+    dx = out if out is not None else torch.empty(M, w.K, dtype=torch.bfloat16, device=dy.device)
+    if out is not None:
+        _mat(out, w.K)
+        assert out.shape[0] == M
     ld = P.lora_desc(*lora)
     d = w.desc()
     P.check(P.lib().plz_bwd_dx_with_dt(C.byref(d), dy.data_ptr(), dy.stride(0), M, C.byref(ld), dt.data_ptr(), dx.data_ptr(),
