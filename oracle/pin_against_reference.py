@@ -25,7 +25,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-REF = os.environ.get("PLZ_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("PLZ_REFERENCE_DIR")
+if not REF or not os.path.isdir(REF):
+    sys.exit("set PLZ_REFERENCE_DIR to a checkout of the reference repository (pkhairkh/qwen-palettize)")
 sys.dont_write_bytecode = True
 sys.path.insert(0, os.path.join(REF, "scripts"))
 sys.path.insert(0, HERE)

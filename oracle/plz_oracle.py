@@ -147,12 +147,15 @@ def soft_weights(logits_nk4: torch.Tensor, noise_nk4: torch.Tensor | None, palet
 # --------------------------------------------------------------------------------------------
 
 def soft_backward(x: torch.Tensor, dy: torch.Tensor, w_fwd_nk: torch.Tensor, p_nk4: torch.Tensor,
-                  palette: torch.Tensor, gs_n: int, gs_k: int):
+                  palette: torch.Tensor, gs_n: int, gs_k: int, dx_fp32: bool = False):
     """x bf16 [M, K], dy bf16 [M, N], w_fwd_nk bf16 [N, K] = the weight the forward multiplied by
     (W_hard under the straight-through estimator, W_soft otherwise).
-    Returns dX bf16 [M, K], dLogits fp32 [N, K, 4] (no 1/tau factor), dPalette fp32 [groups, 4], dW fp32 [N, K]."""
+    Returns dX bf16 [M, K] (fp32, before the rounding, with dx_fp32: a caller that adds the LoRA term rounds the sum),
+    dLogits fp32 [N, K, 4] (no 1/tau factor), dPalette fp32 [groups, 4], dW fp32 [N, K]."""
     n, k = w_fwd_nk.shape
-    dx = (dy.float() @ w_fwd_nk.float()).to(torch.bfloat16)
+    dx = dy.float() @ w_fwd_nk.float()
+    if not dx_fp32:
+        dx = dx.to(torch.bfloat16)
     dw = dy.float().t() @ x.float()  # [N, K]
     c = group_palette(palette, n, k, gs_n, gs_k)
     w_soft = (p_nk4 * c).sum(-1)
@@ -231,8 +234,7 @@ def linear_step(x, dy, logits_nk4, noise_nk4, palette, tau, gs_n, gs_k, lora=Non
         yf = yf + lora_forward(x, *lora)
     out = {"y": yf.to(torch.bfloat16), "hard": hard, "w_fwd": w_fwd}
     if dy is not None:
-        dx, dlogits, dpal, _ = soft_backward(x, dy, w_fwd, p, palette, gs_n, gs_k)
-        dxf = dy.float() @ w_fwd.float()
+        dxf, dlogits, dpal, _ = soft_backward(x, dy, w_fwd, p, palette, gs_n, gs_k, dx_fp32=True)
         if lora is not None:
             dxl, da, db = lora_backward(x, dy, *lora)
             dxf = dxf + dxl

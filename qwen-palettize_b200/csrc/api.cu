@@ -132,19 +132,21 @@ static int lora_up_bwd(const plz_lora_t* l, const void* dY, long long lddy, int 
 
 using namespace plz;
 
+#ifdef PLZ_DIAGNOSTICS
 static void* g_prof_buffer = nullptr;
+#else
+static void* const g_prof_buffer = nullptr;
+#endif
 
 extern "C" {
 
-// Diagnostics: point the LUT GEMM at a device buffer of 8 x uint64 per CTA that receives the MMA thread's
-// cycle counts (wait for TMA, wait for decode, main loop). NULL (default) turns it off. Not part of the ABI.
+#ifdef PLZ_DIAGNOSTICS
+// Diagnostics build only (-DPLZ_DIAGNOSTICS): point the kernels at a device buffer of 8 x uint64 per CTA that receives
+// cycle counts of their issuing threads; keep the small-M forward off the mma.sync kernel. Not part of the ABI.
 void plz_debug_set_profile_buffer(void* dev_ptr) { g_prof_buffer = dev_ptr; }
-// Diagnostics: run the persistent kernels on at most `n` CTAs (0 = one per SM), so that small test problems
-// exercise the multi-tile schedule. Not part of the ABI.
-void plz_debug_set_sm_limit(int n) { g_debug_sm_limit = n; }
-// Diagnostics: 1 = keep the small-M forward off the mma.sync kernel (to time the other kernels). Not part of the ABI.
 void plz_debug_set_smallm_variant(int v) { g_debug_smallm_variant = v; }
-int32_t plz_set_cta_limit(int32_t n) { g_debug_sm_limit = n > 0 ? n : 0; return PLZ_OK; }
+#endif
+int32_t plz_set_cta_limit(int32_t n) { g_cta_limit = n > 0 ? n : 0; return PLZ_OK; }
 
 int32_t plz_set_smallm_overlap(int32_t on) { g_smallm_overlap = on ? 1 : 0; return PLZ_OK; }
 
@@ -410,7 +412,20 @@ static int bwd_dw_common(int epi, const plz_weight_t* w, const void* x, int64_t 
                          int my_rank = 0, int scatter_add = 0) {
     int rc = check_weight(w, epi == EPI_HARD);
     if (rc) return rc;
-    if (M <= 0) { if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; } return PLZ_OK; }
+    if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) {
+        // A rank without tokens contributes zeros. In the slot form of the fused reduce-scatter its slots would otherwise
+        // keep the previous step's partials, which the owners' slot reduction would add again: clear them.
+        if (world > 1 && !scatter_add) {
+            if (w->N % world) { set_last_error("bwd_dw_soft_scatter: N=%d must be a multiple of world=%d", w->N, world); return PLZ_ERR_BAD_SHAPE; }
+            const size_t shard_bytes = (size_t)(w->N / world) * (size_t)w->K * 16u;
+            for (int r = 0; r < world; ++r) {
+                if (!peer_stage[r]) { set_last_error("null peer staging pointer"); return PLZ_ERR_NULL; }
+                PLZ_CUDA_CHECK(cudaMemsetAsync((char*)peer_stage[r] + (size_t)my_rank * shard_bytes, 0, shard_bytes, (cudaStream_t)stream));
+            }
+        }
+        return PLZ_OK;
+    }
     if (!x || !dY) { set_last_error("null activation pointer"); return PLZ_ERR_NULL; }
     TnArgs a = {};
     a.epi = epi; a.M = M;

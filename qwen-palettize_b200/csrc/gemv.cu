@@ -85,7 +85,7 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + bar_off + 8 * (2 * kGvStages + 34));
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
-    const long long t_entry = p.prof ? clock64() : 0;
+    const long long t_entry = PLZ_PROF_ON(p.prof) ? clock64() : 0;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int n_begin = (int)(((long long)blockIdx.x * p.N) / gridDim.x);
@@ -157,14 +157,14 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
                 const uint32_t idesc = make_idesc(128, p.mpad, 0, 0);
                 bool ok = true;
                 long long wait_x = 0, wait_w = 0;
-                const long long t_begin = p.prof ? clock64() : 0;
+                const long long t_begin = PLZ_PROF_ON(p.prof) ? clock64() : 0;
                 for (int it = q; it < nkb && ok; it += kGvMmaWarps) {
                     const int s = it % kGvStages, xs = it % x_stages;
-                    const long long c0 = p.prof ? clock64() : 0;
+                    const long long c0 = PLZ_PROF_ON(p.prof) ? clock64() : 0;
                     ok = mbar_wait(full_x(xs), (it / x_stages) & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
-                    const long long c1 = p.prof ? clock64() : 0;
+                    const long long c1 = PLZ_PROF_ON(p.prof) ? clock64() : 0;
                     if (ok) ok = mbar_wait(full_w(s), (it / kGvStages) & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 2);
-                    if (p.prof) { wait_x += c1 - c0; wait_w += clock64() - c1; }
+                    if (PLZ_PROF_ON(p.prof)) { wait_x += c1 - c0; wait_w += clock64() - c1; }
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t sW = base + s * kGvStageBytes;         // decoded weights: MMA operand A
@@ -182,7 +182,7 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
                     umma_commit(empty_x(xs));
                 }
                 if (ok) umma_commit(accum_full);
-                if (p.prof && q == 0) {
+                if (PLZ_PROF_ON(p.prof) && q == 0) {
                     unsigned long long* q = p.prof + 8ull * blockIdx.x;
                     q[0] = wait_x; q[1] = wait_w; q[2] = clock64() - t_begin; q[3] = t_begin - t_entry;
                 }
@@ -292,7 +292,7 @@ lut_gemv_kernel(const __grid_constant__ CUtensorMap tmX, const GemvParams p) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 8u * p.mpad);
     }
-    if (p.prof && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 4] = clock64() - t_entry;
+    if (PLZ_PROF_ON(p.prof) && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 4] = clock64() - t_entry;
 }
 
 // ---------------------------------------------------------------------------------------------

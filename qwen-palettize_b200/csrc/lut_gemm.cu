@@ -27,7 +27,7 @@
 
 namespace plz {
 
-int g_debug_sm_limit = 0;  // > 0: persistent kernels use at most this many CTAs (plz_debug_set_sm_limit)
+int g_cta_limit = 0;  // > 0: persistent kernels use at most this many CTAs (plz_set_cta_limit)
 
 struct LutGemmParams {
     int M, J, R;         // D is [M, J]; R = reduction length of the main product (multiple of 64)
@@ -208,16 +208,16 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t idesc_main = make_idesc(128, p.mma_n, 0, kBMn ? 1 : 0);
             bool ok = true;
             long long wait_a = 0, wait_b = 0, wait_t = 0;
-            const long long t_begin = p.prof ? clock64() : 0;
+            const long long t_begin = PLZ_PROF_ON(p.prof) ? clock64() : 0;
             int git = 0, lt = 0;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
                 int m0, j0, nmt;
                 tile_origin(t, m0, j0, nmt);
                 if (lt > 0) {
                     // the epilogue warps must have read the previous tile out of TMEM
-                    const long long c0 = p.prof ? clock64() : 0;
+                    const long long c0 = PLZ_PROF_ON(p.prof) ? clock64() : 0;
                     ok = mbar_wait(tmem_empty, (lt - 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 1);
-                    if (p.prof) wait_t += clock64() - c0;
+                    if (PLZ_PROF_ON(p.prof)) wait_t += clock64() - c0;
                     if (!ok) break;
                     tc_fence_after_sync();
                 }
@@ -226,12 +226,12 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const int s = git % C::STAGES;
                     const uint32_t ph = (git / C::STAGES) & 1;
                     const bool extra = it >= nkb;
-                    const long long c0 = p.prof ? clock64() : 0;
+                    const long long c0 = PLZ_PROF_ON(p.prof) ? clock64() : 0;
                     ok = mbar_wait(full_a(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
-                    const long long c1 = p.prof ? clock64() : 0;
+                    const long long c1 = PLZ_PROF_ON(p.prof) ? clock64() : 0;
                     if (ok && kDecode && !extra)
                         ok = mbar_wait(full_b(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 2);
-                    if (p.prof) { wait_a += c1 - c0; wait_b += clock64() - c1; }
+                    if (PLZ_PROF_ON(p.prof)) { wait_a += c1 - c0; wait_b += clock64() - c1; }
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t sA = base + s * C::STAGE_BYTES;
@@ -252,7 +252,7 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 if (ok) umma_commit(accum_full);
             }
-            if (p.prof && q == 0) {
+            if (PLZ_PROF_ON(p.prof) && q == 0) {
                 unsigned long long* q = p.prof + 8ull * blockIdx.x;
                 q[0] = wait_a; q[1] = wait_b; q[2] = wait_t; q[3] = clock64() - t_begin; q[4] = lt;
             }
@@ -554,7 +554,7 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
     }
     PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     if (a.sm_limit > 0 && a.sm_limit < sms) sms = a.sm_limit;
-    if (g_debug_sm_limit > 0 && g_debug_sm_limit < sms) sms = g_debug_sm_limit;
+    if (g_cta_limit > 0 && g_cta_limit < sms) sms = g_cta_limit;
     const int tiles = p.tiles_m * p.tiles_j;
     const int grid = tiles < sms ? tiles : sms;
     p.n_whole = tiles; p.n_items = tiles;

@@ -26,7 +26,7 @@ struct LutGemmArgs {
     void* prof;  // optional device buffer of cycle counters, 8 x uint64 per CTA (diagnostics)
 };
 int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream);
-extern int g_debug_sm_limit;
+extern int g_cta_limit;
 
 // ---- tn_gemm.cu -------------------------------------------------------------------------------
 enum Epi { EPI_STORE = 0, EPI_SOFT = 1, EPI_HARD = 2 };

@@ -15,6 +15,14 @@
 #define PLZ_WAIT_LIMIT_NS 2000000000ull  // 2 s
 #endif
 
+// Cycle counters inside the kernels exist only in a diagnostics build (-DPLZ_DIAGNOSTICS); otherwise the
+// condition is a compile-time false and the counter code disappears.
+#ifdef PLZ_DIAGNOSTICS
+#define PLZ_PROF_ON(ptr) ((ptr) != nullptr)
+#else
+#define PLZ_PROF_ON(ptr) false
+#endif
+
 namespace plz {
 
 // ---------------------------------------------------------------------------

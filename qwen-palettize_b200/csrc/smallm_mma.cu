@@ -108,7 +108,7 @@ lut_smallm_mma_kernel(const SmallmParams p) {
     uint8_t* xs = wsm + (size_t)p.rows_alloc * row_bytes;
     float* acc_s = reinterpret_cast<float*>(xs + (size_t)p.M * p.x_pitch);
 
-    const long long t_entry = p.prof ? clock64() : 0;
+    const long long t_entry = PLZ_PROF_ON(p.prof) ? clock64() : 0;
     // ---- the CTA's packed rows: one bulk copy per 16-row strip (rows of a matrix are contiguous when its pitch is the
     // row size; otherwise, and where a strip crosses into the next matrix, one copy per contiguous piece), each strip
     // with its own mbarrier so that its items can start as soon as its 16 rows have landed
@@ -117,7 +117,7 @@ lut_smallm_mma_kernel(const SmallmParams p) {
         if (lane == 0) { abort_flag[0] = 0u; abort_flag[1] = 0u; }
         mbar_fence_init();
         __syncwarp();
-        if (p.prof && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 5] = clock64() - t_entry;
+        if (PLZ_PROF_ON(p.prof) && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 5] = clock64() - t_entry;
         for (int s = lane; s < strips; s += 32) {
             const int a = s * 16, b = min(rows, a + 16);
             mbar_arrive_expect_tx(bar0 + 8u * s, (uint32_t)(b - a) * row_bytes);
@@ -132,12 +132,12 @@ lut_smallm_mma_kernel(const SmallmParams p) {
             }
         }
     }
-    if (p.prof && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 6] = clock64() - t_entry;
+    if (PLZ_PROF_ON(p.prof) && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 6] = clock64() - t_entry;
     // Programmatic dependent launch (no-ops unless the launch carries the attribute): the next kernel of the stream may
     // start its own weight copies now; this one must not read x, nor write y, before the previous kernel has finished.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (p.prof && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 7] = clock64() - t_entry;
+    if (PLZ_PROF_ON(p.prof) && threadIdx.x == 0) p.prof[8ull * blockIdx.x + 7] = clock64() - t_entry;
     uint2 pa[kBatch], pb[kBatch];
     // (strip, k group) of an item without a division: a warp's items are 16 apart
     auto advance = [&](int& s, int& kg) {
@@ -165,7 +165,7 @@ lut_smallm_mma_kernel(const SmallmParams p) {
     };
     int s_cur = 0, kg_cur = warp;  // (strip, k group) of the warp's next item
     while (kg_cur >= kgs) { kg_cur -= kgs; ++s_cur; }
-    const long long t_a = p.prof ? clock64() : 0;
+    const long long t_a = PLZ_PROF_ON(p.prof) ? clock64() : 0;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     {
         // x in the permuted order of the fragments: 16 bytes = 8 consecutive k of one token = the 8-byte units of k-steps
@@ -197,9 +197,9 @@ lut_smallm_mma_kernel(const SmallmParams p) {
     }
     load_palettes(warp, s_cur, kg_cur);
     for (int i = threadIdx.x; i < rows_pad * 8 * MT; i += kThreads) acc_s[i] = 0.f;
-    const long long t_pro = p.prof ? clock64() : 0;
+    const long long t_pro = PLZ_PROF_ON(p.prof) ? clock64() : 0;
     __syncthreads();
-    const long long t_sync = p.prof ? clock64() : 0;
+    const long long t_sync = PLZ_PROF_ON(p.prof) ? clock64() : 0;
     bool ok = true;
     int strip_ready = -1;  // strips up to this one have been waited for by this warp
 
@@ -270,7 +270,7 @@ lut_smallm_mma_kernel(const SmallmParams p) {
             }
         }
     }
-    const long long t_comp = p.prof ? clock64() : 0;
+    const long long t_comp = PLZ_PROF_ON(p.prof) ? clock64() : 0;
     // a CTA must not exit with copies in flight into its shared memory: every warp has waited for every strip it used;
     // warp 0 waits for all of them (again bounded), and a timeout anywhere disables the output below
     if (warp == 0) {
@@ -285,7 +285,7 @@ lut_smallm_mma_kernel(const SmallmParams p) {
         const int mi = mat_of(p, r0 + r), lr = r0 + r - p.row_start[mi];
         p.out[mi][(long long)m * p.ld_out[mi] + lr] = __float2bfloat16_rn(acc_s[(size_t)r * (8 * MT) + m]);
     }
-    if (p.prof && threadIdx.x == 0) {
+    if (PLZ_PROF_ON(p.prof) && threadIdx.x == 0) {
         unsigned long long* o = p.prof + 8ull * blockIdx.x;
         o[0] = t_a - t_entry; o[1] = t_pro - t_entry; o[2] = t_sync - t_entry; o[3] = t_comp - t_entry;
         o[4] = clock64() - t_entry;

@@ -177,7 +177,6 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                     const uint32_t sB = sA + kTnABytes;
                     mbar_arrive_expect_tx(full(s), kTnABytes + (uint32_t)c_num * 128u);
                     const int m = m_begin + it * 64;
-#pragma unroll
                     const CUtensorMap* mp = (job < 0) ? &tmP : (job == 0 ? &tmS0 : &tmS1);
                     const CUtensorMap* mq = (job < 0) ? &tmQ : (p.side[job].q_is_p ? &tmP : &tmQ);
 #pragma unroll
@@ -633,8 +632,13 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
     }
     p.status = device_status_ptr();
     const int tiles = ((a.I + 127) / 128) * ((a.J + 255) / 256) * p.splits;
-    int sms = a.sm_count > 0 ? a.sm_count : 148;
-    if (g_debug_sm_limit > 0 && g_debug_sm_limit < sms) sms = g_debug_sm_limit;
+    int sms = a.sm_count;
+    if (sms <= 0) {
+        int dev = 0;
+        PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+        PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    if (g_cta_limit > 0 && g_cta_limit < sms) sms = g_cta_limit;
     const int grid = tiles < sms ? tiles : sms;
     p.n_whole = tiles; p.n_items = tiles;
     CUtensorMap tmS0 = tmP, tmS1 = tmP;

@@ -217,11 +217,16 @@ class LogitGradScatter:
 
     def dw(self, w, x, dy, logits, noise, tau, seed=0, lora_ws=None):
         """Weight-gradient launch; returns this rank's (dPalette, dA, dB). The dLogits partials are in flight to their owners."""
+        if self.world > 1 and getattr(self, "_pending", False):
+            # the staging slots / accumulator and `full` of the previous step are still being reduced and gathered
+            raise RuntimeError("LogitGradScatter.dw(): the previous step's exchange has not been finished; call "
+                               "start(...) and finish(handle) before the next dw()")
         import plz_ops as ops
         if self.world == 1:
             r = ops.backward_dw_soft(w, x, dy, logits, "nk4", noise=noise, tau=tau, seed=seed, lora_ws=lora_ws)
             self.full = r[0]
             return (r[1], r[2], r[3]) if lora_ws is not None else (r[1], None, None)
+        self._pending = True
         # the small gradients are produced as views of ONE flat buffer, which sync_small all-reduces in place: no packing
         n_pal = w.palette.numel()
         r = lora_ws[0].shape[1] if lora_ws is not None else 0
@@ -346,6 +351,7 @@ class LogitGradScatter:
         """The compute stream waits for the pushes; afterwards `self.full` holds the reduced dLogits on every rank."""
         if handle is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._stream)
+        self._pending = False
         return self.full
 
     def _release(self):

@@ -27,6 +27,7 @@ from __future__ import annotations
 
 import os
 import sys
+import weakref
 
 import torch
 from torch import Tensor
@@ -59,19 +60,25 @@ def _get_module():
     return _P
 
 
-# packed copies of frozen int8 index buffers, keyed on storage identity and version counter
+# Packed copies of frozen index buffers. An entry belongs to ONE caller tensor object: it holds a weak reference to that
+# tensor and its version counter, and is dropped when the tensor is collected. Only the caller's own int8 / uint8
+# contiguous tensor is cached (the module's `indices_int8` buffer); anything that needs a conversion is a temporary
+# whose address the allocator may hand to the next layer's temporary, so it is packed on every call.
 _PACK_CACHE: dict = {}
 
 
 def _packed_for(indices: Tensor) -> Tensor:
-    key = (indices.data_ptr(), tuple(indices.shape), indices._version, indices.device.index)
+    if indices.dtype not in (torch.int8, torch.uint8) or not indices.is_contiguous():
+        tmp = indices if indices.dtype in (torch.int8, torch.uint8) else indices.to(torch.int8)
+        return _ops.pack_indices(tmp.contiguous(), n_major=False)
+    key = id(indices)
     hit = _PACK_CACHE.get(key)
-    if hit is None:
-        if len(_PACK_CACHE) > 512:
-            _PACK_CACHE.clear()
-        hit = _ops.pack_indices(indices, n_major=False)
-        _PACK_CACHE[key] = hit
-    return hit
+    if hit is not None and hit[0]() is indices and hit[1] == indices._version and hit[2] == indices.data_ptr():
+        return hit[3]
+    packed = _ops.pack_indices(indices, n_major=False)
+    _PACK_CACHE[key] = (weakref.ref(indices, lambda _r, k=key: _PACK_CACHE.pop(k, None)), indices._version,
+                        indices.data_ptr(), packed)
+    return packed
 
 
 def _check_common(x: Tensor, palette: Tensor, K: int, N: int, group_size: int):
@@ -101,8 +108,6 @@ class CUDAFusedLUTLinear(torch.autograd.Function):
     def forward(ctx, x, palette, indices, bias, group_size):
         x = x.contiguous()
         palette = palette.contiguous()
-        indices = indices if indices.dtype == torch.int8 else indices.to(torch.int8)
-        indices = indices.contiguous()
         K, N = indices.shape
         _check_common(x, palette, K, N, group_size)
         w = _ops.PackedWeight(_packed_for(indices), palette.detach(), N, K, group_size, K)

@@ -1,4 +1,5 @@
-"""The benchmark configurations at their FULL sizes (BASELINE configs 0 and 1: N = 9728, K = 2560, M = 512 / 16384).
+"""The two single-Linear benchmark configurations at their FULL sizes (N = 9728, K = 2560; hard forward at M = 512, soft
+forward + full backward at M = 16384).
 
 The CPU oracle cannot run 16384 x 9728 x 2560 three times in a test, so the full-size step is checked through
   * the oracle on SAMPLES that need no approximation: all outputs that belong to 64 sampled weight rows (y columns,

@@ -123,14 +123,14 @@ def test_persistent_schedule_with_few_ctas(limit):
     b = (torch.randn(N, 16, generator=g) * 0.05).to(torch.bfloat16)
     w = _weight(idx, pal, N, K, 1, 256)
     lora = (a.cuda(), b.cuda(), 1.0)
-    P.lib().plz_debug_set_sm_limit(limit)
+    P.lib().plz_set_cta_limit(limit)
     try:
         y, t = ops.hard_forward(w, x.cuda(), lora)
         dx, dt = ops.backward_dx(w, dy.cuda(), lora)
         dpal = ops.backward_dw_hard(w, x.cuda(), dy.cuda())
         check_status()
     finally:
-        P.lib().plz_debug_set_sm_limit(0)
+        P.lib().plz_set_cta_limit(0)
     wd = O.dequantize(idx.long(), pal, 1, 256)
     dxl, _, _ = O.lora_backward(x, dy, a, b, 1.0)
     assert_close(y, (x.float() @ wd.float().t() + O.lora_forward(x, a, b, 1.0)), "y")

@@ -100,12 +100,12 @@ def test_persistent_schedule_with_few_ctas(limit):
     half tiles; all outputs must still match the oracle."""
     import plz_native as P
     d = _inputs(300, 1024, 768, seed=11)
-    P.lib().plz_debug_set_sm_limit(limit)
+    P.lib().plz_set_cta_limit(limit)
     try:
         got = _run(d, 1.0, True)
         check_status()
     finally:
-        P.lib().plz_debug_set_sm_limit(0)
+        P.lib().plz_set_cta_limit(0)
     want = _oracle(d, 1.0, True, noise=d["noise"])
     for k in ("y", "dx", "dlogits", "dpalette", "da", "db"):
         assert_close(got[k], want[k], k)
