@@ -79,6 +79,10 @@ typedef struct plz_noise {
 } plz_noise_t;
 
 int32_t plz_version(void);
+/* Number of kernels this library has launched in this process so far (all entry points, all devices, all threads; not
+ * synchronized across threads: read it from the thread that makes the calls). For callers that report how many device
+ * kernels a region of their program ran. */
+uint64_t plz_launch_count(void);
 const char* plz_last_error(void);
 /* Synchronizes the current device, copies the 4-word status {code, where, count, 0} to the HOST
  * array `out4` (may be NULL) and clears it. Returns PLZ_ERR_DEVICE_WAIT if a kernel gave up. */
@@ -287,6 +291,46 @@ int32_t plz_adamw_step(float* master, float* m, float* v, const void* grad, int3
  * ds (may be NULL) receives upstream * dLoss/ds in ds_dtype (0 fp32, 2 bf16). ws: caller workspace of 4 + 3*M floats. */
 int32_t plz_distill_loss(const void* s, int64_t lds, const void* t, int64_t ldt, int32_t M, int32_t H, float w_cos, float w_mse,
                          float upstream, float* ws, float* out4, void* ds, int64_t ldds, int32_t ds_dtype, void* stream);
+
+/* ---- bias -------------------------------------------------------------------------------------
+ * plz_hard_fwd_bias: y = x W^T + bias with the bias (bf16 [N], 16-byte aligned, may be NULL) added in fp32 before the
+ * bf16 store, as fused_lut_linear_fwd_tc_kernel does (scripts/fused_lut_kernel.cu:512-514; wrapper
+ * scripts/fused_lut_linear_cuda.py:74-117). No LoRA branch (the reference's LoRA wraps a bias-carrying Linear from outside).
+ * plz_col_sum: out[n] += sum_m dY[m, n] (fp32, ACCUMULATED): the bias gradient grad_y.sum(0),
+ * fused_lut_linear_bwd_grad_bias (scripts/fused_lut_kernel.cu:1129). */
+int32_t plz_hard_fwd_bias(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const void* bias, void* y, int64_t ldy,
+                          void* stream);
+int32_t plz_col_sum(const void* dY, int64_t lddy, int32_t M, int32_t N, float* out, void* stream);
+
+/* ---- the soft path with its intermediates as tensors -----------------------------------------
+ * For callers of the reference's lower-level extension functions (scripts/fused_lut_linear_cuda.py:721-732), which pass
+ * P, W_soft / W_hard and a materialised dW between calls. The training path above needs none of them.
+ * Outputs of one matrix, each through element strides (element (n, k[, p])), each may be NULL:
+ *   P fp16 = softmax((logits + g) / tau);  w_soft bf16 = sum_p P[p] palette[p];  w_hard bf16 = palette[hard index]. */
+typedef struct plz_soft_out {
+    void* P; int64_t p_n, p_k, p_p;
+    void* w_soft; int64_t ws_n, ws_k;
+    void* w_hard; int64_t wh_n, wh_k;
+} plz_soft_out_t;
+/* One launch (per 12 matrices) over `count` matrices: the compute_P_W kernels (scripts/fused_lut_kernel.cu:1946-2004) and
+ * their batched form fused_compute_P_W_batched (:2097-2158; the caller passes noise[i]->seed = step_seed ^ (i * 0x9E3779B9u)
+ * to reproduce its per-layer seeds). ws[i]->packed is not used. noise may be NULL (no noise), as may any noise[i].
+ * hard_from_noisy = 1: hard index = argmax of P, i.e. of the NOISED logits, as compute_P_W_hard_aos_kernel does
+ * (:1996-2003); 0: argmax of the plain logits (scripts/triton_soft_forward.py:160-168), the rule of plz_soft_select. */
+int32_t plz_soft_weights(int32_t count, const plz_weight_t* const* ws, const plz_logits_t* const* logits,
+                         const plz_noise_t* const* noise, float tau, int32_t hard_from_noisy, const plz_soft_out_t* const* outs,
+                         void* stream);
+/* Element-wise soft backward from a materialised dW (dtype 0 fp32 / 2 bf16, element (n, k) at dW[n * dw_n + k * dw_k]) and
+ * P (fp16, strides as above): dLogits[p] = dW P[p] (palette[p] - W_soft) into `dlogits` (dtype / strides of a logits
+ * descriptor; NULL to skip) and dPalette[group][p] += dW P[p] (fp32, ACCUMULATED; NULL to skip).
+ * soft_bwd_elementwise_aos_kernel (scripts/fused_lut_kernel.cu:1877-1924), fused_lut_linear_soft_bwd (wrappers in
+ * scripts/fused_lut_linear_cuda.py:275-340). */
+int32_t plz_soft_bwd_elementwise(const plz_weight_t* w, const void* dW, int32_t dw_dtype, int64_t dw_n, int64_t dw_k, const void* P,
+                                 int64_t p_n, int64_t p_k, int64_t p_p, const plz_logits_t* dlogits, float* dpalette, void* stream);
+/* dW[n * dw_n + k * dw_k] += sum_m dY[m, n] x[m, k] (fp32, ACCUMULATED: zero it first): grad_W = x^T grad_y as a tensor
+ * (scripts/fused_lut_linear_cuda.py:952). N and K multiples of 8. */
+int32_t plz_weight_grad(const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M, int32_t N, int32_t K, float* dW,
+                        int64_t dw_n, int64_t dw_k, void* stream);
 
 #ifdef __cplusplus
 }

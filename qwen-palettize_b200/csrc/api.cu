@@ -19,6 +19,8 @@ void set_last_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+unsigned long long g_launch_count = 0;
+
 __device__ StatusWord g_status_word;
 
 StatusWord* device_status_ptr() {
@@ -150,7 +152,8 @@ int32_t plz_set_cta_limit(int32_t n) { g_cta_limit = n > 0 ? n : 0; return PLZ_O
 
 int32_t plz_set_smallm_overlap(int32_t on) { g_smallm_overlap = on ? 1 : 0; return PLZ_OK; }
 
-int32_t plz_version(void) { return 100; }
+int32_t plz_version(void) { return 110; }
+uint64_t plz_launch_count(void) { return g_launch_count; }
 const char* plz_last_error(void) { return g_err; }
 
 int32_t plz_device_status(uint32_t* out4) {
@@ -698,6 +701,97 @@ int32_t plz_distill_loss(const void* s, int64_t lds, const void* t, int64_t ldt,
     if (((uintptr_t)s & 3) || ((uintptr_t)t & 3) || (lds & 1) || (ldt & 1) || (ds && (ldds & 1))) { set_last_error("distill_loss: rows must be 4-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
     if (ds_dtype != 0 && ds_dtype != 2) { set_last_error("distill_loss: gradient dtype must be 0 (fp32) or 2 (bf16)"); return PLZ_ERR_UNSUPPORTED; }
     return launch_distill_loss(s, lds, t, ldt, M, H, 1e-4f, w_cos, w_mse, upstream, ws, out4, ds, ldds, ds_dtype, (cudaStream_t)stream);
+}
+
+// ---- bias, and the soft path with its intermediates as tensors ------------------------------------------
+int32_t plz_hard_fwd_bias(const plz_weight_t* w, const void* x, int64_t ldx, int32_t M, const void* bias, void* y, int64_t ldy,
+                          void* stream) {
+    int rc = check_weight(w, true);
+    if (rc) return rc;
+    if (M < 0) { set_last_error("negative M"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !y) { set_last_error("null activation pointer"); return PLZ_ERR_NULL; }
+    if (bias && ((uintptr_t)bias & 15)) { set_last_error("bias must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    LutGemmArgs g = {};
+    g.bmode = B_DECODE_K; g.M = M; g.J = w->N; g.R = w->K;
+    g.A = x; g.lda = ldx;
+    g.packed = w->packed; g.packed_pitch = w->packed_pitch; g.palette = w->palette;
+    g.gs_n = w->gs_n; g.gs_k = w->gs_k; g.Wn = w->N; g.Wk = w->K;
+    g.fuse = 2; g.bias = bias;
+    g.out = y; g.ld_out = ldy; g.alpha = 1.0f;
+    return launch_lut_gemm(g, (cudaStream_t)stream);
+}
+
+int32_t plz_col_sum(const void* dY, int64_t lddy, int32_t M, int32_t N, float* out, void* stream) {
+    if (M < 0 || N < 0 || (N & 1)) { set_last_error("col_sum: N must be even (M=%d, N=%d)", M, N); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0 || N == 0) return PLZ_OK;
+    if (!dY || !out) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)dY & 3) || (lddy & 1)) { set_last_error("col_sum: rows must be 4-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    return launch_col_sum(dY, lddy, M, N, out, (cudaStream_t)stream);
+}
+
+int32_t plz_soft_weights(int32_t count, const plz_weight_t* const* ws, const plz_logits_t* const* logits,
+                         const plz_noise_t* const* noise, float tau, int32_t hard_from_noisy, const plz_soft_out_t* const* outs,
+                         void* stream) {
+    if (count < 0 || count > 256) { set_last_error("soft_weights: 0 to 256 matrices per call"); return PLZ_ERR_BAD_SHAPE; }
+    if (count == 0) return PLZ_OK;
+    if (!ws || !logits || !outs) { set_last_error("soft_weights: null table"); return PLZ_ERR_NULL; }
+    PwItem items[256];
+    for (int i = 0; i < count; ++i) {
+        int rc = check_weight(ws[i], false);
+        if (rc) return rc;
+        if (!logits[i] || !logits[i]->ptr || !outs[i]) { set_last_error("soft_weights: null logits or output descriptor %d", i); return PLZ_ERR_NULL; }
+        if (logits[i]->dtype != 0 && logits[i]->dtype != 1) { set_last_error("soft_weights: logits dtype must be 0 (fp32) or 1 (fp16)"); return PLZ_ERR_UNSUPPORTED; }
+        PwItem& d = items[i];
+        d = PwItem{};
+        d.logits = logits[i]->ptr; d.ls_n = logits[i]->s_n; d.ls_k = logits[i]->s_k; d.ls_p = logits[i]->s_p;
+        d.logits_f16 = logits[i]->dtype == 1;
+        const plz_noise_t* nz = noise ? noise[i] : nullptr;
+        if (nz) { d.noise = nz->ptr; d.ns_n = nz->s_n; d.ns_k = nz->s_k; d.ns_p = nz->s_p; d.noise_mode = nz->mode; d.seed = nz->seed; }
+        d.palette = (const __nv_bfloat16*)ws[i]->palette; d.gs_n = ws[i]->gs_n; d.gs_k = ws[i]->gs_k;
+        d.n_kgroups = ws[i]->K / ws[i]->gs_k; d.N = ws[i]->N; d.K = ws[i]->K;
+        d.n_fast = (logits[i]->s_n <= logits[i]->s_k) ? 1 : 0;
+        d.P = outs[i]->P; d.p_n = outs[i]->p_n; d.p_k = outs[i]->p_k; d.p_p = outs[i]->p_p;
+        d.w_soft = (__nv_bfloat16*)outs[i]->w_soft; d.ws_n = outs[i]->ws_n; d.ws_k = outs[i]->ws_k;
+        d.w_hard = (__nv_bfloat16*)outs[i]->w_hard; d.wh_n = outs[i]->wh_n; d.wh_k = outs[i]->wh_k;
+    }
+    return launch_soft_weights(items, count, tau, hard_from_noisy ? 1 : 0, (cudaStream_t)stream);
+}
+
+int32_t plz_soft_bwd_elementwise(const plz_weight_t* w, const void* dW, int32_t dw_dtype, int64_t dw_n, int64_t dw_k, const void* P,
+                                 int64_t p_n, int64_t p_k, int64_t p_p, const plz_logits_t* dlogits, float* dpalette, void* stream) {
+    int rc = check_weight(w, false);
+    if (rc) return rc;
+    BwdElemArgs a = {};
+    a.dW = dW; a.dw_dtype = dw_dtype; a.dw_n = dw_n; a.dw_k = dw_k;
+    a.P = P; a.p_n = p_n; a.p_k = p_k; a.p_p = p_p;
+    a.palette = w->palette; a.gs_n = w->gs_n; a.gs_k = w->gs_k; a.N = w->N; a.K = w->K;
+    if (dlogits && dlogits->ptr) {
+        if (dlogits->dtype != 0 && dlogits->dtype != 1) { set_last_error("soft_bwd_elementwise: dLogits dtype must be 0 or 1"); return PLZ_ERR_UNSUPPORTED; }
+        a.dlogits = dlogits->ptr; a.dl_f16 = dlogits->dtype == 1; a.dl_n = dlogits->s_n; a.dl_k = dlogits->s_k; a.dl_p = dlogits->s_p;
+    }
+    a.dpalette = dpalette;
+    return launch_soft_bwd_elementwise(a, (cudaStream_t)stream);
+}
+
+int32_t plz_weight_grad(const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M, int32_t N, int32_t K, float* dW,
+                        int64_t dw_n, int64_t dw_k, void* stream) {
+    if (M < 0 || N <= 0 || K <= 0 || (N % 8) || (K % 8)) { set_last_error("weight_grad: bad shape M=%d N=%d K=%d", M, N, K); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !dY || !dW) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    int dev = 0, sms = 0;
+    PLZ_CUDA_CHECK(cudaGetDevice(&dev));
+    PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    TnArgs a = {};
+    a.epi = EPI_STORE; a.M = M; a.alpha = 1.0f;
+    // the 32 lanes of an epilogue warp are consecutive D rows: give them the axis along which dW is contiguous
+    if (dw_n <= dw_k) { a.I = N; a.J = K; a.P = dY; a.ldp = lddy; a.Q = x; a.ldq = ldx; a.out_si = dw_n; a.out_sj = dw_k; }
+    else { a.I = K; a.J = N; a.P = x; a.ldp = ldx; a.Q = dY; a.ldq = lddy; a.out_si = dw_k; a.out_sj = dw_n; }
+    a.out = dW; a.out_I = a.I; a.out_J = a.J;
+    const int tiles = ((a.I + 127) / 128) * ((a.J + 255) / 256);
+    a.splits = tiles >= sms ? 1 : (sms + tiles - 1) / tiles;
+    a.sm_count = sms;
+    return launch_tn_gemm(a, (cudaStream_t)stream);
 }
 
 }  // extern "C"

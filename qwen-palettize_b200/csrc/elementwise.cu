@@ -59,7 +59,7 @@ int launch_pack_indices(const void* src, long long s_n, long long s_k, int N, in
     if (N <= 0 || K <= 0) return PLZ_OK;
     dim3 grid((N + 31) / 32, ((K + 3) / 4 + 31) / 32);
     pack_indices_kernel<<<grid, 256, 0, stream>>>((const int8_t*)src, s_n, s_k, N, K, (uint8_t*)dst, pitch);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 
@@ -84,7 +84,7 @@ int launch_unpack_indices(const void* src, long long pitch, int N, int K, void* 
     if (total <= 0) return PLZ_OK;
     unpack_indices_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const uint8_t*)src, pitch, N, K,
                                                                                (int8_t*)dst, s_n, s_k);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 
@@ -131,7 +131,7 @@ int launch_dequant(const void* packed, long long pitch, const void* palette, int
     dequant_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
         (const uint8_t*)packed, pitch, (const __nv_bfloat16*)palette, gs_n, gs_k, K / gs_k, N, K,
         (__nv_bfloat16*)dst, d_n, d_k);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 
@@ -267,7 +267,7 @@ int launch_soft_select(const SelectParams& p, int logits_f16, cudaStream_t strea
         if (logits_f16) soft_select_kfast_kernel<__half><<<grid, 256, 0, stream>>>(p);
         else soft_select_kfast_kernel<float><<<grid, 256, 0, stream>>>(p);
     }
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 

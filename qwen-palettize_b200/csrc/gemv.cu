@@ -390,7 +390,7 @@ static int launch_rows(const GemvArgs& a, cudaStream_t stream) {
     kern<<<grid, 512, smem, stream>>>((const __nv_bfloat16*)a.x, a.ldx, a.M, a.N, a.K, (const uint8_t*)a.packed,
                                       a.packed_pitch, (const __nv_bfloat16*)a.palette, a.gs_n, a.gs_k, shift, a.K / a.gs_k,
                                       (__nv_bfloat16*)a.out, a.ld_out);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 
@@ -444,7 +444,7 @@ int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream) {
         attr_smem[dev & 63] = 227 * 1024;
     }
     lut_gemv_kernel<<<grid, kGvThreads, smem, stream>>>(tmX, p);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 

@@ -48,6 +48,7 @@ struct LutGemmParams {
     __nv_bfloat16* gate_out; __nv_bfloat16* up_out; long long ld_gu;  // FUSE == 1: optional copies of the two pre-activations
     const __nv_bfloat16* col_scale;  // [K]: norm weight g[k], multiplied into the decoded weights (may be null)
     const float* row_scale;          // [M]: 1 / rms(x[m, :]), applied to the accumulator rows (may be null)
+    const __nv_bfloat16* bias;       // FUSE == 2: [J], added in fp32 before the bf16 store (may be null)
     StatusWord* status;
     unsigned long long* prof;  // optional [gridDim][8] cycle counters of the MMA thread (diagnostics)
 };
@@ -471,6 +472,32 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             __syncwarp();
                             if (lane == 0) mbar_arrive(tmem_empty);
                         }
+                        if (FUSE == 2 && p.bias != nullptr) {
+                            // bias in fp32 before the rounding (scripts/fused_lut_kernel.cu:512-514); columns past J are
+                            // clipped by the TMA store, so only the loads need the bound
+                            const int jc = j0 + col + c * 32;
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                uint4 bb = make_uint4(0u, 0u, 0u, 0u);
+                                if (jc + g * 8 < p.J) bb = __ldg(reinterpret_cast<const uint4*>(p.bias + jc + g * 8));
+                                const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    v[g * 8 + 2 * i] = __float_as_uint(__uint_as_float(v[g * 8 + 2 * i]) * scale + __uint_as_float(bw[i] << 16));
+                                    v[g * 8 + 2 * i + 1] = __float_as_uint(__uint_as_float(v[g * 8 + 2 * i + 1]) * scale + __uint_as_float(bw[i] & 0xFFFF0000u));
+                                }
+                            }
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                uint4 o;
+                                o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+                                o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+                                o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+                                o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+                                *reinterpret_cast<uint4*>(stage + swz128(lane, c * 4 + g)) = o;
+                            }
+                            continue;
+                        }
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
                             uint4 o;
@@ -542,6 +569,7 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
     p.packed2 = (const uint8_t*)a.packed2; p.palette2 = (const __nv_bfloat16*)a.palette2;
     p.gate_out = (__nv_bfloat16*)a.gate_out; p.up_out = (__nv_bfloat16*)a.up_out; p.ld_gu = a.ld_gu;
     p.col_scale = (const __nv_bfloat16*)a.col_scale; p.row_scale = a.row_scale;
+    p.bias = (const __nv_bfloat16*)a.bias;
     p.status = device_status_ptr();
     p.prof = (unsigned long long*)a.prof;
     auto kern = lut_gemm_kernel<MT, BMODE, NARROW, FUSE>;
@@ -564,7 +592,7 @@ static int launch_t(const LutGemmArgs& a, cudaStream_t stream) {
         if (tiles > grid && rem > 0 && 2 * rem <= grid) { p.n_whole = tiles - rem; p.n_items = p.n_whole + 2 * rem; }
     }
     kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, tmD, p);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 

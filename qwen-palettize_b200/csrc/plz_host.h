@@ -44,4 +44,13 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t c
         }                                                                               \
     } while (0)
 
+// Every kernel launch of the library is followed by this: the launch error check, and a process-wide launch counter
+// (plz_launch_count) so that a caller can state how many kernels of this library a region of its program ran.
+extern unsigned long long g_launch_count;
+#define PLZ_LAUNCH_CHECK()                       \
+    do {                                         \
+        PLZ_CUDA_CHECK(cudaGetLastError());      \
+        ++plz::g_launch_count;                   \
+    } while (0)
+
 }  // namespace plz

@@ -22,6 +22,7 @@ struct LutGemmArgs {
     // col_scale bf16 [K] and row_scale fp32 [M] are the RMSNorm factors (either may be null)
     int fuse; const void* packed2; const void* palette2; const void* col_scale; const float* row_scale;
     void* gate_out; void* up_out; long long ld_gu;  // fuse == 1: optional bf16 copies of the two pre-activations
+    const void* bias;  // fuse == 2: optional bf16 [J], added in fp32 before the bf16 store
     int sm_limit;  // > 0: use at most this many CTAs (tests of the multi-tile schedule)
     void* prof;  // optional device buffer of cycle counters, 8 x uint64 per CTA (diagnostics)
 };
@@ -88,6 +89,29 @@ int launch_unpack_indices(const void* src, long long pitch, int N, int K, void* 
                           cudaStream_t stream);
 int launch_dequant(const void* packed, long long pitch, const void* palette, int gs_n, int gs_k, int N, int K,
                    void* dst, long long d_n, long long d_k, cudaStream_t stream);
+
+// ---- soft_tensors.cu ---------------------------------------------------------------------------
+// One matrix of a (batched) soft-weight pass; every tensor through element strides, any output may be null.
+struct PwItem {
+    const void* logits; long long ls_n, ls_k, ls_p; int logits_f16;
+    const float* noise; long long ns_n, ns_k, ns_p; int noise_mode; uint32_t seed;
+    const __nv_bfloat16* palette; int gs_n, gs_k, n_kgroups;
+    int N, K, n_fast;  // n_fast: consecutive threads walk n (planar (4, K, N) logits), else k
+    void* P; long long p_n, p_k, p_p;                 // fp16
+    __nv_bfloat16* w_soft; long long ws_n, ws_k;
+    __nv_bfloat16* w_hard; long long wh_n, wh_k;
+};
+int launch_soft_weights(const PwItem* items, int count, float tau, int hard_from_noisy, cudaStream_t stream);
+struct BwdElemArgs {
+    const void* dW; int dw_dtype; long long dw_n, dw_k;
+    const void* P; long long p_n, p_k, p_p;
+    const void* palette; int gs_n, gs_k;
+    int N, K;
+    void* dlogits; int dl_f16; long long dl_n, dl_k, dl_p;
+    float* dpalette;
+};
+int launch_soft_bwd_elementwise(const BwdElemArgs& a, cudaStream_t stream);
+int launch_col_sum(const void* dY, long long ld, int M, int N, float* out, cudaStream_t stream);
 
 // ---- train_ops.cu ------------------------------------------------------------------------------
 struct AdamParams {

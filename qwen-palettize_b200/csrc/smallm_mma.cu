@@ -379,6 +379,7 @@ int launch_lut_smallm_mma_multi(const GemvArgs* mats, int count, cudaStream_t st
     cfg.attrs = attr; cfg.numAttrs = g_smallm_overlap ? 1 : 0;
     if (mt == 1) PLZ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, lut_smallm_mma_kernel<1>, p));
     else PLZ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, lut_smallm_mma_kernel<2>, p));
+    ++g_launch_count;
     return PLZ_OK;
 }
 

@@ -551,7 +551,7 @@ static int launch_tn_t(const TnArgs& a, const TnParams& p, const CUtensorMap& tm
         attr_set[dev & 63] = true;
     }
     kern<<<grid, kTnThreads, kTnSmemBytes, stream>>>(tmP, tmQ, tmS0, tmS1, p);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 

@@ -56,7 +56,7 @@ int launch_adamw(const AdamParams& p, int grad_dtype, int param_dtype, cudaStrea
         if (param_dtype == 0) PLZ_ADAM(__nv_bfloat16, float); else if (param_dtype == 1) PLZ_ADAM(__nv_bfloat16, __half); else PLZ_ADAM(__nv_bfloat16, __nv_bfloat16);
     }
 #undef PLZ_ADAM
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 
@@ -151,14 +151,14 @@ int launch_distill_loss(const void* s, long long lds, const void* t, long long l
     int blocks = (M + 7) / 8;
     if (blocks > 148 * 8) blocks = 148 * 8;
     distill_stats_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)s, lds, (const __nv_bfloat16*)t, ldt, M, H, eps, ws);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     if (ds_dtype == 0)
         distill_grad_kernel<float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)s, lds, (const __nv_bfloat16*)t, ldt, M, H, eps,
                                                                 w_cos, w_mse, upstream, ws, out4, (float*)ds, ldds);
     else
         distill_grad_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)s, lds, (const __nv_bfloat16*)t, ldt, M, H,
                                                                         eps, w_cos, w_mse, upstream, ws, out4, (__nv_bfloat16*)ds, ldds);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 
@@ -186,7 +186,7 @@ int launch_rms_rstd(const void* x, long long ldx, int M, int K, float eps, float
     int blocks = (M + 7) / 8;
     if (blocks > 148 * 8) blocks = 148 * 8;
     rms_rstd_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, M, K, eps, rstd);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 
@@ -235,7 +235,7 @@ int launch_swiglu_bwd(const void* gate, long long ldg, const void* up, long long
     swiglu_bwd_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate, ldg, (const __nv_bfloat16*)up, ldu,
                                                         (const __nv_bfloat16*)dact, ldd, M, N, (__nv_bfloat16*)dgate, lddg,
                                                         (__nv_bfloat16*)dup, lddu);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 
@@ -315,7 +315,7 @@ int launch_rmsnorm_bwd(const void* x, long long ldx, const void* dh, long long l
     if (K <= 512 * 5) rmsnorm_bwd_kernel<5><<<blocks, 256, 0, stream>>>(xp, ldx, dp, lddh, rstd, gp, M, K, (__nv_bfloat16*)dx, lddx, dg);
     else if (K <= 512 * 10) rmsnorm_bwd_kernel<10><<<blocks, 256, 0, stream>>>(xp, ldx, dp, lddh, rstd, gp, M, K, (__nv_bfloat16*)dx, lddx, dg);
     else rmsnorm_bwd_kernel<20><<<blocks, 256, 0, stream>>>(xp, ldx, dp, lddh, rstd, gp, M, K, (__nv_bfloat16*)dx, lddx, dg);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 
@@ -342,7 +342,7 @@ int launch_reduce_slots(const float* stage, int world, long long shard_elems, fl
     long long blocks = (vec + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     reduce_slots_kernel<<<(int)blocks, 256, 0, stream>>>((const float4*)stage, world, vec, (float4*)out, scale);
-    PLZ_CUDA_CHECK(cudaGetLastError());
+    PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
 

@@ -54,10 +54,10 @@ def _next_soft_step_seed() -> int:
 
 
 def _get_module():
-    """The reference returns its JIT-built pybind extension here; this returns the loaded C-ABI library
-    binding (raises if libplz.so has not been built)."""
+    """The reference returns its JIT-built pybind extension here (scripts/fused_lut_linear_cuda.py:742-749); this returns
+    an object with the same ten functions, served by libplz.so (raises if the library has not been built)."""
     _P.lib()
-    return _P
+    return _Extension
 
 
 # Packed copies of frozen index buffers. An entry belongs to ONE caller tensor object: it holds a weak reference to that
@@ -94,6 +94,12 @@ def _check_common(x: Tensor, palette: Tensor, K: int, N: int, group_size: int):
         raise RuntimeError(f"G mismatch: N//GS={N // group_size} vs palette.size(0)={palette.shape[0]}")
 
 
+def _bias_bf16(bias: Tensor, N: int) -> Tensor:
+    if bias.dim() != 1 or bias.shape[0] != N:
+        raise RuntimeError(f"bias must be ({N},), got {tuple(bias.shape)}")
+    return bias.detach().to(torch.bfloat16).contiguous()
+
+
 def _forward_weight(w, x):
     if x.shape[0] <= SMALL_M:
         return _ops.hard_forward_smallm(w, x)
@@ -111,9 +117,10 @@ class CUDAFusedLUTLinear(torch.autograd.Function):
         K, N = indices.shape
         _check_common(x, palette, K, N, group_size)
         w = _ops.PackedWeight(_packed_for(indices), palette.detach(), N, K, group_size, K)
-        y = _forward_weight(w, x)
         if bias is not None:
-            y = y + bias.to(y.dtype)
+            y = _ops.hard_forward_bias(w, x, _bias_bf16(bias, N))   # added in fp32 inside the GEMM epilogue
+        else:
+            y = _forward_weight(w, x)
         ctx.save_for_backward(x, palette, w.packed)
         ctx.dims = (N, K, group_size)
         ctx.has_bias = bias is not None
@@ -130,7 +137,7 @@ class CUDAFusedLUTLinear(torch.autograd.Function):
         grad_palette = None
         if ctx.needs_input_grad[1]:
             grad_palette = _ops.backward_dw_hard(w, x, grad_y).to(palette.dtype)
-        grad_bias = grad_y.sum(dim=0) if (ctx.has_bias and ctx.bias_requires_grad) else None
+        grad_bias = _ops.col_sum(grad_y).to(grad_y.dtype) if (ctx.has_bias and ctx.bias_requires_grad) else None
         return grad_x, grad_palette, None, grad_bias, None
 
 
@@ -160,12 +167,14 @@ class CUDAFusedLUTLinearSoft(torch.autograd.Function):
         w = _ops.PackedWeight(_ops.empty_packed(N, K, x.device), palette.detach(), N, K, group_size, K)
         w_soft = _ops.soft_select(w, logits.detach(), "4kn", noise=nz, tau=tau, seed=seed, want_packed=True,
                                   want_soft=not ste)
-        if ste:
+        if ste and bias is not None:
+            y = _ops.hard_forward_bias(w, x, _bias_bf16(bias, N))
+        elif ste:
             y = _forward_weight(w, x)
         else:
             y = _ops.dense_forward(w_soft, x)[0]
-        if bias is not None:
-            y = y + bias.to(y.dtype)
+            if bias is not None:
+                y = y + bias.to(y.dtype)
         ctx.save_for_backward(x, palette, logits, w.packed, w_soft if not ste else None,
                               noise if noise is not None else None)
         ctx.cfg = (N, K, group_size, float(tau), seed, ste)
@@ -188,7 +197,7 @@ class CUDAFusedLUTLinearSoft(torch.autograd.Function):
                 want_dlogits=ctx.needs_input_grad[2], want_dpalette=ctx.needs_input_grad[1])
             if grad_palette is not None:
                 grad_palette = grad_palette.to(palette.dtype)
-        grad_bias = grad_y.sum(dim=0) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
+        grad_bias = _ops.col_sum(grad_y).to(grad_y.dtype) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
         return grad_x, grad_palette, grad_logits, grad_bias, None, None, None, None
 
 
@@ -197,3 +206,140 @@ def fused_lut_linear_soft(x: Tensor, palette: Tensor, logits: Tensor, bias: Tens
                           ste: bool = True) -> Tensor:
     """Soft (Gumbel-Softmax) functional interface -- supports autograd."""
     return CUDAFusedLUTLinearSoft.apply(x, palette, logits, bias, group_size, tau, noise, ste)
+
+
+# ─── the reference extension's function surface (scripts/fused_lut_linear_cuda.py:721-732) ─────────────────────────────
+def _soft_item(palette: Tensor, logits: Tensor, group_size: int, seed: int, **outs):
+    _, K, N = logits.shape
+    if palette.dim() != 2 or palette.shape[1] != 4 or N % group_size or N // group_size != palette.shape[0]:
+        raise RuntimeError(f"G mismatch: N//GS={N // max(group_size, 1)} vs palette {tuple(palette.shape)}")
+    if logits.dtype != torch.float16 or logits.dim() != 3 or logits.shape[0] != 4:
+        raise RuntimeError("logits must be (4, K, N) fp16")
+    d = dict(N=N, K=K, gs_n=group_size, gs_k=K, palette=palette.contiguous(), logits=logits.contiguous(), logits_layout="4kn",
+             noise="hash", seed=int(seed) & 0xFFFFFFFF)
+    d.update(outs)
+    return d
+
+
+class _Extension:
+    """The ten functions the reference's extension module exports, with its argument order, shapes and dtypes.
+    P and W are real tensors here, as in the reference; the library's own training path never materialises them."""
+
+    @staticmethod
+    def fused_lut_linear_fwd(x, palette, indices, bias, group_size):
+        """-> y (M, N) bf16  (:74-117)"""
+        with torch.no_grad():
+            return CUDAFusedLUTLinear.apply(x, palette, indices, bias, int(group_size))
+
+    @staticmethod
+    def fused_lut_linear_bwd(grad_y, x, palette, indices, bias, group_size, needs_grad_x, needs_grad_palette):
+        """-> [grad_x (M, K) bf16, grad_palette (G, 4) bf16, grad_bias (N,) bf16]; entries not asked for are None  (:119-185)"""
+        K, N = indices.shape
+        x, grad_y, palette = x.contiguous(), grad_y.contiguous(), palette.contiguous()
+        _check_common(x, palette, K, N, int(group_size))
+        w = _ops.PackedWeight(_packed_for(indices), palette, N, K, int(group_size), K)
+        gx = _ops.backward_dx(w, grad_y)[0] if needs_grad_x else None
+        gp = _ops.backward_dw_hard(w, x, grad_y).to(torch.bfloat16) if needs_grad_palette else None
+        gb = _ops.col_sum(grad_y).to(torch.bfloat16) if bias is not None else None
+        return [gx, gp, gb]
+
+    @staticmethod
+    def fused_lut_linear_soft_fwd(x, palette, logits, group_size, tau, step_seed):
+        """-> [y = x @ W, P (4, K, N) fp16, W (K, N) bf16 = soft weights]  (:239-275)"""
+        _, K, N = logits.shape
+        P4 = torch.empty(4, K, N, dtype=torch.float16, device=logits.device)
+        W = torch.empty(K, N, dtype=torch.bfloat16, device=logits.device)
+        _ops.soft_weights([_soft_item(palette, logits, int(group_size), step_seed, P=(P4, "4kn"), w_soft=(W, "kn"))], float(tau))
+        y = _ops.dense_backward_dx(W, x.contiguous())[0]   # reduction over the rows of a row-major (K, N) operand
+        return [y, P4, W]
+
+    @staticmethod
+    def fused_lut_linear_soft_fwd_aos(x, palette, logits, group_size, tau, step_seed):
+        """-> [P_aos (K, N, 4) fp16, W (K, N) bf16]; no matmul  (:372-405)"""
+        _, K, N = logits.shape
+        Pa = torch.empty(K, N, 4, dtype=torch.float16, device=logits.device)
+        W = torch.empty(K, N, dtype=torch.bfloat16, device=logits.device)
+        _ops.soft_weights([_soft_item(palette, logits, int(group_size), step_seed, P=(Pa, "kn4"), w_soft=(W, "kn"))], float(tau))
+        return [Pa, W]
+
+    @staticmethod
+    def fused_lut_linear_soft_fwd_with_hard(x, palette, logits, group_size, tau, step_seed):
+        """-> [P_aos, W_soft, W_hard]; the hard index is the argmax of P, i.e. of the noised logits, as in the
+        reference kernel (scripts/fused_lut_kernel.cu:1996-2003)  (:636-660)"""
+        _, K, N = logits.shape
+        Pa = torch.empty(K, N, 4, dtype=torch.float16, device=logits.device)
+        Ws = torch.empty(K, N, dtype=torch.bfloat16, device=logits.device)
+        Wh = torch.empty(K, N, dtype=torch.bfloat16, device=logits.device)
+        _ops.soft_weights([_soft_item(palette, logits, int(group_size), step_seed, P=(Pa, "kn4"), w_soft=(Ws, "kn"),
+                                      w_hard=(Wh, "kn"))], float(tau), hard_from_noisy=True)
+        return [Pa, Ws, Wh]
+
+    @staticmethod
+    def _bwd_from(grad_w, dw_layout, P, p_layout, palette, group_size):
+        if p_layout == "4kn":
+            _, K, N = P.shape
+        else:
+            K, N, _ = P.shape
+        gl = torch.empty(4, K, N, dtype=torch.float16, device=P.device)
+        gp = _ops.soft_bwd_elementwise(N, K, int(group_size), K, palette.contiguous(), grad_w, dw_layout, P, p_layout, gl, "4kn")
+        return [gl, gp.to(torch.bfloat16)]
+
+    @staticmethod
+    def fused_lut_linear_soft_bwd(grad_W, P, palette, group_size):
+        """grad_W (K, N) fp32, P (4, K, N) fp16 -> [grad_logits (4, K, N) fp16, grad_palette (G, 4) bf16]  (:283-323)"""
+        return _Extension._bwd_from(grad_W.contiguous(), "kn", P.contiguous(), "4kn", palette, group_size)
+
+    @staticmethod
+    def soft_bwd_elementwise(grad_W, P_aos, palette, group_size):
+        """grad_W (K, N) bf16 (or fp32), P_aos (K, N, 4) fp16 -> [grad_logits, grad_palette]  (:662-683)"""
+        return _Extension._bwd_from(grad_W.contiguous(), "kn", P_aos.contiguous(), "kn4", palette, group_size)
+
+    @staticmethod
+    def fused_lut_linear_soft_bwd_fused(grad_y, x, P, palette, group_size):
+        """grad_W = x^T grad_y computed here (fp32, tensor cores), then the element-wise backward  (:338-366)"""
+        gw = _ops.weight_grad(x.contiguous(), grad_y.contiguous(), "kn")
+        return _Extension._bwd_from(gw, "kn", P.contiguous(), "4kn", palette, group_size)
+
+    @staticmethod
+    def fused_lut_linear_soft_bwd_fused_aos(grad_y, x, P_aos, palette, group_size):
+        """Same with P in the (K, N, 4) layout  (:421-452)"""
+        gw = _ops.weight_grad(x.contiguous(), grad_y.contiguous(), "kn")
+        return _Extension._bwd_from(gw, "kn", P_aos.contiguous(), "kn4", palette, group_size)
+
+    @staticmethod
+    def fused_compute_P_W_batched(logits_list, palette_list, group_size, tau, step_seed):
+        """One launch for all layers -> flat [P_aos_0, W_0, P_aos_1, W_1, ...]; layer i draws its noise with the seed
+        step_seed ^ (i * 0x9E3779B9)  (:505-607; scripts/fused_lut_kernel.cu:2097-2158)"""
+        if len(logits_list) != len(palette_list):
+            raise RuntimeError("palette_list size must match logits_list size")
+        items, flat = [], []
+        for i, (lg, pal) in enumerate(zip(logits_list, palette_list)):
+            _, K, N = lg.shape
+            Pa = torch.empty(K, N, 4, dtype=torch.float16, device=lg.device)
+            W = torch.empty(K, N, dtype=torch.bfloat16, device=lg.device)
+            seed = (int(step_seed) ^ ((i * 0x9E3779B9) & 0xFFFFFFFF)) & 0xFFFFFFFF
+            items.append(_soft_item(pal.detach(), lg.detach(), int(group_size), seed, P=(Pa, "kn4"), w_soft=(W, "kn")))
+            flat += [Pa, W]
+        if items:
+            _ops.soft_weights(items, float(tau))
+        return flat
+
+
+def fused_compute_P_W_batched(student, tau: float, step_seed: int, group_size: int | None = None):
+    """(P_aos, W_soft) of every soft PalettizedLinear under `student` in one launch, in named_modules() order
+    (scripts/fused_lut_linear_cuda.py:1016-1077). Modules are recognised by their attributes (index_logits, palette,
+    group_size, _use_cuda), so the reference's class and any module shaped like it both qualify."""
+    layers = [m for _, m in student.named_modules()
+              if type(m).__name__ == "PalettizedLinear" and getattr(m, "index_logits", None) is not None
+              and getattr(m, "_use_cuda", False)]
+    if not layers:
+        return []
+    if group_size is None:
+        group_size = layers[0].group_size
+    for i, m in enumerate(layers):
+        if m.group_size != group_size:
+            raise ValueError(f"All PalettizedLinears must share group_size for the batched compute_P_W kernel; layer {i} has "
+                             f"group_size={m.group_size} vs expected {group_size}")
+    flat = _Extension.fused_compute_P_W_batched([m.index_logits for m in layers], [m.palette for m in layers], int(group_size),
+                                                float(tau), int(step_seed))
+    return [(flat[i], flat[i + 1]) for i in range(0, len(flat), 2)]

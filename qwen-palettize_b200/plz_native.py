@@ -30,6 +30,12 @@ class Logits(C.Structure):
                 ("s_p", C.c_int64)]
 
 
+class SoftOut(C.Structure):
+    _fields_ = [("P", C.c_void_p), ("p_n", C.c_int64), ("p_k", C.c_int64), ("p_p", C.c_int64),
+                ("w_soft", C.c_void_p), ("ws_n", C.c_int64), ("ws_k", C.c_int64),
+                ("w_hard", C.c_void_p), ("wh_n", C.c_int64), ("wh_k", C.c_int64)]
+
+
 class Noise(C.Structure):
     _fields_ = [("mode", C.c_int32), ("seed", C.c_uint32), ("ptr", C.c_void_p), ("s_n", C.c_int64),
                 ("s_k", C.c_int64), ("s_p", C.c_int64)]
@@ -42,6 +48,7 @@ _WP, _LP, _GP, _NP = C.POINTER(Weight), C.POINTER(Lora), C.POINTER(Logits), C.PO
 SIGNATURES = {
     "plz_version": [],
     "plz_last_error": [],
+    "plz_launch_count": [],
     "plz_device_status": [C.POINTER(C.c_uint32)],
     "plz_set_cta_limit": [_I32],
     "plz_pack_indices": [_P, _I64, _I64, _I32, _I32, _P, _I64, _P],
@@ -78,9 +85,14 @@ SIGNATURES = {
     "plz_mlp_gate_up_fwd": [_WP, _WP, _P, _I64, _I32, _P, _P, _P, _I64, _P],
     "plz_mlp_gate_up_fwd_keep": [_WP, _WP, _P, _I64, _I32, _P, _P, _P, _I64, _P, _P, _I64, _P],
     "plz_adamw_step": [_P, _P, _P, _P, _I32, _F, _I64, _F, _F, _F, _F, _F, _I32, _F, _F, _I32, _P, _I32, _P],
+    "plz_hard_fwd_bias": [_WP, _P, _I64, _I32, _P, _P, _I64, _P],
+    "plz_col_sum": [_P, _I64, _I32, _I32, _P, _P],
+    "plz_soft_weights": [_I32, C.POINTER(_WP), C.POINTER(_GP), C.POINTER(_NP), _F, _I32, C.POINTER(C.POINTER(SoftOut)), _P],
+    "plz_soft_bwd_elementwise": [_WP, _P, _I32, _I64, _I64, _P, _I64, _I64, _I64, _GP, _P, _P],
+    "plz_weight_grad": [_P, _I64, _P, _I64, _I32, _I32, _I32, _P, _I64, _I64, _P],
     "plz_distill_loss": [_P, _I64, _P, _I64, _I32, _I32, _F, _F, _F, _P, _P, _P, _I64, _I32, _P],
 }
-_RESTYPES = {"plz_last_error": C.c_char_p}
+_RESTYPES = {"plz_last_error": C.c_char_p, "plz_launch_count": C.c_uint64}
 
 
 def lib():

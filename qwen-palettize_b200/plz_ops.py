@@ -398,3 +398,87 @@ def mlp_front_backward(w_gate: PackedWeight, w_up: PackedWeight, x: torch.Tensor
         return dh, None, dgate, dup
     dx, dg = rmsnorm_backward(x, dh, rstd, norm_weight)
     return dx, dg, dgate, dup
+
+
+def hard_forward_bias(w: PackedWeight, x: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+    """y = x W^T + bias, the bias (bf16 [N]) added in fp32 inside the GEMM epilogue."""
+    _mat(x, w.K)
+    M = x.shape[0]
+    y = torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device)
+    if bias is not None:
+        P._need_cuda(bias)
+        assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == w.N
+    d = w.desc()
+    P.check(P.lib().plz_hard_fwd_bias(C.byref(d), x.data_ptr(), x.stride(0), M, bias.data_ptr() if bias is not None else None,
+                                      y.data_ptr(), y.stride(0), P.stream_ptr()), "plz_hard_fwd_bias")
+    return y
+
+
+def col_sum(dy: torch.Tensor) -> torch.Tensor:
+    """fp32 [N]: sum over the rows of a bf16 [M, N] matrix (the bias gradient)."""
+    _mat(dy, dy.shape[1])
+    out = torch.zeros(dy.shape[1], dtype=torch.float32, device=dy.device)
+    P.check(P.lib().plz_col_sum(dy.data_ptr(), dy.stride(0), dy.shape[0], dy.shape[1], out.data_ptr(), P.stream_ptr()), "plz_col_sum")
+    return out
+
+
+def _strides_nk(t: torch.Tensor, layout: str):
+    """(s_n, s_k[, s_p]) of a tensor given as 'kn' (K, N), 'nk' [N, K], 'kn4' (K, N, 4), '4kn' (4, K, N) or 'nk4' [N, K, 4]."""
+    st = t.stride()
+    return {"kn": (st[1], st[0]), "nk": (st[0], st[1]), "kn4": (st[1], st[0], st[2]), "4kn": (st[2], st[1], st[0]),
+            "nk4": (st[0], st[1], st[2])}[layout]
+
+
+def soft_weights(items, tau: float, hard_from_noisy: bool = False):
+    """One launch over several matrices. items: list of dicts with keys
+      N, K, gs_n, gs_k, palette (bf16), logits (tensor), logits_layout ('4kn' | 'nk4'), noise (None | 'hash' | fp32 tensor in the
+      logits' layout), seed, and the wanted outputs as (tensor, layout) pairs or None: P (fp16; '4kn' | 'kn4' | 'nk4'),
+      w_soft / w_hard (bf16; 'kn' | 'nk')."""
+    n = len(items)
+    keep, wps, lps, nps, ops_ = [], [], [], [], []
+    for it in items:
+        wd = P.Weight(it["N"], it["K"], it["gs_n"], it["gs_k"], None, 0, it["palette"].data_ptr())
+        ld = P.logits_desc(it["logits"], it["logits_layout"])
+        nd = P.noise_desc(it.get("noise"), it["logits_layout"], it.get("seed", 0))
+        so = P.SoftOut()
+        if it.get("P") is not None:
+            t, lay = it["P"]
+            assert t.dtype == torch.float16
+            so.P, (so.p_n, so.p_k, so.p_p) = t.data_ptr(), _strides_nk(t, lay)
+        for key, fld in (("w_soft", "ws"), ("w_hard", "wh")):
+            if it.get(key) is not None:
+                t, lay = it[key]
+                assert t.dtype == torch.bfloat16
+                s_n, s_k = _strides_nk(t, lay)
+                setattr(so, key, t.data_ptr()); setattr(so, fld + "_n", s_n); setattr(so, fld + "_k", s_k)
+        keep += [wd, ld, nd, so]
+        wps.append(C.pointer(wd)); lps.append(C.pointer(ld)); nps.append(C.pointer(nd)); ops_.append(C.pointer(so))
+    P.check(P.lib().plz_soft_weights(n, (C.POINTER(P.Weight) * n)(*wps), (C.POINTER(P.Logits) * n)(*lps), (C.POINTER(P.Noise) * n)(*nps),
+                                     float(tau), int(hard_from_noisy), (C.POINTER(P.SoftOut) * n)(*ops_), P.stream_ptr()),
+            "plz_soft_weights")
+
+
+def soft_bwd_elementwise(N, K, gs_n, gs_k, palette, dw, dw_layout, p, p_layout, dlogits, dlogits_layout, want_dpalette=True):
+    """dLogits (written into `dlogits`, fp16 or fp32, may be None) and dPalette fp32 [groups, 4] from a materialised
+    dW (fp32 or bf16) and P (fp16)."""
+    wd = P.Weight(N, K, gs_n, gs_k, None, 0, palette.data_ptr())
+    dw_n, dw_k = _strides_nk(dw, dw_layout)
+    p_n, p_k, p_p = _strides_nk(p, p_layout)
+    dl = P.logits_desc(dlogits, dlogits_layout) if dlogits is not None else None
+    dpal = torch.zeros(palette.numel() // 4, 4, dtype=torch.float32, device=dw.device) if want_dpalette else None
+    P.check(P.lib().plz_soft_bwd_elementwise(C.byref(wd), dw.data_ptr(), _DT[dw.dtype], dw_n, dw_k, p.data_ptr(), p_n, p_k, p_p,
+                                             C.byref(dl) if dl is not None else None, dpal.data_ptr() if dpal is not None else None,
+                                             P.stream_ptr()), "plz_soft_bwd_elementwise")
+    return dpal
+
+
+def weight_grad(x: torch.Tensor, dy: torch.Tensor, layout: str = "kn") -> torch.Tensor:
+    """dW = x^T dY as an fp32 tensor: (K, N) for layout 'kn', [N, K] for 'nk'."""
+    M, K = x.shape
+    N = dy.shape[1]
+    _mat(x, K), _mat(dy, N)
+    dw = torch.zeros((K, N) if layout == "kn" else (N, K), dtype=torch.float32, device=x.device)
+    s_n, s_k = _strides_nk(dw, layout)
+    P.check(P.lib().plz_weight_grad(x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), M, N, K, dw.data_ptr(), s_n, s_k,
+                                    P.stream_ptr()), "plz_weight_grad")
+    return dw

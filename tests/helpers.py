@@ -25,3 +25,16 @@ def check_status():
     import plz_native as P
     st = P.device_status()
     assert st[0] == 0, f"device status {st}"
+
+
+def assert_close_rows(got: torch.Tensor, want: torch.Tensor, what: str, rel=REL_TOL, floor=0.02):
+    """The per-tensor metric again, but per ROW (a palette group, a LoRA rank row...): max |a - b| over the row divided by
+    that row's own max |b| (not below `floor` x the tensor's max, so that a row that is all noise cannot fail alone).
+    One large element elsewhere in the tensor cannot hide a wrong small row."""
+    g, w = got.detach().double().cpu(), want.detach().double().cpu()
+    assert g.shape == w.shape, f"{what}: shape {tuple(g.shape)} vs {tuple(w.shape)}"
+    g, w = g.reshape(g.shape[0], -1), w.reshape(w.shape[0], -1)
+    den = w.abs().amax(1).clamp(min=floor * w.abs().max().item())
+    err = (g - w).abs().amax(1) / den
+    worst = int(err.argmax())
+    assert err[worst].item() <= rel, f"{what}: row {worst} has max rel err {err[worst].item():.3e} (<= {rel})"

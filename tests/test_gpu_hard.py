@@ -136,3 +136,35 @@ def test_persistent_schedule_with_few_ctas(limit):
     assert_close(y, (x.float() @ wd.float().t() + O.lora_forward(x, a, b, 1.0)), "y")
     assert_close(dx, (dy.float() @ wd.float() + dxl), "dX")
     assert_close(dpal, O.hard_backward(x, dy, idx.long(), pal, 1, 256)[1], "dPalette")
+
+
+@pytest.mark.parametrize("N,K,gs_n,gs_k", [(768, 512, 1, 256), (512, 256, 256, 256), (1024, 512, 256, 512), (320, 192, 1, 64)])
+def test_in_gemm_decode_is_bit_exact(N, K, gs_n, gs_k):
+    """x = I makes every output the sum of ONE weight times 1 plus zeros, which is exact in fp32 and in the bf16 store:
+    y = I W^T must equal the gathered weights bit for bit (decode inside the forward GEMM), and dX = I W likewise (decode
+    inside the dX GEMM), for both palette groupings."""
+    import plz_ops as ops
+    g = torch.Generator().manual_seed(N + K)
+    idx = torch.randint(0, 4, (N, K), generator=g, dtype=torch.uint8)
+    pal = (torch.randn((N // gs_n) * (K // gs_k), 4, generator=g) * 0.02).to(torch.bfloat16)
+    pal[pal == 0] = 0.0078125
+    w = _weight(idx, pal, N, K, gs_n, gs_k)
+    wd = O.dequantize(idx.long(), pal, gs_n, gs_k)                       # [N, K] bf16, pure gather
+    assert torch.equal(ops.dequantize(w).cpu(), wd)
+    eye_k = torch.eye(K, dtype=torch.bfloat16, device="cuda")
+    y, _ = ops.hard_forward(w, eye_k)                                     # [K, N] = W^T
+    check_status()
+    assert torch.equal(y.cpu(), wd.t()), "forward GEMM decode"
+    if N % 64 == 0:
+        eye_n = torch.eye(N, dtype=torch.bfloat16, device="cuda")
+        dx, _ = ops.backward_dx(w, eye_n)                                 # [N, K] = W
+        check_status()
+        assert torch.equal(dx.cpu(), wd), "dX GEMM decode"
+    # the small-M kernels: 16 rows of the identity at a time
+    for k0 in range(0, K, 16):
+        for rows in ((16, 1) if k0 == 0 else (16,)):
+            ys = ops.hard_forward_smallm(w, eye_k[k0:k0 + rows].contiguous())  # [rows, N]
+            assert torch.equal(ys.cpu(), wd[:, k0:k0 + rows].t()), f"small-M decode, columns {k0}..{k0 + rows}"
+    y64 = ops.hard_forward_smallm(w, eye_k[:64].contiguous())
+    assert torch.equal(y64.cpu(), wd[:, :64].t()), "small-M (17..64 rows) decode"
+    check_status()

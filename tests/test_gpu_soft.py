@@ -3,7 +3,7 @@ import pytest
 import torch
 
 import plz_oracle as O
-from helpers import assert_close, check_status
+from helpers import assert_close, assert_close_rows, check_status
 
 pytestmark = pytest.mark.gpu
 
@@ -42,6 +42,10 @@ def test_linear_step_matches_oracle(M, N, K, tau, ste):
     assert_close(got["dpalette"], want["dpalette"], "dPalette")
     assert_close(got["da"], want["da"], "dA")
     assert_close(got["db"], want["db"], "dB")
+    # the same bound per palette group / per LoRA row, so that small-magnitude rows are checked on their own scale
+    assert_close_rows(got["dpalette"], want["dpalette"], "dPalette per group")
+    assert_close_rows(got["da"], want["da"], "dA per rank row")
+    assert_close_rows(got["db"], want["db"], "dB per weight row")
 
 
 def test_linear_step_without_lora_and_noise():

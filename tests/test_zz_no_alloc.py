@@ -13,23 +13,29 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _call_pair(M, seed):
+def _call_pair(M, seed, r=16, dev=0, watch_memory=False):
     import plz_native as P
     import plz_ops as ops
     import synth
-    N, K, r = 512, 512, 16
+    N, K = 512, 512
     d = synth.make_linear_inputs(M, N, K, seed=seed, rank=r, soft=False, with_dy=False)
-    x = d["x"].cuda()
-    w = ops.PackedWeight(ops.pack_indices(d["idx"].cuda().view(torch.int8), n_major=True),
-                         d["palette"].reshape(-1, 4).cuda(), N, K, 1, 256)
-    a, b = d["lora_a"].cuda(), d["lora_b"].cuda()
-    y_ref, _ = ops.hard_forward(w, x, (a, b, 2.0))            # existing entry point, caller-owned workspace
-    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-    wd, ld = w.desc(), P.lora_desc(a, b, 2.0)
-    rc = P.lib().plz_hard_fwd_lora_static(C.byref(wd), x.data_ptr(), x.stride(0), M, C.byref(ld), y.data_ptr(),
-                                          y.stride(0), P.stream_ptr())
-    P.check(rc, "plz_hard_fwd_lora_static")
-    assert P.device_status()[0] == 0
+    with torch.cuda.device(dev):
+        x = d["x"].cuda()
+        w = ops.PackedWeight(ops.pack_indices(d["idx"].cuda().view(torch.int8), n_major=True),
+                             d["palette"].reshape(-1, 4).cuda(), N, K, 1, 256)
+        a, b = d["lora_a"].cuda(), d["lora_b"].cuda()
+        y_ref, _ = ops.hard_forward(w, x, (a, b, 2.0))            # existing entry point, caller-owned workspace
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        wd, ld = w.desc(), P.lora_desc(a, b, 2.0)
+        torch.cuda.synchronize()
+        free0, used0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+        rc = P.lib().plz_hard_fwd_lora_static(C.byref(wd), x.data_ptr(), x.stride(0), M, C.byref(ld), y.data_ptr(),
+                                              y.stride(0), P.stream_ptr())
+        P.check(rc, "plz_hard_fwd_lora_static")
+        assert P.device_status()[0] == 0                           # synchronizes
+        if watch_memory:
+            # neither the driver's free-memory figure (cudaMemGetInfo) nor torch's allocator moved across the call
+            assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == used0
     return y, y_ref
 
 
@@ -37,9 +43,23 @@ def test_static_scratch_matches_workspace_entry_point_twice():
     from helpers import assert_close
     y1, r1 = _call_pair(300, seed=1)      # first call on this device: looks up the scratch address
     assert_close(y1, r1, "first call")
-    y2, r2 = _call_pair(130, seed=2)      # smaller batch: rows 130.. of the scratch still hold call 1's data
+    y2, r2 = _call_pair(130, seed=2, watch_memory=True)   # smaller batch: rows 130.. of the scratch still hold call 1's data
     assert_close(y2, r2, "second call")
     assert torch.equal(y1, r1) and torch.equal(y2, r2)   # same kernels, same inputs: identical bits
+
+
+def test_static_scratch_at_its_largest_size():
+    """Exactly M * rank = 262144 elements (4096 rows at rank 64) is accepted and correct."""
+    y, r = _call_pair(4096, seed=3, r=64, watch_memory=True)
+    assert torch.equal(y, r)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs a second GPU")
+def test_static_scratch_on_a_second_device():
+    """Every device has its own copy of the array and its own cached address."""
+    y0, r0 = _call_pair(200, seed=4, dev=0)
+    y1, r1 = _call_pair(200, seed=4, dev=1)
+    assert torch.equal(y0, r0) and torch.equal(y1, r1) and torch.equal(y0.cpu(), y1.cpu())
 
 
 def test_static_scratch_rejects_oversized_calls():
