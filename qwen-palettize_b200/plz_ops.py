@@ -425,8 +425,17 @@ def col_sum(dy: torch.Tensor) -> torch.Tensor:
 def _strides_nk(t: torch.Tensor, layout: str):
     """(s_n, s_k[, s_p]) of a tensor given as 'kn' (K, N), 'nk' [N, K], 'kn4' (K, N, 4), '4kn' (4, K, N) or 'nk4' [N, K, 4]."""
     st = t.stride()
-    return {"kn": (st[1], st[0]), "nk": (st[0], st[1]), "kn4": (st[1], st[0], st[2]), "4kn": (st[2], st[1], st[0]),
-            "nk4": (st[0], st[1], st[2])}[layout]
+    if layout == "kn":
+        return st[1], st[0]
+    if layout == "nk":
+        return st[0], st[1]
+    if layout == "kn4":
+        return st[1], st[0], st[2]
+    if layout == "4kn":
+        return st[2], st[1], st[0]
+    if layout == "nk4":
+        return st[0], st[1], st[2]
+    raise ValueError(f"unknown layout {layout}")
 
 
 def soft_weights(items, tau: float, hard_from_noisy: bool = False):

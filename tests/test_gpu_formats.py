@@ -95,3 +95,82 @@ def test_idx2_and_lut_files_load_into_the_native_layout(golden):
     assert pal.shape == (2, 4) and pal.dtype == torch.bfloat16
     assert torch.equal(pal.cpu(), torch.from_numpy(golden["lut_vals"]).to(torch.bfloat16).reshape(2, 4))
     check_status()
+
+
+@pytest.fixture(scope="module")
+def real():
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return np.load(os.path.join(root, "tests", "golden", "real_k_proj.npz"))
+
+
+def test_real_shipped_pair_loads_bit_exact(tmp_path, real):
+    """One .idx2 / .lut_scalar pair of the reference's palettized/superblock_0 (stored with what the reference's own
+    load_indices / load_lut return for it): the device loader must reproduce both bit for bit, write the same bytes back,
+    and the loaded weight must run."""
+    import json
+    import formats as F
+    import plz_ops as ops
+    N, K = 1024, 2560
+    entry, name = json.loads(str(real["entry"])), str(real["name"])
+    idx_payload, lut_payload = real["idx2"].tobytes(), real["lut_scalar"].tobytes()
+    packed, idx_kn = F.load_idx2(idx_payload, N, K)
+    assert np.array_equal(packed.cpu().numpy(), real["ref_packed_nk"])
+    assert np.array_equal(O.pack_rows(idx_kn.t().contiguous().cpu().numpy().astype(np.uint8)), real["ref_packed_nk"])
+    pal = F.load_lut_scalar(lut_payload)
+    assert pal.shape == (N // 256, 4) and torch.equal(pal.cpu(), torch.from_numpy(real["ref_lut"]).to(torch.bfloat16).reshape(-1, 4))
+    assert F.save_idx2(packed, K) == idx_payload
+    # through the directory reader (metadata.json + sha256 verification)
+    open(tmp_path / entry["index_file"], "wb").write(idx_payload)
+    open(tmp_path / entry["lut_file"], "wb").write(lut_payload)
+    F.write_metadata(str(tmp_path / "metadata.json"), [(name, entry)])
+    loaded = F.load_palettized_dir(str(tmp_path))
+    w, idx2 = loaded[name]
+    assert torch.equal(w.packed, packed) and torch.equal(idx2, idx_kn) and (w.N, w.K, w.gs_n, w.gs_k) == (N, K, 256, K)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(200, K, generator=g).to(torch.bfloat16)
+    y, _ = ops.hard_forward(w, x.cuda())
+    check_status()
+    idx_nk = torch.from_numpy(O.unpack_rows(real["ref_packed_nk"], K)).long()
+    want = O.hard_forward(x, O.dequantize(idx_nk, pal.cpu(), 256, K))
+    from helpers import assert_close
+    assert_close(y, want, "y from the shipped k_proj weights")
+
+
+def test_checkpoint_round_trip(tmp_path):
+    """save_checkpoint writes the reference's checkpoint layout (.idx2 + .lut_scalar per Linear, .pt per small parameter,
+    _resume.json); load_checkpoint and load_palettized_dir read it back bit for bit."""
+    import json
+    import os
+    import formats as F
+    import plz_ops as ops
+    g = torch.Generator().manual_seed(3)
+    shapes = {"layers.0.self_attn.q_proj.base": (512, 256), "layers.0.mlp.down_proj.base": (256, 768)}
+    lin = {}
+    for name, (N, K) in shapes.items():
+        lg = torch.randn(N, K, 4, generator=g).cuda()
+        pal = (torch.randn(N // 256, 4, generator=g) * 0.02).to(torch.bfloat16).cuda()
+        w = ops.PackedWeight(ops.empty_packed(N, K, "cuda"), pal, N, K, 256, K)
+        ops.soft_select(w, lg, "nk4", want_packed=True)               # hard indices = argmax of the trained logits
+        lin[name] = (w.packed, pal, K)
+    small = {"layers.0.self_attn.q_proj.lora_A": torch.randn(256, 16, generator=g).to(torch.bfloat16).cuda(),
+             "layers.0.input_layernorm.weight": torch.randn(256, generator=g).to(torch.bfloat16).cuda()}
+    n = F.save_checkpoint(str(tmp_path), lin, small, sb_idx=0, step=120, cos=0.93, loss=0.08)
+    assert n == (2, 2)
+    files = sorted(os.listdir(tmp_path))
+    assert "layers_0_self_attn_q_proj_base.idx2" in files and "layers_0_self_attn_q_proj_lora_A.pt" in files
+    assert json.load(open(tmp_path / "_resume.json")) == {"step": 120, "cos": 0.93, "loss": 0.08, "sb_idx": 0}
+    resume, lin2, small2 = F.load_checkpoint(str(tmp_path), shapes, list(small) + ["not.saved"])
+    assert resume["step"] == 120 and set(small2) == set(small)
+    for name in shapes:
+        packed, pal, idx_kn = lin2[name]
+        assert torch.equal(packed, lin[name][0])
+        assert torch.equal(pal, lin[name][1].to(torch.float16).to(torch.bfloat16))   # palettes travel as fp16
+        lg = F.one_hot_logits(idx_kn)                                                # restart logits: +1 on the index, -1 elsewhere
+        assert lg.shape == (4,) + tuple(idx_kn.shape) and torch.equal(lg.argmax(0).to(torch.int8), idx_kn)
+        assert lg.float().sum(0).eq(-2).all()
+    for k in small:
+        assert torch.equal(small2[k], small[k])
+    both = F.load_palettized_dir(str(tmp_path))                                      # the checkpoint also reads as a palettized dir
+    assert set(both) == set(shapes) and torch.equal(both["layers.0.mlp.down_proj.base"][0].packed, lin["layers.0.mlp.down_proj.base"][0])
+    check_status()
