@@ -288,7 +288,8 @@ int32_t plz_adamw_step(float* master, float* m, float* v, const void* grad, int3
 /* Distillation loss of compute_loss (scripts/train_qwen.py:229-249), type "1-cos+norm_mse", fp32 math on bf16
  * student / teacher states s, t [M, H]:  loss = w_cos * mean_tokens(1 - cos(s, t)) + w_mse * mean((s-t)^2) / max(mean(t^2), 1e-6),
  * cosine with each norm clamped at 1e-4. out4 (device, may be NULL) receives {loss, l_cos, l_mse, mean(t^2)}.
- * ds (may be NULL) receives upstream * dLoss/ds in ds_dtype (0 fp32, 2 bf16). ws: caller workspace of 4 + 3*M floats. */
+ * ds (may be NULL) receives upstream * dLoss/ds in ds_dtype (0 fp32, 2 bf16). ws: caller workspace of 4 + 4*M floats, 16-byte aligned; the three sums are reduced in a fixed order, so the loss is
+ * bit-identical from run to run. */
 int32_t plz_distill_loss(const void* s, int64_t lds, const void* t, int64_t ldt, int32_t M, int32_t H, float w_cos, float w_mse,
                          float upstream, float* ws, float* out4, void* ds, int64_t ldds, int32_t ds_dtype, void* stream);
 

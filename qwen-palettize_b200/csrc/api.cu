@@ -698,6 +698,7 @@ int32_t plz_distill_loss(const void* s, int64_t lds, const void* t, int64_t ldt,
     if (M < 0 || H <= 0 || (H & 1)) { set_last_error("distill_loss: H must be even and positive (M=%d, H=%d)", M, H); return PLZ_ERR_BAD_SHAPE; }
     if (M == 0) return PLZ_OK;
     if (!s || !t || !ws) { set_last_error("distill_loss: null input or workspace"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)ws & 15)) { set_last_error("distill_loss: the workspace must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
     if (((uintptr_t)s & 3) || ((uintptr_t)t & 3) || (lds & 1) || (ldt & 1) || (ds && (ldds & 1))) { set_last_error("distill_loss: rows must be 4-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
     if (ds_dtype != 0 && ds_dtype != 2) { set_last_error("distill_loss: gradient dtype must be 0 (fp32) or 2 (bf16)"); return PLZ_ERR_UNSUPPORTED; }
     return launch_distill_loss(s, lds, t, ldt, M, H, 1e-4f, w_cos, w_mse, upstream, ws, out4, ds, ldds, ds_dtype, (cudaStream_t)stream);

@@ -378,7 +378,7 @@ static int launch_rows(const GemvArgs& a, cudaStream_t stream) {
         PLZ_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_smem[dev & 63] = (int)smem;
     }
-    const int sms = a.sm_count > 0 ? a.sm_count : 148;
+    const int sms = a.sm_count > 0 ? a.sm_count : 1;
     int blocks_per_sm = (int)((200u * 1024u) / (smem + 1024));
     if (blocks_per_sm > 4) blocks_per_sm = 4;
     if (blocks_per_sm < 1) blocks_per_sm = 1;
@@ -421,7 +421,7 @@ int launch_lut_gemv(const GemvArgs& a, cudaStream_t stream) {
     int max_rows = (int)(budget / (uint32_t)(row_bytes + kg_per_row * 8));
     if (max_rows > 128) max_rows = 128;
     if (max_rows < 1) { set_last_error("small-M forward: K=%d too large for shared memory", a.K); return PLZ_ERR_TOO_LARGE; }
-    int sms = a.sm_count > 0 ? a.sm_count : 148;
+    int sms = a.sm_count > 0 ? a.sm_count : 1;
     int grid = sms;
     if ((a.N + grid - 1) / grid > max_rows) grid = (a.N + max_rows - 1) / max_rows;
     if (grid > a.N) grid = a.N;

@@ -317,7 +317,7 @@ int launch_lut_smallm_mma_multi(const GemvArgs* mats, int count, cudaStream_t st
     for (int i = count; i <= kMaxMats; ++i) p.row_start[i] = total;
     p.n_mats = count;
     const int mt = a.M <= 8 ? 1 : 2;
-    const int sms = a.sm_count > 0 ? a.sm_count : 148;
+    const int sms = a.sm_count > 0 ? a.sm_count : 1;
     int grid = sms;
     if (grid > (total + 15) / 16) grid = (total + 15) / 16;
     int rows_per_cta = (total + grid - 1) / grid;

@@ -13,6 +13,20 @@
 
 namespace plz {
 
+// number of SMs of the current device (grid sizing of the grid-stride kernels below)
+static int sm_count_of_current_device() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+    dev &= 63;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 __device__ __forceinline__ float ld_as_f32(const float* p, long long i) { return p[i]; }
 __device__ __forceinline__ float ld_as_f32(const __half* p, long long i) { return __half2float(p[i]); }
 __device__ __forceinline__ float ld_as_f32(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
@@ -46,7 +60,7 @@ __global__ void __launch_bounds__(256) adamw_clamp_kernel(const AdamParams p) {
 int launch_adamw(const AdamParams& p, int grad_dtype, int param_dtype, cudaStream_t stream) {
     if (p.n <= 0) return PLZ_OK;
     long long blocks = (p.n + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > sm_count_of_current_device() * 16) blocks = sm_count_of_current_device() * 16;
 #define PLZ_ADAM(GT, PT) adamw_clamp_kernel<GT, PT><<<(unsigned)blocks, 256, 0, stream>>>(p)
     if (grad_dtype == 0) {
         if (param_dtype == 0) PLZ_ADAM(float, float); else if (param_dtype == 1) PLZ_ADAM(float, __half); else PLZ_ADAM(float, __nv_bfloat16);
@@ -62,7 +76,8 @@ int launch_adamw(const AdamParams& p, int grad_dtype, int param_dtype, cudaStrea
 
 // ---------------------------------------------------------------------------------------------
 // distillation loss. ws layout (fp32): [0] sum(1 - cos), [1] sum((s-t)^2), [2] sum(t^2), [3] unused,
-// then per token: dot, |s|^2, |t|^2 (3 floats).
+// then per token: dot, |s|^2, |t|^2, |s - t|^2 (4 floats). The three totals are summed by ONE block in a fixed order
+// (no atomics), so the loss and everything scaled by it are bit-identical from run to run.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum_f(float v) {
 #pragma unroll
@@ -74,9 +89,7 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 __global__ void __launch_bounds__(256)
 distill_stats_kernel(const __nv_bfloat16* __restrict__ s, long long lds, const __nv_bfloat16* __restrict__ t, long long ldt,
                      int M, int H, float eps, float* __restrict__ ws) {
-    __shared__ float part[3][8];
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    float a_cos = 0.f, a_d2 = 0.f, a_t2 = 0.f;
     for (int row = blockIdx.x * 8 + wib; row < M; row += gridDim.x * 8) {
         const __nv_bfloat16* sr = s + (long long)row * lds;
         const __nv_bfloat16* tr = t + (long long)row * ldt;
@@ -91,20 +104,30 @@ distill_stats_kernel(const __nv_bfloat16* __restrict__ s, long long lds, const _
             d2 += dx * dx + dy * dy;
         }
         dot = warp_sum_f(dot); s2 = warp_sum_f(s2); t2 = warp_sum_f(t2); d2 = warp_sum_f(d2);
-        if (lane == 0) {
-            float* st = ws + 4 + 3ll * row;
-            st[0] = dot; st[1] = s2; st[2] = t2;
-            const float cosv = dot / (fmaxf(sqrtf(s2), eps) * fmaxf(sqrtf(t2), eps));
-            a_cos += 1.0f - cosv; a_d2 += d2; a_t2 += t2;
-        }
+        if (lane == 0) *reinterpret_cast<float4*>(ws + 4 + 4ll * row) = make_float4(dot, s2, t2, d2);
     }
-    if (lane == 0) { part[0][wib] = a_cos; part[1][wib] = a_d2; part[2][wib] = a_t2; }
+}
+
+// one block: thread i sums rows i, i + 1024, ...; then a fixed tree over the 1024 partials
+__global__ void __launch_bounds__(1024)
+distill_reduce_kernel(int M, float eps, float* __restrict__ ws) {
+    __shared__ float part[3][1024];
+    float a_cos = 0.f, a_d2 = 0.f, a_t2 = 0.f;
+    for (int row = threadIdx.x; row < M; row += 1024) {
+        const float4 st = *reinterpret_cast<const float4*>(ws + 4 + 4ll * row);
+        const float cosv = st.x / (fmaxf(sqrtf(st.y), eps) * fmaxf(sqrtf(st.z), eps));
+        a_cos += 1.0f - cosv; a_d2 += st.w; a_t2 += st.z;
+    }
+    part[0][threadIdx.x] = a_cos; part[1][threadIdx.x] = a_d2; part[2][threadIdx.x] = a_t2;
     __syncthreads();
-    if (threadIdx.x < 3) {
-        float v = 0.f;
-        for (int i = 0; i < 8; ++i) v += part[threadIdx.x][i];
-        atomicAdd(ws + threadIdx.x, v);
+    for (int w = 512; w > 0; w >>= 1) {
+        if (threadIdx.x < w) {
+#pragma unroll
+            for (int q = 0; q < 3; ++q) part[q][threadIdx.x] += part[q][threadIdx.x + w];
+        }
+        __syncthreads();
     }
+    if (threadIdx.x < 3) ws[threadIdx.x] = part[threadIdx.x][0];
 }
 
 template <typename GradT>
@@ -122,8 +145,8 @@ distill_grad_kernel(const __nv_bfloat16* __restrict__ s, long long lds, const __
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const float c_mse = upstream * w_mse * 2.0f * inv_mh / t_var;
     for (int row = blockIdx.x * 8 + wib; row < M; row += gridDim.x * 8) {
-        const float* st = ws + 4 + 3ll * row;
-        const float dot = st[0], s2 = st[1], t2 = st[2];
+        const float4 st = *reinterpret_cast<const float4*>(ws + 4 + 4ll * row);
+        const float dot = st.x, s2 = st.y, t2 = st.z;
         const float ns = sqrtf(s2), nt = sqrtf(t2);
         const float cs = fmaxf(ns, eps), ct = fmaxf(nt, eps);
         // cos = dot / (cs * ct); d cos / d s = t / (cs ct) - [ns >= eps] * cos * s / ns^2 (the clamp has no slope below eps)
@@ -147,10 +170,11 @@ int launch_distill_loss(const void* s, long long lds, const void* t, long long l
                         float w_mse, float upstream, float* ws, float* out4, void* ds, long long ldds, int ds_dtype,
                         cudaStream_t stream) {
     if (M <= 0 || H <= 0) return PLZ_OK;
-    PLZ_CUDA_CHECK(cudaMemsetAsync(ws, 0, 4 * sizeof(float), stream));
     int blocks = (M + 7) / 8;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count_of_current_device() * 8) blocks = sm_count_of_current_device() * 8;
     distill_stats_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)s, lds, (const __nv_bfloat16*)t, ldt, M, H, eps, ws);
+    PLZ_LAUNCH_CHECK();
+    distill_reduce_kernel<<<1, 1024, 0, stream>>>(M, eps, ws);
     PLZ_LAUNCH_CHECK();
     if (ds_dtype == 0)
         distill_grad_kernel<float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)s, lds, (const __nv_bfloat16*)t, ldt, M, H, eps,
@@ -184,7 +208,7 @@ rms_rstd_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int M, int K
 int launch_rms_rstd(const void* x, long long ldx, int M, int K, float eps, float* rstd, cudaStream_t stream) {
     if (M <= 0) return PLZ_OK;
     int blocks = (M + 7) / 8;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count_of_current_device() * 8) blocks = sm_count_of_current_device() * 8;
     rms_rstd_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, M, K, eps, rstd);
     PLZ_LAUNCH_CHECK();
     return PLZ_OK;
@@ -231,7 +255,7 @@ int launch_swiglu_bwd(const void* gate, long long ldg, const void* up, long long
                       void* dgate, long long lddg, void* dup, long long lddu, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return PLZ_OK;
     long long blocks = ((long long)M * (N >> 3) + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > sm_count_of_current_device() * 16) blocks = sm_count_of_current_device() * 16;
     swiglu_bwd_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate, ldg, (const __nv_bfloat16*)up, ldu,
                                                         (const __nv_bfloat16*)dact, ldd, M, N, (__nv_bfloat16*)dgate, lddg,
                                                         (__nv_bfloat16*)dup, lddu);
@@ -310,7 +334,7 @@ int launch_rmsnorm_bwd(const void* x, long long ldx, const void* dh, long long l
                        void* dx, long long lddx, float* dg, cudaStream_t stream) {
     if (M <= 0) return PLZ_OK;
     if (K > 512 * kNormPairsMax) { set_last_error("rmsnorm_bwd: K=%d exceeds %d", K, 512 * kNormPairsMax); return PLZ_ERR_TOO_LARGE; }
-    int blocks = M < 148 * 8 ? M : 148 * 8;
+    int blocks = M < sm_count_of_current_device() * 8 ? M : sm_count_of_current_device() * 8;
     const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *dp = (const __nv_bfloat16*)dh, *gp = (const __nv_bfloat16*)g;
     if (K <= 512 * 5) rmsnorm_bwd_kernel<5><<<blocks, 256, 0, stream>>>(xp, ldx, dp, lddh, rstd, gp, M, K, (__nv_bfloat16*)dx, lddx, dg);
     else if (K <= 512 * 10) rmsnorm_bwd_kernel<10><<<blocks, 256, 0, stream>>>(xp, ldx, dp, lddh, rstd, gp, M, K, (__nv_bfloat16*)dx, lddx, dg);
@@ -340,7 +364,7 @@ int launch_reduce_slots(const float* stage, int world, long long shard_elems, fl
     if (shard_elems <= 0) return PLZ_OK;
     const long long vec = shard_elems / 4;
     long long blocks = (vec + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > sm_count_of_current_device() * 16) blocks = sm_count_of_current_device() * 16;
     reduce_slots_kernel<<<(int)blocks, 256, 0, stream>>>((const float4*)stage, world, vec, (float4*)out, scale);
     PLZ_LAUNCH_CHECK();
     return PLZ_OK;

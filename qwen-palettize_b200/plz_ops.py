@@ -308,7 +308,7 @@ def distill_loss(s: torch.Tensor, t: torch.Tensor, w_cos: float = 0.5, w_mse: fl
     tot = float(w_cos) + float(w_mse)   # the reference normalises the two weights to sum 1 (normalize_weights)
     if tot > 0:
         w_cos, w_mse = w_cos / tot, w_mse / tot
-    ws = torch.empty(4 + 3 * M, dtype=torch.float32, device=s.device)
+    ws = torch.empty(4 + 4 * M, dtype=torch.float32, device=s.device)
     out4 = torch.empty(4, dtype=torch.float32, device=s.device)
     ds = torch.empty(M, H, dtype=grad_dtype, device=s.device) if want_grad else None
     P.check(P.lib().plz_distill_loss(s2.data_ptr(), s2.stride(0), t2.data_ptr(), t2.stride(0), M, H, float(w_cos), float(w_mse),
