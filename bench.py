@@ -154,6 +154,7 @@ def run_ours(args):
     os.dup2(2, 1)  # anything a library prints (NCCL's version banner) goes to stderr; the JSON line gets stdout back
     rank, world, local = dist_setup(args.gpus)
     dev = torch.device("cuda", local if world > 1 else 0)
+    plz_native.lib().plz_set_pair_gemm(args.pair_gemm)
     d = synth.make_linear_inputs_cuda(M_TOK, N_OUT, K_IN, seed=rank, rank=RANK, device=dev)
     # parameters are replicated: every rank uses rank 0's parameters, its own tokens
     if world > 1:
@@ -908,6 +909,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="N = 1: skip the extra_configs measurements (config 0, small-M decode, reference-API step)")
     ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the correctness check of the fused exchange that runs before the timed region")
     ap.add_argument("--sustained-s", type=float, default=3.0, help="length of the sustained leg in seconds (0 = off)")
+    ap.add_argument("--pair-gemm", type=int, default=1, help="0: keep the large products on the one-CTA-per-tile kernels (comparison)")
     ap.add_argument("--case", default=None, help="run ONE kernel of the hot path a few times on a small case and exit (for ncu captures)")
     ap.add_argument("--kernels", action="store_true", help="per-kernel table: one JSON line per measurement")
     ap.add_argument("--M", type=int, default=4096)

@@ -93,6 +93,10 @@ int32_t plz_device_status(uint32_t* out4);
  * leaves the other SMs to a communication library: set it around the dX product while the gradient all-reduce of the
  * same Linear is in flight. Process-wide. (No counterpart in the reference, which is single-GPU.) */
 int32_t plz_set_cta_limit(int32_t n);
+/* The large forward / dX products run on pairs of CTAs that share one 256 x 256 tile (tcgen05 cta_group::2). on = 0 keeps
+ * them on the one-CTA-per-tile kernel that serves all other shapes (for comparisons and tests); default 1. Process-wide.
+ * (No counterpart in the reference.) */
+int32_t plz_set_pair_gemm(int32_t on);
 
 /* ---- formats ---------------------------------------------------------------------------------
  * Pack unpacked int8/uint8 indices, element (n, k) at src[n * s_n + k * s_k], into `dst`.

@@ -150,6 +150,8 @@ void plz_debug_set_smallm_variant(int v) { g_debug_smallm_variant = v; }
 #endif
 int32_t plz_set_cta_limit(int32_t n) { g_cta_limit = n > 0 ? n : 0; return PLZ_OK; }
 
+int32_t plz_set_pair_gemm(int32_t on) { g_pair_gemm = on ? 1 : 0; return PLZ_OK; }
+
 int32_t plz_set_smallm_overlap(int32_t on) { g_smallm_overlap = on ? 1 : 0; return PLZ_OK; }
 
 int32_t plz_version(void) { return 110; }

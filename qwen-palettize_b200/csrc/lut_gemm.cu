@@ -207,6 +207,10 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int q = warp - 1;
         if (lane == 0) {
             const uint32_t idesc_main = make_idesc(128, p.mma_n, 0, kBMn ? 1 : 0);
+            const uint64_t ad0 = make_sdesc(base, 16u, 1024u);
+            const uint64_t bd0 = kBMn ? make_sdesc(base + C::A_BYTES, 8192u, 1024u) : make_sdesc(base + C::A_BYTES, 16u, 1024u);
+            const uint32_t a_hi = (uint32_t)(ad0 >> 32), b_hi = (uint32_t)(bd0 >> 32);
+            const uint32_t a_lo0 = (uint32_t)ad0, b_lo0 = (uint32_t)bd0;
             bool ok = true;
             long long wait_a = 0, wait_b = 0, wait_t = 0;
             const long long t_begin = PLZ_PROF_ON(p.prof) ? clock64() : 0;
@@ -235,18 +239,18 @@ lut_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (PLZ_PROF_ON(p.prof)) { wait_a += c1 - c0; wait_b += clock64() - c1; }
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t sA = base + s * C::STAGE_BYTES;
-                    const uint32_t sB = sA + C::A_BYTES;
+                    // precomputed descriptor words: only the low word moves (stage base, then a constant per k step)
+                    const uint32_t a_lo = a_lo0 + (uint32_t)s * (C::STAGE_BYTES >> 4);
+                    const uint32_t b_lo = b_lo0 + (uint32_t)s * (C::STAGE_BYTES >> 4);
+                    const uint32_t acc0 = (it >= kIssuers) ? 1u : 0u;
 #pragma unroll
                     for (int ks = 0; ks < kBK / 16; ++ks) {
-                        const uint64_t bdesc = kBMn ? make_sdesc(sB + ks * 2048u, 8192u, 1024u)
-                                                    : make_sdesc(sB + ks * 32u, 16u, 1024u);
+                        const uint32_t offb = kBMn ? (uint32_t)(ks * 128) : (uint32_t)(ks * 2);
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt) {
                             if (mt >= nmt) break;
-                            const uint64_t adesc = make_sdesc(sA + mt * 16384u + ks * 32u, 16u, 1024u);
-                            umma_bf16(tmem_base + mt * 256u + (kIssuers > 1 ? q * 64u : 0u), adesc, bdesc, idesc_main,
-                                      (it >= kIssuers || ks > 0) ? 1u : 0u);
+                            umma_bf16_words<1>(tmem_base + mt * 256u + (kIssuers > 1 ? q * 64u : 0u), a_lo + (uint32_t)(mt * 1024 + ks * 2), a_hi,
+                                               b_lo + offb, b_hi, idesc_main, (ks > 0) ? 1u : acc0);
                         }
                     }
                     umma_commit(empty(s));
@@ -608,6 +612,11 @@ int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream) {
         if (((uintptr_t)a.packed & 15) || (a.packed_pitch & 15)) { set_last_error("lut_gemm: packed index rows must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
         if ((uintptr_t)a.palette & 7) { set_last_error("lut_gemm: palette must be 8-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
         if (a.gs_k % 64 || a.Wk % a.gs_k || a.Wk % 64) { set_last_error("lut_gemm: K group size %d must be a multiple of 64 dividing K=%d", a.gs_k, a.Wk); return PLZ_ERR_BAD_SHAPE; }
+    }
+    if (decode && a.fuse == 0) {
+        // the large products run on CTA pairs (lut_gemm_pair.cu); everything else, and shapes it declines, stays here
+        const int rc = launch_lut_gemm_pair(a, stream);
+        if (rc != PLZ_ERR_UNSUPPORTED) return rc;
     }
     // narrow outputs (the rank-16/32 LoRA products) are bound by streaming A: 128-row tiles give twice the CTAs
     const bool big = a.M > 128 && a.J > 64;

@@ -27,6 +27,9 @@ struct LutGemmArgs {
     void* prof;  // optional device buffer of cycle counters, 8 x uint64 per CTA (diagnostics)
 };
 int launch_lut_gemm(const LutGemmArgs& a, cudaStream_t stream);
+// lut_gemm_pair.cu: the decode modes on CTA pairs (cta_group::2); PLZ_ERR_UNSUPPORTED = not a shape for it
+int launch_lut_gemm_pair(const LutGemmArgs& a, cudaStream_t stream);
+extern int g_pair_gemm;  // 0: keep every product on the single-CTA kernel
 extern int g_cta_limit;
 
 // ---- tn_gemm.cu -------------------------------------------------------------------------------

@@ -68,6 +68,13 @@ constexpr uint32_t kTnBBytes = 256 * 64 * 2;  // 4 boxes of [64 m][64 j]
 constexpr uint32_t kTnStageBytes = kTnABytes + kTnBBytes;
 constexpr uint32_t kTnRedBytes = 4 * 256 * 4 * 4;  // per-warp palette-gradient partials
 constexpr uint32_t kTnSmemBytes = kTnStages * kTnStageBytes + kTnRedBytes + 1024 + 256;
+// CTA-pair form (cta_group::2, one 256 x 256 tile per pair): each CTA stages its own 128 i columns and HALF of the j
+// columns, 32 KB per 64 rows of m, so the ring holds six stages; every CTA reads 2/3 of the operand bytes of the one-CTA
+// form for the same work, which matters because this product is bound by the L2 -> SM operand feed.
+constexpr int kTnStagesPair = 6;
+constexpr uint32_t kTnBBytesPair = 128 * 64 * 2;
+constexpr uint32_t kTnStageBytesPair = kTnABytes + kTnBBytesPair;
+constexpr uint32_t kTnSmemBytesPair = kTnStagesPair * kTnStageBytesPair + kTnRedBytes + 1024 + 256;
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -76,38 +83,49 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-template <int EPI, typename LogitT, bool ROWS_K>
+template <int EPI, typename LogitT, bool ROWS_K, bool PAIR>
 __global__ void __launch_bounds__(kTnThreads, 1)
 tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                const __grid_constant__ CUtensorMap tmS0, const __grid_constant__ CUtensorMap tmS1, const TnParams p) {
+    constexpr int kStages = PAIR ? kTnStagesPair : kTnStages;
+    constexpr uint32_t kBBytes = PAIR ? kTnBBytesPair : kTnBBytes;
+    constexpr uint32_t kStageBytes = kTnABytes + kBBytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (base - raw);
-    float* red = reinterpret_cast<float*>(smem + kTnStages * kTnStageBytes);
-    const uint32_t bar_base = base + kTnStages * kTnStageBytes + kTnRedBytes;
+    float* red = reinterpret_cast<float*>(smem + kStages * kStageBytes);
+    const uint32_t bar_base = base + kStages * kStageBytes + kTnRedBytes;
     auto full = [&](int s) { return bar_base + 8u * s; };
-    auto empty = [&](int s) { return bar_base + 8u * (kTnStages + s); };
-    auto acc_full = [&](int b) { return bar_base + 8u * (2 * kTnStages + b); };
-    auto acc_empty = [&](int b) { return bar_base + 8u * (2 * kTnStages + 2 + b); };
+    auto empty = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto acc_full = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+    auto acc_empty = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
-        smem + kTnStages * kTnStageBytes + kTnRedBytes + 8 * (2 * kTnStages + 4));
+        smem + kStages * kStageBytes + kTnRedBytes + 8 * (2 * kStages + 4));
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int tiles_i = (p.I + 127) / 128;
+    // PAIR: the two CTAs of a cluster share every work item; full[] and acc_empty[] are used in the leader's copy only
+    // (remote arrivals / TMA completions from the partner), empty[] and acc_full[] in each CTA's own copy (multicast commit)
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const uint32_t lead_bar_base = PAIR ? leader_addr(bar_base) : bar_base;
+    auto lead_full = [&](int s) { return lead_bar_base + 8u * s; };
+    auto lead_acc_empty = [&](int b) { return lead_bar_base + 8u * (2 * kStages + 2 + b); };
+    const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int n_units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int tiles_i = PAIR ? (p.I + 255) / 256 : (p.I + 127) / 128;
     const int tiles_j = (p.J + 255) / 256;
     const int n_tiles = p.n_items + p.n_side_items;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kTnStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(full(s), 1);
             mbar_init(empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full(b), 1);
-            mbar_init(acc_empty(b), 8);
+            mbar_init(acc_empty(b), PAIR ? 16 : 8);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -116,11 +134,12 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         if (p.n_side_items) { tma_prefetch_desc(&tmS0); tma_prefetch_desc(&tmS1); }
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32((const void*)tmem_slot), 512);
-        tmem_relinquish();
+        if (PAIR) { tmem_alloc_pair(smem_u32((const void*)tmem_slot), 512); tmem_relinquish_pair(); }
+        else { tmem_alloc(smem_u32((const void*)tmem_slot), 512); tmem_relinquish(); }
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (PAIR) cluster_sync_all();   // both CTAs' barriers exist before anyone arrives on the partner's
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -132,7 +151,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         if (item >= p.n_items) {
             job = (p.side[1].splits > 0 && item >= p.side[1].first_item) ? 1 : 0;
             const int r = item - p.side[job].first_item;
-            ti = 0;
+            ti = PAIR ? (int)rank : 0;   // PAIR: the partner's 128 rows lie past the skinny operand: zeros in, nothing out
             tj = r % p.side[job].tiles_j;
             sp = r / p.side[job].tiles_j;
             return;
@@ -148,6 +167,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         tj = r % tiles_j + p.tj_rot;
         if (tj >= tiles_j) tj -= tiles_j;
         sp = r / tiles_j;
+        if (PAIR) ti = 2 * ti + (int)rank;   // this CTA's 128 rows of the pair's 256
     };
     auto m_range = [&](int sp, int job, int& m_begin, int& nkb) {
         const int chunk = (job < 0) ? p.m_chunk : p.side[job].m_chunk;
@@ -160,37 +180,49 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 
     if (warp == 0) {
         if (lane == 0) {
-            int last_fill[kTnStages];
-            for (int s = 0; s < kTnStages; ++s) last_fill[s] = -1;
+            int last_fill[kStages];
+            for (int s = 0; s < kStages; ++s) last_fill[s] = -1;
             bool ok = true;
             int git = 0;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            for (int t = unit; t < n_tiles && ok; t += n_units) {
                 int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
                 tile_coords(t, sp, ti, tj, c_off, c_num, job);
                 m_range(sp, job, m_begin, nkb);
+                const int c_mine = PAIR ? (c_num >> 1) : c_num;                  // j columns this CTA stages
+                const int j_mine = tj * 256 + c_off + (PAIR ? (int)rank * c_mine : 0);
                 for (int it = 0; it < nkb; ++it, ++git) {
-                    const int s = git % kTnStages;
-                    const uint32_t ph = (git / kTnStages) & 1;
+                    const int s = git % kStages;
+                    const uint32_t ph = (git / kStages) & 1;
                     ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY, 0);
                     if (!ok) break;
-                    const uint32_t sA = base + s * kTnStageBytes;
+                    const uint32_t sA = base + s * kStageBytes;
                     const uint32_t sB = sA + kTnABytes;
-                    mbar_arrive_expect_tx(full(s), kTnABytes + (uint32_t)c_num * 128u);
+                    // PAIR: the leader announces the bytes of both CTAs; each CTA's copies complete on the leader's barrier
+                    if (!PAIR) mbar_arrive_expect_tx(full(s), kTnABytes + (uint32_t)c_num * 128u);
+                    else if (rank == 0) mbar_arrive_expect_tx(full(s), 2u * (kTnABytes + (uint32_t)c_mine * 128u));
                     const int m = m_begin + it * 64;
                     const CUtensorMap* mp = (job < 0) ? &tmP : (job == 0 ? &tmS0 : &tmS1);
                     const CUtensorMap* mq = (job < 0) ? &tmQ : (p.side[job].q_is_p ? &tmP : &tmQ);
+                    if (PAIR) {
 #pragma unroll
-                    for (int q = 0; q < 2; ++q) tma_load_2d(sA + q * 8192u, mp, full(s), ti * 128 + q * 64, m);
+                        for (int q = 0; q < 2; ++q) tma_load_2d_pair(sA + q * 8192u, mp, lead_full(s), ti * 128 + q * 64, m);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        if (q * 64 < c_num) tma_load_2d(sB + q * 8192u, mq, full(s), tj * 256 + c_off + q * 64, m);
+                        for (int q = 0; q < 2; ++q)
+                            if (q * 64 < c_mine) tma_load_2d_pair(sB + q * 8192u, mq, lead_full(s), j_mine + q * 64, m);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) tma_load_2d(sA + q * 8192u, mp, full(s), ti * 128 + q * 64, m);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (q * 64 < c_num) tma_load_2d(sB + q * 8192u, mq, full(s), j_mine + q * 64, m);
+                    }
                     last_fill[s] = git;
                 }
             }
-            if (!ok) {
-                for (int s = 0; s < kTnStages; ++s) {
+            if (!ok && !PAIR) {
+                for (int s = 0; s < kStages; ++s) {
                     if (last_fill[s] < 0) continue;
-                    const uint32_t ph = (last_fill[s] / kTnStages) & 1;
+                    const uint32_t ph = (last_fill[s] / kStages) & 1;
                     const uint64_t t0 = globaltimer_ns();
                     while (!mbar_try_wait(full(s), ph)) {
                         if (globaltimer_ns() - t0 > 100000000ull) {
@@ -202,35 +234,41 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // MMA issuer (PAIR: the leader's only). Kept lean on purpose: a lone thread retires a dependent instruction every
+        // five or six cycles and an MMA lasts 128, so the descriptor words are precomputed (one integer add per operand
+        // and MMA) and the usual, already-completed barrier costs a single try_wait.
+        if (lane == 0 && rank == 0) {
             bool ok = true;
-            int git = 0, lt = 0;
-            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+            int lt = 0, s = 0;
+            uint32_t ph = 0;
+            const uint64_t ad0 = make_sdesc(base, 8192u, 1024u);
+            const uint64_t bd0 = make_sdesc(base + kTnABytes, 8192u, 1024u);
+            const uint32_t a_hi = (uint32_t)(ad0 >> 32), b_hi = (uint32_t)(bd0 >> 32);
+            const uint32_t a_lo0 = (uint32_t)ad0, b_lo0 = (uint32_t)bd0;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0;
+            for (int t = unit; t < n_tiles && ok; t += n_units, ++lt) {
                 int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
                 tile_coords(t, sp, ti, tj, c_off, c_num, job);
                 m_range(sp, job, m_begin, nkb);
                 const int buf = lt & 1;
-                const uint32_t idesc = make_idesc(128, c_num, 1, 1);
-                ok = mbar_wait(acc_empty(buf), ((lt >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_ACCUM, 1);
+                const uint32_t idesc = make_idesc(PAIR ? 256 : 128, c_num, 1, 1);
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                ok = mbar_wait_lean(acc_empty(buf), ((lt >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_ACCUM, 1);
                 if (!ok) break;
                 tc_fence_after_sync();
-                for (int it = 0; it < nkb; ++it, ++git) {
-                    const int s = git % kTnStages;
-                    const uint32_t ph = (git / kTnStages) & 1;
-                    ok = mbar_wait(full(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
+                for (int it = 0; it < nkb; ++it) {
+                    ok = mbar_wait_lean(full(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t sA = base + s * kTnStageBytes;
-                    const uint32_t sB = sA + kTnABytes;
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t adesc = make_sdesc(sA + ks * 2048u, 8192u, 1024u);
-                        const uint64_t bdesc = make_sdesc(sB + ks * 2048u, 8192u, 1024u);
-                        umma_bf16(tmem_base + buf * 256u, adesc, bdesc, idesc, (it > 0 || ks > 0) ? 1u : 0u);
-                    }
-                    umma_commit(empty(s));
+                    for (int ks = 0; ks < 4; ++ks)   // 16 rows of m = 2048 bytes per step in both MN-major operands
+                        umma_bf16_words<PAIR ? 2 : 1>(d_tmem, a_lo + ks * 128u, a_hi, b_lo + ks * 128u, b_hi, idesc,
+                                                     (ks > 0) ? 1u : (it > 0 ? 1u : 0u));
+                    if (PAIR) umma_commit_pair(empty(s)); else umma_commit(empty(s));
+                    if (++s == kStages) { s = 0; ph ^= 1u; a_lo = a_lo0; b_lo = b_lo0; }
+                    else { a_lo += kStageBytes >> 4; b_lo += kStageBytes >> 4; }
                 }
-                if (ok) umma_commit(acc_full(buf));
+                if (ok) { if (PAIR) umma_commit_pair(acc_full(buf)); else umma_commit(acc_full(buf)); }
             }
         }
     } else {
@@ -243,7 +281,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         const int ew = warp - 2;  // 0..7
         bool ok = true;
         int lt = 0;
-        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+        for (int t = unit; t < n_tiles && ok; t += n_units, ++lt) {
             int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
             tile_coords(t, sp, ti, tj, c_off, c_num, job);
             m_range(sp, job, m_begin, nkb);
@@ -524,14 +562,17 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty(buf));
+            if (lane == 0) { if (PAIR) mbar_arrive_cluster(lead_acc_empty(buf)); else mbar_arrive(acc_empty(buf)); }
         }
     }
     tc_fence_before_sync();
     __syncthreads();
+    // PAIR: neither CTA leaves while its partner may still read its shared memory (pair MMA operands), arrive on its
+    // barriers or use its tensor memory
+    if (PAIR) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 512);
+        if (PAIR) tmem_dealloc_pair(tmem_base, 512); else tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -539,19 +580,31 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 // host side
 // ---------------------------------------------------------------------------------------------
 
-template <int EPI, typename LogitT, bool ROWS_K>
+template <int EPI, typename LogitT, bool ROWS_K, bool PAIR>
 static int launch_tn_t(const TnArgs& a, const TnParams& p, const CUtensorMap& tmP, const CUtensorMap& tmQ,
                        const CUtensorMap& tmS0, const CUtensorMap& tmS1, int grid, cudaStream_t stream) {
-    auto kern = tn_gemm_kernel<EPI, LogitT, ROWS_K>;
+    auto kern = tn_gemm_kernel<EPI, LogitT, ROWS_K, PAIR>;
+    constexpr uint32_t smem = PAIR ? kTnSmemBytesPair : kTnSmemBytes;
     static bool attr_set[64] = {};
     int dev = 0;
     PLZ_CUDA_CHECK(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        PLZ_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTnSmemBytes));
+        PLZ_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_set[dev & 63] = true;
     }
-    kern<<<grid, kTnThreads, kTnSmemBytes, stream>>>(tmP, tmQ, tmS0, tmS1, p);
-    PLZ_LAUNCH_CHECK();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kTnThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (PAIR) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    PLZ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmS0, tmS1, p));
+    ++g_launch_count;
     return PLZ_OK;
 }
 
@@ -631,7 +684,6 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
         }
     }
     p.status = device_status_ptr();
-    const int tiles = ((a.I + 127) / 128) * ((a.J + 255) / 256) * p.splits;
     int sms = a.sm_count;
     if (sms <= 0) {
         int dev = 0;
@@ -639,7 +691,12 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
         PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     }
     if (g_cta_limit > 0 && g_cta_limit < sms) sms = g_cta_limit;
-    const int grid = tiles < sms ? tiles : sms;
+    // CTA pairs (one 256 x 256 tile per two CTAs) for the fused weight-gradient launches; the plain store form and small
+    // problems stay on one CTA per 128 x 256 tile
+    const bool pair = g_pair_gemm && a.epi != EPI_STORE && a.I >= 256 && a.J >= 256 && sms >= 2;
+    const int tiles = (pair ? (a.I + 255) / 256 : (a.I + 127) / 128) * ((a.J + 255) / 256) * p.splits;
+    const int units = pair ? sms / 2 : sms;
+    const int grid = tiles < units ? tiles : units;   // work units: CTAs, or pairs of CTAs
     p.n_whole = tiles; p.n_items = tiles;
     CUtensorMap tmS0 = tmP, tmS1 = tmP;
     p.n_side_items = 0;
@@ -675,15 +732,23 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
             p.side[0] = p.side[1]; tmS0 = tmS1; p.side[1].splits = 0; p.side[0].first_item = p.n_items;
         }
     }
+    const int ctas = pair ? 2 * grid : grid;
     switch (a.epi) {
-        case EPI_STORE: return launch_tn_t<EPI_STORE, float, false>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream);
+        case EPI_STORE: return launch_tn_t<EPI_STORE, float, false, false>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream);
         case EPI_HARD:
-            return a.rows_are_k ? launch_tn_t<EPI_HARD, float, true>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream)
-                                : launch_tn_t<EPI_HARD, float, false>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream);
+            if (pair) return a.rows_are_k ? launch_tn_t<EPI_HARD, float, true, true>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream)
+                                          : launch_tn_t<EPI_HARD, float, false, true>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream);
+            return a.rows_are_k ? launch_tn_t<EPI_HARD, float, true, false>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream)
+                                : launch_tn_t<EPI_HARD, float, false, false>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream);
         case EPI_SOFT:
-            if (a.rows_are_k) return launch_tn_t<EPI_SOFT, float, true>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream);
-            return a.logits_f16 ? launch_tn_t<EPI_SOFT, __half, false>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream)
-                                : launch_tn_t<EPI_SOFT, float, false>(a, p, tmP, tmQ, tmS0, tmS1, grid, stream);
+            if (pair) {
+                if (a.rows_are_k) return launch_tn_t<EPI_SOFT, float, true, true>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream);
+                return a.logits_f16 ? launch_tn_t<EPI_SOFT, __half, false, true>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream)
+                                    : launch_tn_t<EPI_SOFT, float, false, true>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream);
+            }
+            if (a.rows_are_k) return launch_tn_t<EPI_SOFT, float, true, false>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream);
+            return a.logits_f16 ? launch_tn_t<EPI_SOFT, __half, false, false>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream)
+                                : launch_tn_t<EPI_SOFT, float, false, false>(a, p, tmP, tmQ, tmS0, tmS1, ctas, stream);
     }
     set_last_error("tn_gemm: unknown epilogue %d", a.epi);
     return PLZ_ERR_UNSUPPORTED;

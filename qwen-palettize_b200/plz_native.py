@@ -51,6 +51,7 @@ SIGNATURES = {
     "plz_launch_count": [],
     "plz_device_status": [C.POINTER(C.c_uint32)],
     "plz_set_cta_limit": [_I32],
+    "plz_set_pair_gemm": [_I32],
     "plz_pack_indices": [_P, _I64, _I64, _I32, _I32, _P, _I64, _P],
     "plz_unpack_indices": [_P, _I64, _I32, _I32, _P, _I64, _I64, _P],
     "plz_dequantize": [_WP, _P, _I64, _I64, _P],
