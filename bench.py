@@ -439,8 +439,10 @@ def run_ours(args):
                              "NCCL's own kernels at N > 1 are not included",
         "phases_ms": phase_ms,
         "tflops_step": 3 * GEMM_FLOPS * world / (ms / args.steps * 1e-3) / 1e12,
-        "roofline": {"bound": "tensor", "kernel": {"fwd": "lut_gemm_kernel<2,B_DECODE_K>", "dw": "tn_gemm_kernel<EPI_SOFT,float,true> (+ dA, dB items)",
-                                                    "dx": "lut_gemm_kernel<2,B_DECODE_MN>"}[gemm_phase],
+        "roofline": {"bound": "tensor", "kernel": ({"fwd": "lut_gemm_pair_kernel<B_DECODE_K> (cta_group::2)", "dw": "tn_gemm_kernel<EPI_SOFT,float,rows=k,pair> (cta_group::2; + dA, dB items)",
+                                                     "dx": "lut_gemm_pair_kernel<B_DECODE_MN> (cta_group::2)"} if args.pair_gemm else
+                                                    {"fwd": "lut_gemm_kernel<2,B_DECODE_K>", "dw": "tn_gemm_kernel<EPI_SOFT,float,rows=k> (+ dA, dB items)",
+                                                     "dx": "lut_gemm_kernel<2,B_DECODE_MN>"})[gemm_phase],
                      "achieved": achieved, "peak": peak_val, "unit": "TFLOP/s", "frac": achieved / peak_val,
                      "peak_kind": ("burst" if burst_region else "sustained") + " cuBLAS bf16, " + pk["source"],
                      "timed_region_s": ms * 1e-3,

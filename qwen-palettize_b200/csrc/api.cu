@@ -475,7 +475,7 @@ static int bwd_dw_common(int epi, const plz_weight_t* w, const void* x, int64_t 
     int dev = 0, sms = 0;
     PLZ_CUDA_CHECK(cudaGetDevice(&dev));
     PLZ_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    a.sm_count = sms;
+    a.sm_count = sms; a.prof = g_prof_buffer;
     if (world > 1) {
         a.world = world; a.rank = my_rank; a.scatter_add = scatter_add;
         for (int r = 0; r < world && r < 8; ++r) a.peer_stage[r] = peer_stage[r];

@@ -55,6 +55,7 @@ struct TnArgs {
     float* side_out[2]; long long side_si[2], side_sj[2];
     // fused reduce-scatter of dLogits over peer memory (world > 1): staging base of every rank, as mapped in THIS process
     int world, rank, scatter_add; float* peer_stage[8];
+    void* prof;  // optional device buffer of cycle counters (diagnostics build)
 };
 int launch_tn_gemm(const TnArgs& a, cudaStream_t stream);
 

@@ -59,6 +59,7 @@ struct TnParams {
     // that GPU's NVLink ingress throttles everybody (measured at 8 ranks: the slowest rank's launch 1.4 ms against 0.8).
     int tj_rot;
     StatusWord* status;
+    unsigned long long* prof;  // diagnostics build: [gridDim][8] cycle counters of the MMA thread
 };
 
 constexpr int kTnThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue
@@ -246,6 +247,8 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             const uint32_t a_hi = (uint32_t)(ad0 >> 32), b_hi = (uint32_t)(bd0 >> 32);
             const uint32_t a_lo0 = (uint32_t)ad0, b_lo0 = (uint32_t)bd0;
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
+            long long wait_f = 0, wait_t = 0, n_st = 0;
+            const long long t_begin = PLZ_PROF_ON(p.prof) ? clock64() : 0;
             for (int t = unit; t < n_tiles && ok; t += n_units, ++lt) {
                 int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
                 tile_coords(t, sp, ti, tj, c_off, c_num, job);
@@ -253,11 +256,15 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                 const int buf = lt & 1;
                 const uint32_t idesc = make_idesc(PAIR ? 256 : 128, c_num, 1, 1);
                 const uint32_t d_tmem = tmem_base + buf * 256u;
+                const long long c_t = PLZ_PROF_ON(p.prof) ? clock64() : 0;
                 ok = mbar_wait_lean(acc_empty(buf), ((lt >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_ACCUM, 1);
+                if (PLZ_PROF_ON(p.prof)) wait_t += clock64() - c_t;
                 if (!ok) break;
                 tc_fence_after_sync();
                 for (int it = 0; it < nkb; ++it) {
+                    const long long c_f = PLZ_PROF_ON(p.prof) ? clock64() : 0;
                     ok = mbar_wait_lean(full(s), ph, abort_flag, p.status, ST_TIMEOUT_FULL, 1);
+                    if (PLZ_PROF_ON(p.prof)) { wait_f += clock64() - c_f; ++n_st; }
                     if (!ok) break;
                     tc_fence_after_sync();
 #pragma unroll
@@ -269,6 +276,10 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                     else { a_lo += kStageBytes >> 4; b_lo += kStageBytes >> 4; }
                 }
                 if (ok) { if (PAIR) umma_commit_pair(acc_full(buf)); else umma_commit(acc_full(buf)); }
+            }
+            if (PLZ_PROF_ON(p.prof)) {
+                unsigned long long* o = p.prof + 8ull * blockIdx.x;
+                o[0] = wait_f; o[1] = n_st; o[2] = wait_t; o[3] = clock64() - t_begin; o[4] = lt;
             }
         }
     } else {
@@ -684,6 +695,7 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
         }
     }
     p.status = device_status_ptr();
+    p.prof = (unsigned long long*)a.prof;
     int sms = a.sm_count;
     if (sms <= 0) {
         int dev = 0;
