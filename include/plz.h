@@ -337,6 +337,21 @@ int32_t plz_soft_bwd_elementwise(const plz_weight_t* w, const void* dW, int32_t 
 int32_t plz_weight_grad(const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M, int32_t N, int32_t K, float* dW,
                         int64_t dw_n, int64_t dw_k, void* stream);
 
+/* ---- attention of the decoder layers -----------------------------------------------------------
+ * Causal grouped-query attention on tokens-major activations: q bf16 [B * S, Hq * 128] (row pitch ldq), k / v bf16
+ * [B * S, Hkv * 128], o in the layout of q: exactly what the q/k/v projections write and o_proj reads. S % 128 == 0,
+ * head_dim = 128, Hq % Hkv == 0. o = softmax(q k^T * scale + causal mask) v per (batch, head), fp32 softmax.
+ * lse (fp32 [B, Hq, S], may be NULL in the forward) receives the natural-log sum-exp of the scaled scores; the backward
+ * needs it, together with o, and a workspace dsum_ws of B * Hq * S floats. Gradients dq / dk / dv have the layouts and
+ * pitches of q / k / v and are WRITTEN (dk, dv already summed over the q heads of a group).
+ * The reference has no attention code: it calls the HuggingFace decoder layer (scripts/train_qwen.py:1259-1266; SDPA
+ * selected at scripts/qwen_model.py:454); semantics are those of transformers' Qwen3Attention after q/k norm and RoPE. */
+int32_t plz_attn_fwd(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, int32_t B, int32_t S,
+                     int32_t Hq, int32_t Hkv, int32_t head_dim, float scale, void* o, int64_t ldo, float* lse, void* stream);
+int32_t plz_attn_bwd(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const void* o, const void* d_o,
+                     int64_t ldo, const float* lse, int32_t B, int32_t S, int32_t Hq, int32_t Hkv, int32_t head_dim, float scale,
+                     float* dsum_ws, void* dq, void* dk, void* dv, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

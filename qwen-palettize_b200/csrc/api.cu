@@ -797,4 +797,23 @@ int32_t plz_weight_grad(const void* x, int64_t ldx, const void* dY, int64_t lddy
     return launch_tn_gemm(a, (cudaStream_t)stream);
 }
 
+// ---- attention --------------------------------------------------------------------------------------------
+int32_t plz_attn_fwd(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, int32_t B, int32_t S,
+                     int32_t Hq, int32_t Hkv, int32_t head_dim, float scale, void* o, int64_t ldo, float* lse, void* stream) {
+    AttnArgs a = {};
+    a.B = B; a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.head_dim = head_dim; a.scale = scale;
+    a.q = q; a.ldq = ldq; a.k = k; a.ldk = ldk; a.v = v; a.ldv = ldv; a.o = o; a.ldo = ldo; a.lse = lse;
+    return launch_attn_fwd(a, (cudaStream_t)stream);
+}
+
+int32_t plz_attn_bwd(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const void* o, const void* d_o,
+                     int64_t ldo, const float* lse, int32_t B, int32_t S, int32_t Hq, int32_t Hkv, int32_t head_dim, float scale,
+                     float* dsum_ws, void* dq, void* dk, void* dv, void* stream) {
+    AttnArgs a = {};
+    a.B = B; a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.head_dim = head_dim; a.scale = scale;
+    a.q = q; a.ldq = ldq; a.k = k; a.ldk = ldk; a.v = v; a.ldv = ldv; a.o = const_cast<void*>(o); a.ldo = ldo;
+    a.lse = const_cast<float*>(lse); a.d_o = d_o; a.dsum = dsum_ws; a.dq = dq; a.dk = dk; a.dv = dv;
+    return launch_attn_bwd(a, (cudaStream_t)stream);
+}
+
 }  // extern "C"

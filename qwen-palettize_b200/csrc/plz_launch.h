@@ -117,6 +117,21 @@ struct BwdElemArgs {
 int launch_soft_bwd_elementwise(const BwdElemArgs& a, cudaStream_t stream);
 int launch_col_sum(const void* dY, long long ld, int M, int N, float* out, cudaStream_t stream);
 
+// ---- attention.cu -------------------------------------------------------------------------------
+struct AttnArgs {
+    int B, S, Hq, Hkv, head_dim;
+    float scale;
+    const void* q; long long ldq;     // bf16 [B * S, Hq * head_dim]
+    const void* k; long long ldk;     // bf16 [B * S, Hkv * head_dim]
+    const void* v; long long ldv;
+    void* o; long long ldo;           // forward output / backward input, layout of q
+    float* lse;                       // fp32 [B, Hq, S]
+    // backward
+    const void* d_o; void* dq; void* dk; void* dv; float* dsum;   // gradients in the layouts (and pitches) of o, q, k, v
+};
+int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream);
+int launch_attn_bwd(const AttnArgs& a, cudaStream_t stream);
+
 // ---- train_ops.cu ------------------------------------------------------------------------------
 struct AdamParams {
     float* master; float* m; float* v;

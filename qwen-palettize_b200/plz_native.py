@@ -91,6 +91,8 @@ SIGNATURES = {
     "plz_soft_weights": [_I32, C.POINTER(_WP), C.POINTER(_GP), C.POINTER(_NP), _F, _I32, C.POINTER(C.POINTER(SoftOut)), _P],
     "plz_soft_bwd_elementwise": [_WP, _P, _I32, _I64, _I64, _P, _I64, _I64, _I64, _GP, _P, _P],
     "plz_weight_grad": [_P, _I64, _P, _I64, _I32, _I32, _I32, _P, _I64, _I64, _P],
+    "plz_attn_fwd": [_P, _I64, _P, _I64, _P, _I64, _I32, _I32, _I32, _I32, _I32, _F, _P, _I64, _P, _P],
+    "plz_attn_bwd": [_P, _I64, _P, _I64, _P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _I32, _I32, _F, _P, _P, _P, _P, _P],
     "plz_distill_loss": [_P, _I64, _P, _I64, _I32, _I32, _F, _F, _F, _P, _P, _P, _I64, _I32, _P],
 }
 _RESTYPES = {"plz_last_error": C.c_char_p, "plz_launch_count": C.c_uint64}

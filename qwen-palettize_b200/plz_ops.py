@@ -491,3 +491,34 @@ def weight_grad(x: torch.Tensor, dy: torch.Tensor, layout: str = "kn") -> torch.
     P.check(P.lib().plz_weight_grad(x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), M, N, K, dw.data_ptr(), s_n, s_k,
                                     P.stream_ptr()), "plz_weight_grad")
     return dw
+
+
+def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, S: int, n_heads: int, n_kv_heads: int,
+                      head_dim: int = 128, scale: float | None = None):
+    """Causal GQA attention. q bf16 [B*S, n_heads*head_dim], k / v bf16 [B*S, n_kv_heads*head_dim] (rows may be pitched: slices of
+    one fused projection output are fine). Returns (o bf16 [B*S, n_heads*head_dim], lse fp32 [B, n_heads, S])."""
+    _mat(q, n_heads * head_dim), _mat(k, n_kv_heads * head_dim), _mat(v, n_kv_heads * head_dim)
+    assert q.shape[0] == B * S == k.shape[0] == v.shape[0]
+    o = torch.empty(B * S, n_heads * head_dim, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(B, n_heads, S, dtype=torch.float32, device=q.device)
+    sc = float(scale) if scale is not None else head_dim ** -0.5
+    P.check(P.lib().plz_attn_fwd(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), B, S, n_heads, n_kv_heads,
+                                 head_dim, sc, o.data_ptr(), o.stride(0), lse.data_ptr(), P.stream_ptr()), "plz_attn_fwd")
+    return o, lse
+
+
+def attention_backward(q, k, v, o, do, lse, B: int, S: int, n_heads: int, n_kv_heads: int, head_dim: int = 128, scale: float | None = None):
+    """(dq, dk, dv) in the layouts of (q, k, v); dk / dv are summed over the query heads of each group."""
+    _mat(do, n_heads * head_dim), _mat(o, n_heads * head_dim)
+    assert o.stride(0) == do.stride(0)
+    dq = torch.empty(B * S, n_heads * head_dim, dtype=torch.bfloat16, device=q.device)
+    dk = torch.empty(B * S, n_kv_heads * head_dim, dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty_like(dk)
+    assert dq.stride(0) == q.stride(0) and dk.stride(0) == k.stride(0) and dv.stride(0) == v.stride(0), \
+        "gradients are written with the pitches of q / k / v: pass contiguous q, k, v"
+    ws = torch.empty(B * n_heads * S, dtype=torch.float32, device=q.device)
+    sc = float(scale) if scale is not None else head_dim ** -0.5
+    P.check(P.lib().plz_attn_bwd(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), o.data_ptr(), do.data_ptr(),
+                                 o.stride(0), lse.data_ptr(), B, S, n_heads, n_kv_heads, head_dim, sc, ws.data_ptr(), dq.data_ptr(),
+                                 dk.data_ptr(), dv.data_ptr(), P.stream_ptr()), "plz_attn_bwd")
+    return dq, dk, dv
