@@ -352,6 +352,31 @@ int32_t plz_attn_bwd(const void* q, int64_t ldq, const void* k, int64_t ldk, con
                      int64_t ldo, const float* lse, int32_t B, int32_t S, int32_t Hq, int32_t Hkv, int32_t head_dim, float scale,
                      float* dsum_ws, void* dq, void* dk, void* dv, void* stream);
 
+/* ---- element-wise ops of a decoder layer -------------------------------------------------------
+ * The reference has no code for these (it calls the HuggingFace decoder layer, scripts/train_qwen.py:1259-1266);
+ * semantics follow transformers' Qwen3RMSNorm / Qwen3Attention (q_norm, k_norm, apply_rotary_pos_emb) / Qwen3MLP.
+ * plz_rmsnorm_fwd: h = bf16(bf16(x * rstd) * g), rstd = 1 / sqrt(mean x^2 + eps) also written to rstd (fp32 [M], may be NULL);
+ *   the materialised form of the norm that plz_hard_fwd_norm folds into a GEMM, for Linears that carry a LoRA branch.
+ * plz_qknorm_rope_fwd: per (token, head) vector of 128: RMSNorm with weight w (bf16 [128], may be NULL), then the rotary
+ *   embedding out[i] = y[i] cos_i - y[i+64] sin_i, out[i+64] = y[i+64] cos_i + y[i] sin_i with cos / sin fp32 [S, 64] tables
+ *   indexed by the token's position inside its sequence (token index % S). x / out: bf16 [tokens, H * 128].
+ * plz_qknorm_rope_bwd: dy -> dx, and dw[128] += (fp32, ACCUMULATED; NULL to skip).
+ * plz_swiglu_fwd: act = bf16(silu(gate)) * up.  plz_add: out = a + b (+ c if not NULL), fp32 sum rounded once (residuals,
+ *   sums of input gradients).
+ * plz_bwd_dw_hard_lora: plz_bwd_dw_hard plus the LoRA factor gradients in the same launch (as plz_bwd_dw_soft_lora). */
+int32_t plz_rmsnorm_fwd(const void* x, int64_t ldx, const void* g, int32_t M, int32_t K, float eps, void* h, int64_t ldh, float* rstd,
+                        void* stream);
+int32_t plz_qknorm_rope_fwd(const void* x, int64_t ldx, const void* w, const float* cos_tab, const float* sin_tab, int64_t tokens,
+                            int32_t H, int32_t S, int32_t head_dim, float eps, void* out, int64_t ldo, void* stream);
+int32_t plz_qknorm_rope_bwd(const void* x, int64_t ldx, const void* w, const float* cos_tab, const float* sin_tab, const void* dy,
+                            int64_t lddy, int64_t tokens, int32_t H, int32_t S, int32_t head_dim, float eps, void* dx, int64_t lddx,
+                            float* dw, void* stream);
+int32_t plz_swiglu_fwd(const void* gate, int64_t ldg, const void* up, int64_t ldu, int32_t M, int32_t N, void* act, int64_t lda, void* stream);
+int32_t plz_add(const void* a, int64_t lda, const void* b, int64_t ldb, const void* c, int64_t ldc, int32_t M, int32_t N, void* out,
+                int64_t ldo, void* stream);
+int32_t plz_bwd_dw_hard_lora(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M, float* dpalette,
+                             const void* t, const void* dt, int32_t rank, float* dA, float* dB, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

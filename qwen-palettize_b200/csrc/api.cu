@@ -816,4 +816,64 @@ int32_t plz_attn_bwd(const void* q, int64_t ldq, const void* k, int64_t ldk, con
     return launch_attn_bwd(a, (cudaStream_t)stream);
 }
 
+// ---- element-wise ops of a decoder layer ----------------------------------------------------------------
+static bool rows16(const void* p, int64_t ld) { return (((uintptr_t)p & 15) == 0) && ((ld & 7) == 0); }
+
+int32_t plz_rmsnorm_fwd(const void* x, int64_t ldx, const void* g, int32_t M, int32_t K, float eps, void* h, int64_t ldh, float* rstd,
+                        void* stream) {
+    if (M < 0 || K <= 0 || (K & 7)) { set_last_error("rmsnorm_fwd: K must be a positive multiple of 8"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !h) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (!rows16(x, ldx) || !rows16(h, ldh) || (g && ((uintptr_t)g & 15))) { set_last_error("rmsnorm_fwd: rows must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    return launch_rmsnorm_fwd(x, ldx, g, M, K, eps, h, ldh, rstd, (cudaStream_t)stream);
+}
+
+int32_t plz_qknorm_rope_fwd(const void* x, int64_t ldx, const void* w, const float* cos_tab, const float* sin_tab, int64_t tokens,
+                            int32_t H, int32_t S, int32_t head_dim, float eps, void* out, int64_t ldo, void* stream) {
+    if (tokens < 0 || H <= 0 || S <= 0 || head_dim != 128) { set_last_error("qknorm_rope: head_dim must be 128 (H=%d S=%d)", H, S); return PLZ_ERR_BAD_SHAPE; }
+    if (tokens == 0) return PLZ_OK;
+    if (!x || !cos_tab || !sin_tab || !out) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)x & 3) || ((uintptr_t)out & 3) || (ldx & 1) || (ldo & 1) || ((uintptr_t)cos_tab & 7) || ((uintptr_t)sin_tab & 7)) {
+        set_last_error("qknorm_rope: misaligned input"); return PLZ_ERR_BAD_ALIGN;
+    }
+    return launch_qknorm_rope(0, x, ldx, w, cos_tab, sin_tab, nullptr, 0, tokens, H, S, eps, out, ldo, nullptr, (cudaStream_t)stream);
+}
+
+int32_t plz_qknorm_rope_bwd(const void* x, int64_t ldx, const void* w, const float* cos_tab, const float* sin_tab, const void* dy,
+                            int64_t lddy, int64_t tokens, int32_t H, int32_t S, int32_t head_dim, float eps, void* dx, int64_t lddx,
+                            float* dw, void* stream) {
+    if (tokens < 0 || H <= 0 || S <= 0 || head_dim != 128) { set_last_error("qknorm_rope: head_dim must be 128 (H=%d S=%d)", H, S); return PLZ_ERR_BAD_SHAPE; }
+    if (tokens == 0) return PLZ_OK;
+    if (!x || !cos_tab || !sin_tab || !dy || !dx) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)x & 3) || ((uintptr_t)dy & 3) || ((uintptr_t)dx & 3) || (ldx & 1) || (lddy & 1) || (lddx & 1)) {
+        set_last_error("qknorm_rope: misaligned input"); return PLZ_ERR_BAD_ALIGN;
+    }
+    return launch_qknorm_rope(1, x, ldx, w, cos_tab, sin_tab, dy, lddy, tokens, H, S, eps, dx, lddx, dw, (cudaStream_t)stream);
+}
+
+int32_t plz_swiglu_fwd(const void* gate, int64_t ldg, const void* up, int64_t ldu, int32_t M, int32_t N, void* act, int64_t lda, void* stream) {
+    if (M < 0 || N <= 0 || (N & 7)) { set_last_error("swiglu_fwd: N must be a positive multiple of 8"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!gate || !up || !act) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (!rows16(gate, ldg) || !rows16(up, ldu) || !rows16(act, lda)) { set_last_error("swiglu_fwd: rows must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    return launch_swiglu_fwd(gate, ldg, up, ldu, M, N, act, lda, (cudaStream_t)stream);
+}
+
+int32_t plz_add(const void* a, int64_t lda, const void* b, int64_t ldb, const void* c, int64_t ldc, int32_t M, int32_t N, void* out,
+                int64_t ldo, void* stream) {
+    if (M < 0 || N <= 0 || (N & 7)) { set_last_error("add: N must be a positive multiple of 8"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!a || !b || !out) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (!rows16(a, lda) || !rows16(b, ldb) || !rows16(out, ldo) || (c && !rows16(c, ldc))) { set_last_error("add: rows must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    return launch_add(a, lda, b, ldb, c, ldc, M, N, out, ldo, (cudaStream_t)stream);
+}
+
+int32_t plz_bwd_dw_hard_lora(const plz_weight_t* w, const void* x, int64_t ldx, const void* dY, int64_t lddy, int32_t M, float* dpalette,
+                             const void* t, const void* dt, int32_t rank, float* dA, float* dB, void* stream) {
+    if (!dpalette) { set_last_error("null dpalette"); return PLZ_ERR_NULL; }
+    if (rank <= 0 || rank > 64 || rank % 8) { set_last_error("LoRA rank %d must be a multiple of 8 in [8, 64]", rank); return PLZ_ERR_BAD_SHAPE; }
+    if ((dA && !dt) || (dB && !t)) { set_last_error("bwd_dw_hard_lora: dA needs dt and dB needs t"); return PLZ_ERR_NULL; }
+    return bwd_dw_common(EPI_HARD, w, x, ldx, dY, lddy, M, nullptr, nullptr, 1.0f, nullptr, dpalette, stream, t, dt, rank, dA, dB);
+}
+
 }  // extern "C"

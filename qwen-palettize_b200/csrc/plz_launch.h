@@ -132,6 +132,15 @@ struct AttnArgs {
 int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 int launch_attn_bwd(const AttnArgs& a, cudaStream_t stream);
 
+// ---- layer_ops.cu -------------------------------------------------------------------------------
+int launch_rmsnorm_fwd(const void* x, long long ldx, const void* g, int M, int K, float eps, void* h, long long ldh, float* rstd,
+                       cudaStream_t stream);
+int launch_qknorm_rope(int backward, const void* x, long long ldx, const void* w, const float* cs, const float* sn, const void* dy,
+                       long long lddy, long long tokens, int H, int S, float eps, void* out, long long ldo, float* dw, cudaStream_t stream);
+int launch_swiglu_fwd(const void* gate, long long ldg, const void* up, long long ldu, int M, int N, void* act, long long lda, cudaStream_t stream);
+int launch_add(const void* a, long long lda, const void* b, long long ldb, const void* c, long long ldc, int M, int N, void* out, long long ldo,
+               cudaStream_t stream);
+
 // ---- train_ops.cu ------------------------------------------------------------------------------
 struct AdamParams {
     float* master; float* m; float* v;

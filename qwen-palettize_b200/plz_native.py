@@ -93,6 +93,12 @@ SIGNATURES = {
     "plz_weight_grad": [_P, _I64, _P, _I64, _I32, _I32, _I32, _P, _I64, _I64, _P],
     "plz_attn_fwd": [_P, _I64, _P, _I64, _P, _I64, _I32, _I32, _I32, _I32, _I32, _F, _P, _I64, _P, _P],
     "plz_attn_bwd": [_P, _I64, _P, _I64, _P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _I32, _I32, _F, _P, _P, _P, _P, _P],
+    "plz_rmsnorm_fwd": [_P, _I64, _P, _I32, _I32, _F, _P, _I64, _P, _P],
+    "plz_qknorm_rope_fwd": [_P, _I64, _P, _P, _P, _I64, _I32, _I32, _I32, _F, _P, _I64, _P],
+    "plz_qknorm_rope_bwd": [_P, _I64, _P, _P, _P, _P, _I64, _I64, _I32, _I32, _I32, _F, _P, _I64, _P, _P],
+    "plz_swiglu_fwd": [_P, _I64, _P, _I64, _I32, _I32, _P, _I64, _P],
+    "plz_add": [_P, _I64, _P, _I64, _P, _I64, _I32, _I32, _P, _I64, _P],
+    "plz_bwd_dw_hard_lora": [_WP, _P, _I64, _P, _I64, _I32, _P, _P, _P, _I32, _P, _P, _P],
     "plz_distill_loss": [_P, _I64, _P, _I64, _I32, _I32, _F, _F, _F, _P, _P, _P, _I64, _I32, _P],
 }
 _RESTYPES = {"plz_last_error": C.c_char_p, "plz_launch_count": C.c_uint64}

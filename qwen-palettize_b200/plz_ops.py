@@ -522,3 +522,76 @@ def attention_backward(q, k, v, o, do, lse, B: int, S: int, n_heads: int, n_kv_h
                                  o.stride(0), lse.data_ptr(), B, S, n_heads, n_kv_heads, head_dim, sc, ws.data_ptr(), dq.data_ptr(),
                                  dk.data_ptr(), dv.data_ptr(), P.stream_ptr()), "plz_attn_bwd")
     return dq, dk, dv
+
+
+def rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor | None, eps: float = 1e-6):
+    """(h bf16 [M, K] = rmsnorm(x) * weight, rstd fp32 [M])."""
+    M, K = x.shape
+    _mat(x, K)
+    h = torch.empty(M, K, dtype=torch.bfloat16, device=x.device)
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    P.check(P.lib().plz_rmsnorm_fwd(x.data_ptr(), x.stride(0), weight.data_ptr() if weight is not None else None, M, K, float(eps),
+                                    h.data_ptr(), h.stride(0), rstd.data_ptr(), P.stream_ptr()), "plz_rmsnorm_fwd")
+    return h, rstd
+
+
+def rope_tables(S: int, head_dim: int = 128, theta: float = 1e6, device="cuda"):
+    """(cos, sin) fp32 [S, head_dim / 2] of transformers' default rotary embedding: angle = position * theta^(-2i / head_dim)."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
+    ang = torch.arange(S, dtype=torch.float32)[:, None] * inv_freq[None, :]
+    return ang.cos().contiguous().to(device), ang.sin().contiguous().to(device)
+
+
+def qknorm_rope_forward(x: torch.Tensor, weight: torch.Tensor | None, cos: torch.Tensor, sin: torch.Tensor, n_heads: int, S: int,
+                        eps: float = 1e-6) -> torch.Tensor:
+    """Per-head RMSNorm (weight bf16 [128]) + rotary embedding of x bf16 [tokens, n_heads * 128] (rows may be pitched)."""
+    _mat(x, n_heads * 128)
+    out = torch.empty(x.shape[0], n_heads * 128, dtype=torch.bfloat16, device=x.device)
+    P.check(P.lib().plz_qknorm_rope_fwd(x.data_ptr(), x.stride(0), weight.data_ptr() if weight is not None else None, cos.data_ptr(),
+                                        sin.data_ptr(), x.shape[0], n_heads, S, 128, float(eps), out.data_ptr(), out.stride(0), P.stream_ptr()),
+            "plz_qknorm_rope_fwd")
+    return out
+
+
+def qknorm_rope_backward(x: torch.Tensor, weight: torch.Tensor | None, cos: torch.Tensor, sin: torch.Tensor, dy: torch.Tensor, n_heads: int,
+                         S: int, eps: float = 1e-6, want_dw: bool = True):
+    """(dx bf16 in the shape of x, dw fp32 [128] or None) from dy, the gradient of qknorm_rope_forward's output."""
+    _mat(x, n_heads * 128), _mat(dy, n_heads * 128)
+    dx = torch.empty(x.shape[0], n_heads * 128, dtype=torch.bfloat16, device=x.device)
+    dw = torch.zeros(128, dtype=torch.float32, device=x.device) if (want_dw and weight is not None) else None
+    P.check(P.lib().plz_qknorm_rope_bwd(x.data_ptr(), x.stride(0), weight.data_ptr() if weight is not None else None, cos.data_ptr(),
+                                        sin.data_ptr(), dy.data_ptr(), dy.stride(0), x.shape[0], n_heads, S, 128, float(eps), dx.data_ptr(),
+                                        dx.stride(0), dw.data_ptr() if dw is not None else None, P.stream_ptr()), "plz_qknorm_rope_bwd")
+    return dx, dw
+
+
+def swiglu_forward(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    M, N = gate.shape
+    _mat(gate, N), _mat(up, N)
+    act = torch.empty(M, N, dtype=torch.bfloat16, device=gate.device)
+    P.check(P.lib().plz_swiglu_fwd(gate.data_ptr(), gate.stride(0), up.data_ptr(), up.stride(0), M, N, act.data_ptr(), act.stride(0),
+                                   P.stream_ptr()), "plz_swiglu_fwd")
+    return act
+
+
+def add(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """a + b (+ c) of bf16 [M, N] matrices in one pass (fp32 sum, one rounding)."""
+    M, N = a.shape
+    _mat(a, N), _mat(b, N)
+    o = out if out is not None else torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    P.check(P.lib().plz_add(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), c.data_ptr() if c is not None else None,
+                            c.stride(0) if c is not None else 0, M, N, o.data_ptr(), o.stride(0), P.stream_ptr()), "plz_add")
+    return o
+
+
+def backward_dw_hard_lora(w: PackedWeight, x: torch.Tensor, dy: torch.Tensor, t: torch.Tensor, dt: torch.Tensor):
+    """(dPalette fp32 [groups, 4], dA fp32 [r, K], dB fp32 [N, r]) of a hard palettized Linear with LoRA, one launch."""
+    _mat(x, w.K), _mat(dy, w.N)
+    r = t.shape[1]
+    dpal = torch.zeros(w.palette.numel() // 4, 4, dtype=torch.float32, device=x.device)
+    da = torch.zeros(r, w.K, dtype=torch.float32, device=x.device)
+    db = torch.zeros(w.N, r, dtype=torch.float32, device=x.device)
+    d = w.desc()
+    P.check(P.lib().plz_bwd_dw_hard_lora(C.byref(d), x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), x.shape[0], dpal.data_ptr(),
+                                         t.data_ptr(), dt.data_ptr(), r, da.data_ptr(), db.data_ptr(), P.stream_ptr()), "plz_bwd_dw_hard_lora")
+    return dpal, da, db
