@@ -660,6 +660,38 @@ def extra_configs(torch, ops, plz_native, dev, pk):
         plz_native.lib().plz_set_smallm_overlap(0)
     out["smallm_layer_7_linears"] = dict(layer, weight_bytes_per_layer=lbytes, layers_rotated=lcopies,
                                          launches_per_layer=4, timing="CUDA graph of 10 layers, programmatic dependent launches")
+    # config 2: four Qwen3-style decoder layers (hidden 2560, 32 / 8 heads of 128, intermediate 9728, rank-16 LoRA on all seven
+    # hard-palettized Linears), forward + backward at batch 32 x seq 512, every op a kernel of this library
+    import decoder_layer as DL
+    cfg = DL.LayerConfig()
+    Bc, Sc, n_layers = 32, 512, 4
+    layers = [DL.random_layer(cfg, dev, seed=10 + i) for i in range(n_layers)]
+    gl = torch.Generator(device=dev).manual_seed(3)
+    xl = torch.randn(Bc * Sc, cfg.hidden, generator=gl, device=dev).to(torch.bfloat16)
+    dyl = torch.randn(Bc * Sc, cfg.hidden, generator=gl, device=dev).to(torch.bfloat16)
+    cos, sin = ops.rope_tables(Sc, cfg.head_dim, cfg.rope_theta, dev)
+    n0 = plz_native.lib().plz_launch_count()
+    DL.stack_forward_backward(cfg, layers, xl, dyl, Bc, Sc, cos, sin)
+    launches = plz_native.lib().plz_launch_count() - n0
+    for _ in range(2):
+        DL.stack_forward_backward(cfg, layers, xl, dyl, Bc, Sc, cos, sin)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(5):
+        DL.stack_forward_backward(cfg, layers, xl, dyl, Bc, Sc, cos, sin)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 5
+    lin_fl = 3 * 2.0 * Bc * Sc * sum(n * k for n, k in cfg.shapes().values())
+    att_fl = 7 * 2.0 * Bc * cfg.n_heads * Sc * Sc * cfg.head_dim / 2       # 2 forward + 5 backward GEMMs, causal half
+    out["config2_stack_4_layers_B32_S512"] = {
+        "ms": ms, "tokens_per_s": Bc * Sc / (ms * 1e-3), "tflops": n_layers * (lin_fl + att_fl) / (ms * 1e-3) / 1e12,
+        "frac_of_burst_peak": n_layers * (lin_fl + att_fl) / (ms * 1e-3) / 1e12 / pk["tflops_burst"], "kernel_launches": int(launches),
+        "what": "4 decoder layers forward + backward (activations kept, hand-written backward): RMSNorm, q/k/v/o/gate/up/down hard LUT GEMMs "
+                "with LoRA, q/k norm + RoPE, causal GQA attention on tcgen05, SwiGLU, residuals; gradients of palettes, LoRA factors and norm weights"}
+    del layers, xl, dyl
+    torch.cuda.empty_cache()
     # the reference API (layout R: fp16 planar logits (4, K, N), one palette per 256 output columns) through torch autograd
     import fused_lut_linear_cuda as F
     g2 = torch.Generator(device=dev).manual_seed(2)
