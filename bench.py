@@ -692,6 +692,63 @@ def extra_configs(torch, ops, plz_native, dev, pk):
                 "with LoRA, q/k norm + RoPE, causal GQA attention on tcgen05, SwiGLU, residuals; gradients of palettes, LoRA factors and norm weights"}
     del layers, xl, dyl
     torch.cuda.empty_cache()
+    # config 3: the full 36-layer model (vocab 151936, tied embeddings), every Linear hard-palettized, inference only:
+    # prefill of 8 x 2048 tokens, then one decode step at batch 1 / 8 / 64 against a 2048-token bf16 key / value cache
+    import decode_model as DM
+    mcfg = DM.ModelConfig()
+    model = DM.PalettizedQwen.random(mcfg, dev, seed=4, max_positions=2304)
+    gm = torch.Generator(device=dev).manual_seed(5)
+    c3 = {"what": "36 layers, hidden 2560, 32 / 8 heads of 128, intermediate 9728, vocab 151936 tied; random-init; all seven Linears per "
+                  "layer 2-bit palettized, no LoRA", "layer_weight_bytes": model.weight_bytes(), "embedding_bytes": model.embed.numel() * 2}
+    Bp, Sp = 8, 2048
+    ids = torch.randint(0, mcfg.vocab, (Bp, Sp), generator=gm, device=dev)
+    cache = model.new_cache(Bp, Sp)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for it in range(3):
+        cache.length = 0
+        torch.cuda.synchronize()
+        a.record()
+        model.prefill(ids, cache)
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    ms = min(times[1:])
+    lin_fl = 2.0 * Bp * Sp * (sum(n * k for n, k in mcfg.shapes().values()) * mcfg.n_layers)
+    att_fl = mcfg.n_layers * 2 * 2.0 * Bp * mcfg.n_heads * Sp * Sp * mcfg.head_dim / 2
+    c3["prefill_B8_S2048"] = {"ms": ms, "tokens_per_s": Bp * Sp / (ms * 1e-3), "tflops": (lin_fl + att_fl) / (ms * 1e-3) / 1e12,
+                              "frac_of_burst_peak": (lin_fl + att_fl) / (ms * 1e-3) / 1e12 / pk["tflops_burst"]}
+    del cache, ids
+    torch.cuda.empty_cache()
+    T0 = 2048
+    for Bd in (1, 8, 64):
+        cache = model.new_cache(Bd, T0 + 1)
+        cache.k.normal_(generator=gm)
+        cache.v.normal_(generator=gm)
+        cache.length = T0
+        step_ids = torch.randint(0, mcfg.vocab, (Bd,), generator=gm, device=dev)
+        n0 = plz_native.lib().plz_launch_count()
+        graph, _ = model.decode_graph(step_ids, cache, T0)
+        launches = (plz_native.lib().plz_launch_count() - n0) // 2
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(10):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / 10
+        kv_bytes = 2 * mcfg.n_layers * Bd * (T0 + 1) * mcfg.n_kv_heads * mcfg.head_dim * 2
+        total = model.weight_bytes() + model.embed.numel() * 2 + kv_bytes
+        c3[f"decode_B{Bd}_T2048"] = {"ms_per_step": ms, "tokens_per_s": Bd / (ms * 1e-3), "kv_cache_bytes": kv_bytes, "kernel_launches": int(launches),
+                                     "GBps": total / (ms * 1e-3) / 1e9, "frac_of_hbm": total / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                                     "timing": "CUDA graph of one whole step (embedding, 36 layers, final norm, logits), replayed"}
+        del graph, cache
+        torch.cuda.empty_cache()
+    out["config3_inference_36_layers"] = c3
+    del model
+    torch.cuda.empty_cache()
     # the reference API (layout R: fp16 planar logits (4, K, N), one palette per 256 output columns) through torch autograd
     import fused_lut_linear_cuda as F
     g2 = torch.Generator(device=dev).manual_seed(2)

@@ -352,6 +352,21 @@ int32_t plz_attn_bwd(const void* q, int64_t ldq, const void* k, int64_t ldk, con
                      int64_t ldo, const float* lse, int32_t B, int32_t S, int32_t Hq, int32_t Hkv, int32_t head_dim, float scale,
                      float* dsum_ws, void* dq, void* dk, void* dv, void* stream);
 
+/* Attention of ONE new token per sequence against a key / value cache (token decode; transformers' Qwen3Attention at
+ * q_len = 1 with a DynamicCache): out[b, h] = softmax(q[b, h] . K[b, 0..T, h / group] * scale) V[b, 0..T, h / group].
+ * q / out: bf16 [B, Hq * 128]; caches bf16 [B, T_max, Hkv * 128] given by the element strides between sequences and between
+ * positions; T counts the positions to attend to (the new token's key and value already stored). head_dim = 128.
+ * ws: plz_attn_decode_ws_bytes(B, T, Hq, Hkv) bytes of scratch (the sequence is split over several CTAs when B * Hkv alone
+ * would not fill the GPU; 0 bytes when it is not split), 16-byte aligned. */
+int64_t plz_attn_decode_ws_bytes(int32_t B, int32_t T, int32_t Hq, int32_t Hkv);
+int32_t plz_attn_decode(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, int64_t batch_stride, int64_t tok_stride,
+                        int32_t B, int32_t T, int32_t Hq, int32_t Hkv, int32_t head_dim, float scale, void* out, int64_t ldo, void* ws,
+                        int64_t ws_bytes, void* stream);
+/* out[i, :] = table[ids[i], :], bf16 rows of `width` elements (embed_tokens of the HuggingFace model the reference wraps,
+ * scripts/qwen_model.py:897-951). An id outside [0, vocab) gives a zero row and stores 1 to *bad (device int32, may be NULL). */
+int32_t plz_embed_gather(const void* table, int64_t ldt, const int64_t* ids, int64_t n, int32_t width, int64_t vocab, void* out, int64_t ldo,
+                         int32_t* bad, void* stream);
+
 /* ---- element-wise ops of a decoder layer -------------------------------------------------------
  * The reference has no code for these (it calls the HuggingFace decoder layer, scripts/train_qwen.py:1259-1266);
  * semantics follow transformers' Qwen3RMSNorm / Qwen3Attention (q_norm, k_norm, apply_rotary_pos_emb) / Qwen3MLP.

@@ -9,7 +9,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["api.cu", "lut_gemm.cu", "lut_gemm_pair.cu", "tn_gemm.cu", "elementwise.cu", "gemv.cu", "smallm_mma.cu", "train_ops.cu", "soft_tensors.cu", "attention.cu", "layer_ops.cu"]
+SOURCES = ["api.cu", "lut_gemm.cu", "lut_gemm_pair.cu", "tn_gemm.cu", "elementwise.cu", "gemv.cu", "smallm_mma.cu", "train_ops.cu", "soft_tensors.cu", "attention.cu", "attention_decode.cu", "layer_ops.cu"]
 HEADERS = ["plz_sm100.cuh", "plz_host.h", "plz_launch.h", "soft_math.cuh", os.path.join("..", "..", "include", "plz.h")]
 LIB = os.path.join(HERE, "libplz.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

@@ -816,6 +816,39 @@ int32_t plz_attn_bwd(const void* q, int64_t ldq, const void* k, int64_t ldk, con
     return launch_attn_bwd(a, (cudaStream_t)stream);
 }
 
+int64_t plz_attn_decode_ws_bytes(int32_t B, int32_t T, int32_t Hq, int32_t Hkv) {
+    if (B <= 0 || T <= 0 || Hq <= 0 || Hkv <= 0) return 0;
+    return attn_decode_ws_bytes(B, T, Hq, Hkv);
+}
+
+int32_t plz_attn_decode(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, int64_t batch_stride, int64_t tok_stride,
+                        int32_t B, int32_t T, int32_t Hq, int32_t Hkv, int32_t head_dim, float scale, void* out, int64_t ldo, void* ws,
+                        int64_t ws_bytes, void* stream) {
+    if (B < 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || head_dim != 128) {
+        set_last_error("attn_decode: needs T > 0, head_dim 128 and Hq a multiple of Hkv (B=%d T=%d Hq=%d Hkv=%d d=%d)", B, T, Hq, Hkv, head_dim);
+        return PLZ_ERR_BAD_SHAPE;
+    }
+    if (B == 0) return PLZ_OK;
+    if (!q || !k_cache || !v_cache || !out) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || (ldq & 7) || (batch_stride & 7) || (tok_stride & 7) ||
+        ((uintptr_t)ws & 15)) {
+        set_last_error("attn_decode: rows must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN;
+    }
+    AttnDecodeArgs a = {};
+    a.B = B; a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.scale = scale; a.q = q; a.ldq = ldq; a.k = k_cache; a.v = v_cache;
+    a.batch_stride = batch_stride; a.tok_stride = tok_stride; a.out = out; a.ldo = ldo; a.ws = ws; a.ws_bytes = ws ? ws_bytes : 0;
+    return launch_attn_decode(a, (cudaStream_t)stream);
+}
+
+int32_t plz_embed_gather(const void* table, int64_t ldt, const int64_t* ids, int64_t n, int32_t width, int64_t vocab, void* out, int64_t ldo,
+                         int32_t* bad, void* stream) {
+    if (n < 0 || width <= 0 || (width & 7) || vocab <= 0) { set_last_error("embed_gather: width must be a positive multiple of 8"); return PLZ_ERR_BAD_SHAPE; }
+    if (n == 0) return PLZ_OK;
+    if (!table || !ids || !out) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)table & 15) || ((uintptr_t)out & 15) || (ldt & 7) || (ldo & 7)) { set_last_error("embed_gather: rows must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN; }
+    return launch_embed_gather(table, ldt, (const long long*)ids, n, width, vocab, out, ldo, bad, (cudaStream_t)stream);
+}
+
 // ---- element-wise ops of a decoder layer ----------------------------------------------------------------
 static bool rows16(const void* p, int64_t ld) { return (((uintptr_t)p & 15) == 0) && ((ld & 7) == 0); }
 

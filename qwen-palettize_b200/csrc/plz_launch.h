@@ -132,6 +132,21 @@ struct AttnArgs {
 int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 int launch_attn_bwd(const AttnArgs& a, cudaStream_t stream);
 
+// ---- attention_decode.cu ------------------------------------------------------------------------
+struct AttnDecodeArgs {
+    int B, T, Hq, Hkv;
+    float scale;
+    const void* q; long long ldq;                 // bf16 [B, Hq * 128]: the new token of every sequence
+    const void* k; const void* v;                 // bf16 caches [B, T_max, Hkv * 128]
+    long long batch_stride, tok_stride;           // elements between sequences / between positions
+    void* out; long long ldo;                     // bf16 [B, Hq * 128]
+    void* ws; long long ws_bytes;
+};
+long long attn_decode_ws_bytes(int B, int T, int Hq, int Hkv);
+int launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t stream);
+int launch_embed_gather(const void* table, long long ldt, const long long* ids, long long n, int width, long long vocab, void* out,
+                        long long ldo, int* bad, cudaStream_t stream);
+
 // ---- layer_ops.cu -------------------------------------------------------------------------------
 int launch_rmsnorm_fwd(const void* x, long long ldx, const void* g, int M, int K, float eps, void* h, long long ldh, float* rstd,
                        cudaStream_t stream);

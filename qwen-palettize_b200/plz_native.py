@@ -93,6 +93,9 @@ SIGNATURES = {
     "plz_weight_grad": [_P, _I64, _P, _I64, _I32, _I32, _I32, _P, _I64, _I64, _P],
     "plz_attn_fwd": [_P, _I64, _P, _I64, _P, _I64, _I32, _I32, _I32, _I32, _I32, _F, _P, _I64, _P, _P],
     "plz_attn_bwd": [_P, _I64, _P, _I64, _P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _I32, _I32, _F, _P, _P, _P, _P, _P],
+    "plz_attn_decode_ws_bytes": [_I32, _I32, _I32, _I32],
+    "plz_attn_decode": [_P, _I64, _P, _P, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _F, _P, _I64, _P, _I64, _P],
+    "plz_embed_gather": [_P, _I64, _P, _I64, _I32, _I64, _P, _I64, _P, _P],
     "plz_rmsnorm_fwd": [_P, _I64, _P, _I32, _I32, _F, _P, _I64, _P, _P],
     "plz_qknorm_rope_fwd": [_P, _I64, _P, _P, _P, _I64, _I32, _I32, _I32, _F, _P, _I64, _P],
     "plz_qknorm_rope_bwd": [_P, _I64, _P, _P, _P, _P, _I64, _I64, _I32, _I32, _I32, _F, _P, _I64, _P, _P],
@@ -101,7 +104,7 @@ SIGNATURES = {
     "plz_bwd_dw_hard_lora": [_WP, _P, _I64, _P, _I64, _I32, _P, _P, _P, _I32, _P, _P, _P],
     "plz_distill_loss": [_P, _I64, _P, _I64, _I32, _I32, _F, _F, _F, _P, _P, _P, _I64, _I32, _P],
 }
-_RESTYPES = {"plz_last_error": C.c_char_p, "plz_launch_count": C.c_uint64}
+_RESTYPES = {"plz_last_error": C.c_char_p, "plz_launch_count": C.c_uint64, "plz_attn_decode_ws_bytes": C.c_int64}
 
 
 def lib():

@@ -107,11 +107,15 @@ def hard_forward_smallm(w: PackedWeight, x: torch.Tensor, out: torch.Tensor | No
     return y
 
 
-def hard_forward_smallm_multi(ws, x: torch.Tensor):
-    """[x W_i^T for W_i in ws] in ONE launch (1..4 matrices sharing K and the palette grouping, M <= 16)."""
+def hard_forward_smallm_multi(ws, x: torch.Tensor, outs=None):
+    """[x W_i^T for W_i in ws] in ONE launch (1..4 matrices sharing K and the palette grouping, M <= 16). outs: optional list of
+    destinations (None entries are allocated); a destination may be a pitched view, e.g. one position of a key / value cache."""
     _mat(x, ws[0].K)
     M, n = x.shape[0], len(ws)
-    ys = [torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device) for w in ws]
+    ys = [outs[i] if outs is not None and outs[i] is not None else torch.empty(M, w.N, dtype=torch.bfloat16, device=x.device)
+          for i, w in enumerate(ws)]
+    for y, w in zip(ys, ws):
+        assert y.dtype == torch.bfloat16 and tuple(y.shape) == (M, w.N) and y.stride(1) == 1
     descs = [w.desc() for w in ws]
     wp = (C.POINTER(P.Weight) * n)(*[C.pointer(d) for d in descs])
     yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
@@ -524,6 +528,34 @@ def attention_backward(q, k, v, o, do, lse, B: int, S: int, n_heads: int, n_kv_h
     return dq, dk, dv
 
 
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, T: int, n_heads: int, n_kv_heads: int,
+                     head_dim: int = 128, scale: float | None = None) -> torch.Tensor:
+    """Attention of one new token per sequence over the first T positions of the caches. q bf16 [B, n_heads * head_dim]; caches
+    bf16 [B, T_max, n_kv_heads * head_dim] (position T - 1 holds the new token's key / value). Returns bf16 [B, n_heads * head_dim]."""
+    _mat(q, n_heads * head_dim)
+    B = q.shape[0]
+    assert k_cache.dim() == 3 and k_cache.shape == v_cache.shape and k_cache.shape[0] == B and k_cache.stride() == v_cache.stride()
+    assert k_cache.shape[2] == n_kv_heads * head_dim and k_cache.stride(2) == 1 and 0 < T <= k_cache.shape[1]
+    out = torch.empty(B, n_heads * head_dim, dtype=torch.bfloat16, device=q.device)
+    nbytes = int(P.lib().plz_attn_decode_ws_bytes(B, T, n_heads, n_kv_heads))
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    sc = float(scale) if scale is not None else head_dim ** -0.5
+    P.check(P.lib().plz_attn_decode(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
+                                    B, T, n_heads, n_kv_heads, head_dim, sc, out.data_ptr(), out.stride(0), ws.data_ptr(), nbytes,
+                                    P.stream_ptr()), "plz_attn_decode")
+    return out
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """table[ids] for a bf16 [vocab, width] table and int64 ids (any shape); returns bf16 [ids.numel(), width]."""
+    assert table.dtype == torch.bfloat16 and table.dim() == 2 and table.stride(1) == 1 and ids.dtype == torch.int64
+    flat = ids.reshape(-1).contiguous()
+    out = torch.empty(flat.numel(), table.shape[1], dtype=torch.bfloat16, device=table.device)
+    P.check(P.lib().plz_embed_gather(table.data_ptr(), table.stride(0), flat.data_ptr(), flat.numel(), table.shape[1], table.shape[0],
+                                     out.data_ptr(), out.stride(0), None, P.stream_ptr()), "plz_embed_gather")
+    return out
+
+
 def rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor | None, eps: float = 1e-6):
     """(h bf16 [M, K] = rmsnorm(x) * weight, rstd fp32 [M])."""
     M, K = x.shape
@@ -543,10 +575,14 @@ def rope_tables(S: int, head_dim: int = 128, theta: float = 1e6, device="cuda"):
 
 
 def qknorm_rope_forward(x: torch.Tensor, weight: torch.Tensor | None, cos: torch.Tensor, sin: torch.Tensor, n_heads: int, S: int,
-                        eps: float = 1e-6) -> torch.Tensor:
-    """Per-head RMSNorm (weight bf16 [128]) + rotary embedding of x bf16 [tokens, n_heads * 128] (rows may be pitched)."""
+                        eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-head RMSNorm (weight bf16 [128]) + rotary embedding of x bf16 [tokens, n_heads * 128] (rows may be pitched). Row i has
+    position i % S in the cos / sin tables; a decode step passes S = 1 and the table rows of its position. out may be a pitched
+    view (one position of a key cache)."""
     _mat(x, n_heads * 128)
-    out = torch.empty(x.shape[0], n_heads * 128, dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        out = torch.empty(x.shape[0], n_heads * 128, dtype=torch.bfloat16, device=x.device)
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (x.shape[0], n_heads * 128) and out.stride(1) == 1
     P.check(P.lib().plz_qknorm_rope_fwd(x.data_ptr(), x.stride(0), weight.data_ptr() if weight is not None else None, cos.data_ptr(),
                                         sin.data_ptr(), x.shape[0], n_heads, S, 128, float(eps), out.data_ptr(), out.stride(0), P.stream_ptr()),
             "plz_qknorm_rope_fwd")
