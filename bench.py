@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
-    python bench.py --case fwd|dx|dw|dwscatter|smallm|smallm8|select|gateup|layer8 [--M 4096]   one kernel, a few launches (ncu captures)
+    python bench.py --case fwd|dx|dw|dwscatter|smallm|smallm8|select|gateup|layer8|decode1|decode8|decode64|prefill [--M 4096]   one kernel, a few launches (ncu captures)
     python bench.py --kernels [--iters 200]                                              per-kernel table, one JSON line each
 
 One step = soft forward (straight-through) + full backward of ONE palettized Linear with LoRA at the
@@ -790,6 +790,30 @@ def run_case(a):
         run, _ = layer_decode_runner(torch, ops, plz_native, dev, M, 10)
         for i in range(max(a.iters, 1) * 10):
             run(i)
+        torch.cuda.synchronize()
+        print("status", plz_native.device_status())
+        return
+    if a.case in ("decode1", "decode8", "decode64", "prefill"):
+        # two full-size layers of the 36-layer model (vocab cut to 32768 rows) so that a capture stays small: one decode step at
+        # batch 1 / 8 / 64 against a 2048-token cache, or a prefill of 2 x 1024 tokens
+        import decode_model as DM
+        mcfg = DM.ModelConfig(n_layers=2, vocab=32768)
+        model = DM.PalettizedQwen.random(mcfg, dev, seed=4, max_positions=2304)
+        gm = torch.Generator(device=dev).manual_seed(5)
+        if a.case == "prefill":
+            ids = torch.randint(0, mcfg.vocab, (2, 1024), generator=gm, device=dev)
+            cache = model.new_cache(2, 1024)
+            for _ in range(max(a.iters, 1)):
+                cache.length = 0
+                model.prefill(ids, cache)
+        else:
+            Bd = int(a.case[6:])
+            cache = model.new_cache(Bd, 2049)
+            cache.k.normal_(generator=gm)
+            cache.v.normal_(generator=gm)
+            ids = torch.randint(0, mcfg.vocab, (Bd,), generator=gm, device=dev)
+            for _ in range(max(a.iters, 1)):
+                model.decode_logits(ids, cache, 2048)
         torch.cuda.synchronize()
         print("status", plz_native.device_status())
         return

@@ -381,6 +381,13 @@ int32_t plz_embed_gather(const void* table, int64_t ldt, const int64_t* ids, int
  * plz_bwd_dw_hard_lora: plz_bwd_dw_hard plus the LoRA factor gradients in the same launch (as plz_bwd_dw_soft_lora). */
 int32_t plz_rmsnorm_fwd(const void* x, int64_t ldx, const void* g, int32_t M, int32_t K, float eps, void* h, int64_t ldh, float* rstd,
                         void* stream);
+/* sum_out = bf16(x + addend) and h = rmsnorm(sum_out) * g in one pass: a residual add and the norm that follows it. */
+int32_t plz_add_rmsnorm_fwd(const void* x, int64_t ldx, const void* addend, int64_t lda, void* sum_out, int64_t lds, const void* g, int32_t M,
+                            int32_t K, float eps, void* h, int64_t ldh, float* rstd, void* stream);
+/* plz_qknorm_rope_fwd for the q and the k projection of the same tokens in one launch. */
+int32_t plz_qknorm_rope_fwd2(const void* xq, int64_t ldxq, const void* wq, int32_t Hq, void* outq, int64_t ldoq, const void* xk, int64_t ldxk,
+                             const void* wk, int32_t Hk, void* outk, int64_t ldok, const float* cos_tab, const float* sin_tab, int64_t tokens,
+                             int32_t S, int32_t head_dim, float eps, void* stream);
 int32_t plz_qknorm_rope_fwd(const void* x, int64_t ldx, const void* w, const float* cos_tab, const float* sin_tab, int64_t tokens,
                             int32_t H, int32_t S, int32_t head_dim, float eps, void* out, int64_t ldo, void* stream);
 int32_t plz_qknorm_rope_bwd(const void* x, int64_t ldx, const void* w, const float* cos_tab, const float* sin_tab, const void* dy,

@@ -861,6 +861,30 @@ int32_t plz_rmsnorm_fwd(const void* x, int64_t ldx, const void* g, int32_t M, in
     return launch_rmsnorm_fwd(x, ldx, g, M, K, eps, h, ldh, rstd, (cudaStream_t)stream);
 }
 
+int32_t plz_add_rmsnorm_fwd(const void* x, int64_t ldx, const void* addend, int64_t lda, void* sum_out, int64_t lds, const void* g, int32_t M,
+                            int32_t K, float eps, void* h, int64_t ldh, float* rstd, void* stream) {
+    if (M < 0 || K <= 0 || (K & 7)) { set_last_error("add_rmsnorm_fwd: K must be a positive multiple of 8"); return PLZ_ERR_BAD_SHAPE; }
+    if (M == 0) return PLZ_OK;
+    if (!x || !addend || !sum_out || !h) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (!rows16(x, ldx) || !rows16(addend, lda) || !rows16(sum_out, lds) || !rows16(h, ldh) || (g && ((uintptr_t)g & 15))) {
+        set_last_error("add_rmsnorm_fwd: rows must be 16-byte aligned"); return PLZ_ERR_BAD_ALIGN;
+    }
+    return launch_add_rmsnorm(x, ldx, addend, lda, sum_out, lds, g, M, K, eps, h, ldh, rstd, (cudaStream_t)stream);
+}
+
+int32_t plz_qknorm_rope_fwd2(const void* xq, int64_t ldxq, const void* wq, int32_t Hq, void* outq, int64_t ldoq, const void* xk, int64_t ldxk,
+                             const void* wk, int32_t Hk, void* outk, int64_t ldok, const float* cos_tab, const float* sin_tab, int64_t tokens,
+                             int32_t S, int32_t head_dim, float eps, void* stream) {
+    if (tokens < 0 || Hq <= 0 || Hk <= 0 || S <= 0 || head_dim != 128) { set_last_error("qknorm_rope: head_dim must be 128 (Hq=%d Hk=%d S=%d)", Hq, Hk, S); return PLZ_ERR_BAD_SHAPE; }
+    if (tokens == 0) return PLZ_OK;
+    if (!xq || !xk || !outq || !outk || !cos_tab || !sin_tab) { set_last_error("null pointer"); return PLZ_ERR_NULL; }
+    if (((uintptr_t)xq & 3) || ((uintptr_t)xk & 3) || ((uintptr_t)outq & 3) || ((uintptr_t)outk & 3) || (ldxq & 1) || (ldxk & 1) || (ldoq & 1) ||
+        (ldok & 1) || ((uintptr_t)cos_tab & 7) || ((uintptr_t)sin_tab & 7)) {
+        set_last_error("qknorm_rope: misaligned input"); return PLZ_ERR_BAD_ALIGN;
+    }
+    return launch_qknorm_rope2(xq, ldxq, wq, Hq, outq, ldoq, xk, ldxk, wk, Hk, outk, ldok, cos_tab, sin_tab, tokens, S, eps, (cudaStream_t)stream);
+}
+
 int32_t plz_qknorm_rope_fwd(const void* x, int64_t ldx, const void* w, const float* cos_tab, const float* sin_tab, int64_t tokens,
                             int32_t H, int32_t S, int32_t head_dim, float eps, void* out, int64_t ldo, void* stream) {
     if (tokens < 0 || H <= 0 || S <= 0 || head_dim != 128) { set_last_error("qknorm_rope: head_dim must be 128 (H=%d S=%d)", H, S); return PLZ_ERR_BAD_SHAPE; }

@@ -50,6 +50,8 @@ attn_decode_partial_kernel(const DecParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tl = lane >> 4, dl = lane & 15;
     const int t0 = split * p.chunk, t1 = min(p.T, t0 + p.chunk);
     const int head0 = hk * p.group + p.g0;          // first q head of this launch's part of the group
+    pdl_launch_dependents();
+    pdl_wait();
 
     float q[4][8];
 #pragma unroll
@@ -177,20 +179,39 @@ attn_decode_partial_kernel(const DecParams p) {
     }
 }
 
+// Merge of the splits: one block per (head, sequence), thread d = dimension d. The weights exp2(m_s - M) of the splits are
+// computed once (thread s for split s, at most kMaxSplits of them) and shared; the sum over splits then has independent loads.
+constexpr int kMaxSplits = 128;
 __global__ void __launch_bounds__(128)
 attn_decode_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, int splits, int Hq, __nv_bfloat16* __restrict__ out,
                            long long ldo) {
-    const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    __shared__ float wgt[kMaxSplits];
+    __shared__ float red[8];
+    const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x, lane = d & 31, wib = d >> 5;
     const long long slot0 = ((long long)b * Hq + head) * splits;
-    float M = kNegBig;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, ws_ml[(slot0 + s) * 2]);
-    float acc = 0.f, l = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float c = ex2(ws_ml[(slot0 + s) * 2] - M);
-        acc = fmaf(c, ws_o[(slot0 + s) * 128 + d], acc);
-        l = fmaf(c, ws_ml[(slot0 + s) * 2 + 1], l);
-    }
-    out[(long long)b * ldo + (long long)head * 128 + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    pdl_launch_dependents();
+    pdl_wait();
+    const float m = d < splits ? ws_ml[(slot0 + d) * 2] : kNegBig;
+    const float l = d < splits ? ws_ml[(slot0 + d) * 2 + 1] : 0.f;
+    float M = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+    if (lane == 0) red[wib] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const float c = ex2(m - M);
+    wgt[d] = c;
+    float ls = c * l;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ls += __shfl_xor_sync(0xFFFFFFFFu, ls, o);
+    if (lane == 0) red[4 + wib] = ls;
+    __syncthreads();
+    const float L = red[4] + red[5] + red[6] + red[7];
+    float acc = 0.f;
+    const float* src = ws_o + slot0 * 128 + d;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) acc = fmaf(wgt[s], __ldcs(src + (long long)s * 128), acc);
+    out[(long long)b * ldo + (long long)head * 128 + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
 }
 
 // out[i, :] = table[ids[i], :] (bf16 rows of `width`, width % 8 == 0); an id outside [0, vocab) gives a zero row and sets *bad
@@ -219,10 +240,11 @@ int sm_count_now() {
 
 // tokens per split (a multiple of the CTA step) and the number of splits for a launch of B * Hkv groups over T tokens
 void decode_split(int B, int Hkv, int T, int* chunk, int* splits) {
-    const int want_ctas = 4 * sm_count_now();
+    const int want_ctas = 2 * sm_count_now();
     int s = (want_ctas + B * Hkv - 1) / (B * Hkv);
     const int max_s = (T + kCtaStep - 1) / kCtaStep;
     if (s > max_s) s = max_s;
+    if (s > kMaxSplits) s = kMaxSplits;
     if (s < 1) s = 1;
     int c = (T + s - 1) / s;
     c = ((c + kCtaStep - 1) / kCtaStep) * kCtaStep;
@@ -253,12 +275,11 @@ int launch_attn_decode(const AttnDecodeArgs& a, cudaStream_t stream) {
     p.scale_log2e = a.scale * kLog2eDec;
     for (int g0 = 0; g0 < p.group; g0 += 4) {   // groups of more than four q heads: four at a time
         p.g0 = g0; p.G = p.group - g0 < 4 ? p.group - g0 : 4;
-        attn_decode_partial_kernel<<<dim3(p.splits, a.Hkv, a.B), kDecWarps * 32, 0, stream>>>(p);
-        PLZ_LAUNCH_CHECK();
+        PLZ_LAUNCH_CHAIN(attn_decode_partial_kernel, dim3(p.splits, a.Hkv, a.B), dim3(kDecWarps * 32), 0, stream, p);
     }
     if (p.splits > 1) {
-        attn_decode_combine_kernel<<<dim3(a.Hq, a.B), 128, 0, stream>>>(p.ws_o, p.ws_ml, p.splits, a.Hq, p.out, p.ldo);
-        PLZ_LAUNCH_CHECK();
+        PLZ_LAUNCH_CHAIN(attn_decode_combine_kernel, dim3(a.Hq, a.B), dim3(128), 0, stream, (const float*)p.ws_o, (const float*)p.ws_ml, p.splits,
+                         a.Hq, p.out, p.ldo);
     }
     return PLZ_OK;
 }

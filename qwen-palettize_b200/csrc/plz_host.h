@@ -53,4 +53,26 @@ extern unsigned long long g_launch_count;
         ++plz::g_launch_count;                   \
     } while (0)
 
+// Launch of a small kernel of the token-decode chain. When plz_set_smallm_overlap is on, the launch carries the
+// programmatic-stream-serialization attribute: the kernel may start while its predecessor in the stream is still running,
+// so it must execute griddepcontrol.wait before it touches anything another kernel writes (pdl_wait below; a no-op
+// without the attribute), and its griddepcontrol.launch_dependents lets the kernel after it (typically a small-M LUT
+// kernel, which first streams its read-only weights) start early in turn.
+extern int g_smallm_overlap;
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = g_smallm_overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#define PLZ_LAUNCH_CHAIN(...)                        \
+    do {                                             \
+        PLZ_CUDA_CHECK(plz::launch_chain(__VA_ARGS__)); \
+        ++plz::g_launch_count;                       \
+    } while (0)
+
 }  // namespace plz

@@ -150,6 +150,11 @@ int launch_embed_gather(const void* table, long long ldt, const long long* ids, 
 // ---- layer_ops.cu -------------------------------------------------------------------------------
 int launch_rmsnorm_fwd(const void* x, long long ldx, const void* g, int M, int K, float eps, void* h, long long ldh, float* rstd,
                        cudaStream_t stream);
+int launch_add_rmsnorm(const void* x, long long ldx, const void* addend, long long lda, void* sum_out, long long lds, const void* g, int M,
+                       int K, float eps, void* h, long long ldh, float* rstd, cudaStream_t stream);
+int launch_qknorm_rope2(const void* x1, long long ldx1, const void* w1, int H1, void* out1, long long ldo1, const void* x2, long long ldx2,
+                        const void* w2, int H2, void* out2, long long ldo2, const float* cs, const float* sn, long long tokens, int S, float eps,
+                        cudaStream_t stream);
 int launch_qknorm_rope(int backward, const void* x, long long ldx, const void* w, const float* cs, const float* sn, const void* dy,
                        long long lddy, long long tokens, int H, int S, float eps, void* out, long long ldo, float* dw, cudaStream_t stream);
 int launch_swiglu_fwd(const void* gate, long long ldg, const void* up, long long ldu, int M, int N, void* act, long long lda, cudaStream_t stream);

@@ -43,6 +43,12 @@ struct StatusWord {
     unsigned int pad;
 };
 
+// Programmatic dependent launch: let the next kernel of the stream start (it will wait for this one to finish before it
+// reads what this one writes), and wait for the previous kernel to have finished. Both are no-ops in a launch without the
+// programmatic-stream-serialization attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void report(StatusWord* st, uint32_t code, uint32_t role) {
     if (st == nullptr) return;
     atomicAdd(&st->count, 1u);

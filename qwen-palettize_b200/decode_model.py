@@ -24,6 +24,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 if _HERE not in sys.path:
     sys.path.insert(0, _HERE)
 
+import plz_native as P  # noqa: E402
 import plz_ops as ops  # noqa: E402
 from decoder_layer import LINEARS, LayerConfig  # noqa: E402
 
@@ -80,7 +81,21 @@ class PalettizedQwen:
     def logits(self, h: torch.Tensor) -> torch.Tensor:
         """Final RMSNorm and the tied-embedding head: bf16 [rows, vocab]."""
         hn, _ = ops.rmsnorm_forward(h, self.final_norm, self.cfg.eps)
+        return self.head(hn)
+
+    def head(self, hn: torch.Tensor) -> torch.Tensor:
+        """Logits bf16 [rows, vocab] of already normalised hidden states (tied embedding table)."""
         return ops.dense_forward(self.embed, hn)[0]
+
+    def decode_logits(self, ids: torch.Tensor, cache: KVCache, pos: int | None = None) -> torch.Tensor:
+        """One decode step up to the logits, with the small kernels of the chain allowed to start under their predecessors
+        (programmatic dependent launch; the weights are read-only here). Does not advance cache.length."""
+        lib = P.lib()
+        lib.plz_set_smallm_overlap(1)
+        try:
+            return self.head(self.decode_hidden(ids, cache, pos)[1])
+        finally:
+            lib.plz_set_smallm_overlap(0)
 
     # ---- prefill -------------------------------------------------------------------------------------------------
     def prefill(self, ids: torch.Tensor, cache: KVCache, want_logits: bool = True):
@@ -115,30 +130,32 @@ class PalettizedQwen:
             return ops.hard_forward_smallm_multi(ws, x, outs)
         return [ops.hard_forward_smallm(w, x, out=(outs[i] if outs is not None else None)) for i, w in enumerate(ws)]
 
-    def decode_hidden(self, ids: torch.Tensor, cache: KVCache, pos: int | None = None) -> torch.Tensor:
+    def decode_hidden(self, ids: torch.Tensor, cache: KVCache, pos: int | None = None):
         """One token per sequence (ids int64 [B]) at position pos (default: cache.length): writes its key / value into the cache
-        and returns the final hidden state bf16 [B, hidden]. Does not advance cache.length."""
+        and returns (final hidden state, its final RMSNorm), bf16 [B, hidden] each. Does not advance cache.length."""
         c = self.cfg
         B = ids.shape[0]
         pos = cache.length if pos is None else pos
         assert pos < cache.k.shape[2] and pos < self.cos.shape[0]
         cos, sin = self.cos[pos:pos + 1], self.sin[pos:pos + 1]
         h = ops.embed_gather(self.embed, ids)
+        h1, _ = ops.rmsnorm_forward(h, self.layers[0]["input_ln"], c.eps)
+        n = len(self.layers)
         for li, L in enumerate(self.layers):
-            h1, _ = ops.rmsnorm_forward(h, L["input_ln"], c.eps)
             q_raw, k_raw, _ = self._small([L["q"], L["k"], L["v"]], h1, [None, None, cache.v[li, :, pos]])
-            q = ops.qknorm_rope_forward(q_raw, L["q_norm"], cos, sin, c.n_heads, 1, c.eps)
-            ops.qknorm_rope_forward(k_raw, L["k_norm"], cos, sin, c.n_kv_heads, 1, c.eps, out=cache.k[li, :, pos])
+            q, _ = ops.qknorm_rope_forward2(q_raw, L["q_norm"], c.n_heads, k_raw, L["k_norm"], c.n_kv_heads, cos, sin, 1, c.eps,
+                                            out_k=cache.k[li, :, pos])
             a = ops.attention_decode(q, cache.k[li], cache.v[li], pos + 1, c.n_heads, c.n_kv_heads, c.head_dim)
-            x2 = ops.add(h, self._small([L["o"]], a)[0])
-            h2, _ = ops.rmsnorm_forward(x2, L["post_ln"], c.eps)
+            x2, h2 = ops.add_rmsnorm_forward(h, self._small([L["o"]], a)[0], L["post_ln"], c.eps)
             gate, up = self._small([L["gate"], L["up"]], h2)
-            h = ops.add(x2, self._small([L["down"]], ops.swiglu_forward(gate, up))[0])
-        return h
+            d = self._small([L["down"]], ops.swiglu_forward(gate, up))[0]
+            # the residual add closes the layer and the same pass applies the next layer's (or the final) norm
+            h, h1 = ops.add_rmsnorm_forward(x2, d, self.layers[li + 1]["input_ln"] if li + 1 < n else self.final_norm, c.eps)
+        return h, h1
 
     def decode_step(self, ids: torch.Tensor, cache: KVCache) -> torch.Tensor:
         """Logits bf16 [B, vocab] of the next token after ids (int64 [B]); advances the cache by one position."""
-        out = self.logits(self.decode_hidden(ids, cache))
+        out = self.decode_logits(ids, cache)
         cache.length += 1
         return out
 
@@ -148,9 +165,9 @@ class PalettizedQwen:
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
-            self.logits(self.decode_hidden(ids, cache, pos))      # warm-up outside the capture (lazy module state, allocator)
+            self.decode_logits(ids, cache, pos)      # warm-up outside the capture (lazy module state, allocator)
         torch.cuda.current_stream().wait_stream(s)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            out = self.logits(self.decode_hidden(ids, cache, pos))
+            out = self.decode_logits(ids, cache, pos)
         return g, out

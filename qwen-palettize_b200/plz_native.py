@@ -97,6 +97,8 @@ SIGNATURES = {
     "plz_attn_decode": [_P, _I64, _P, _P, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _F, _P, _I64, _P, _I64, _P],
     "plz_embed_gather": [_P, _I64, _P, _I64, _I32, _I64, _P, _I64, _P, _P],
     "plz_rmsnorm_fwd": [_P, _I64, _P, _I32, _I32, _F, _P, _I64, _P, _P],
+    "plz_add_rmsnorm_fwd": [_P, _I64, _P, _I64, _P, _I64, _P, _I32, _I32, _F, _P, _I64, _P, _P],
+    "plz_qknorm_rope_fwd2": [_P, _I64, _P, _I32, _P, _I64, _P, _I64, _P, _I32, _P, _I64, _P, _P, _I64, _I32, _I32, _F, _P],
     "plz_qknorm_rope_fwd": [_P, _I64, _P, _P, _P, _I64, _I32, _I32, _I32, _F, _P, _I64, _P],
     "plz_qknorm_rope_bwd": [_P, _I64, _P, _P, _P, _P, _I64, _I64, _I32, _I32, _I32, _F, _P, _I64, _P, _P],
     "plz_swiglu_fwd": [_P, _I64, _P, _I64, _I32, _I32, _P, _I64, _P],

@@ -567,6 +567,34 @@ def rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor | None, eps: float = 1
     return h, rstd
 
 
+def add_rmsnorm_forward(x: torch.Tensor, addend: torch.Tensor, weight: torch.Tensor | None, eps: float = 1e-6):
+    """(s = x + addend, h = rmsnorm(s) * weight), both bf16 [M, K], in one pass."""
+    M, K = x.shape
+    _mat(x, K), _mat(addend, K)
+    s = torch.empty(M, K, dtype=torch.bfloat16, device=x.device)
+    h = torch.empty(M, K, dtype=torch.bfloat16, device=x.device)
+    P.check(P.lib().plz_add_rmsnorm_fwd(x.data_ptr(), x.stride(0), addend.data_ptr(), addend.stride(0), s.data_ptr(), s.stride(0),
+                                        weight.data_ptr() if weight is not None else None, M, K, float(eps), h.data_ptr(), h.stride(0), None,
+                                        P.stream_ptr()), "plz_add_rmsnorm_fwd")
+    return s, h
+
+
+def qknorm_rope_forward2(xq, wq, n_heads: int, xk, wk, n_kv_heads: int, cos, sin, S: int, eps: float = 1e-6, out_q=None, out_k=None):
+    """qknorm_rope_forward of the q and the k projection of the same tokens in one launch: (q, k)."""
+    _mat(xq, n_heads * 128), _mat(xk, n_kv_heads * 128)
+    T = xq.shape[0]
+    assert xk.shape[0] == T
+    oq = out_q if out_q is not None else torch.empty(T, n_heads * 128, dtype=torch.bfloat16, device=xq.device)
+    ok = out_k if out_k is not None else torch.empty(T, n_kv_heads * 128, dtype=torch.bfloat16, device=xq.device)
+    for o, h in ((oq, n_heads), (ok, n_kv_heads)):
+        assert o.dtype == torch.bfloat16 and tuple(o.shape) == (T, h * 128) and o.stride(1) == 1
+    P.check(P.lib().plz_qknorm_rope_fwd2(xq.data_ptr(), xq.stride(0), wq.data_ptr() if wq is not None else None, n_heads, oq.data_ptr(), oq.stride(0),
+                                         xk.data_ptr(), xk.stride(0), wk.data_ptr() if wk is not None else None, n_kv_heads, ok.data_ptr(),
+                                         ok.stride(0), cos.data_ptr(), sin.data_ptr(), T, S, 128, float(eps), P.stream_ptr()),
+            "plz_qknorm_rope_fwd2")
+    return oq, ok
+
+
 def rope_tables(S: int, head_dim: int = 128, theta: float = 1e6, device="cuda"):
     """(cos, sin) fp32 [S, head_dim / 2] of transformers' default rotary embedding: angle = position * theta^(-2i / head_dim)."""
     inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))

@@ -100,7 +100,7 @@ def test_decode_graph_replays_the_eager_step():
     cache = model.new_cache(B, S + 1)
     model.prefill(ids[:, :S], cache, want_logits=False)
     step_ids = ids[:, S].contiguous()
-    eager = model.logits(model.decode_hidden(step_ids, cache, S))
+    eager = model.decode_logits(step_ids, cache, S)
     graph, out = model.decode_graph(step_ids, cache, S)
     out.zero_()
     graph.replay()
