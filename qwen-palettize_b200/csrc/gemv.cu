@@ -338,11 +338,10 @@ lut_gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int M, 
                 if (k < K) {
                     const int kg = (gs_k_shift >= 0) ? (k >> gs_k_shift) : (k / gs_k);
                     const uint2 praw = __ldg(reinterpret_cast<const uint2*>(pal_row + kg * 4));
-                    const PalRegs pal = pal_split(praw.x, praw.y);
-                    uint32_t s = (b | (b << 4)) & 0x0F0Fu;
-                    s = (s | (s << 2)) & 0x3333u;  // nibble i = index of weight k + i
-                    const uint32_t L = __byte_perm(pal.lo, 0u, s), H = __byte_perm(pal.hi, 0u, s);
-                    const uint32_t w01 = __byte_perm(L, H, 0x5140), w23 = __byte_perm(L, H, 0x7362);
+                    // index of weight k + e into byte e, then the selector bytes 0x22 * i + 0x10 (palette bytes 2i, 2i + 1)
+                    const uint32_t v = (b & 0x3u) | ((b & 0xCu) << 6) | ((b & 0x30u) << 12) | ((b & 0xC0u) << 18);
+                    const uint32_t s = v * 0x22u + 0x10101010u;
+                    const uint32_t w01 = prmt_raw(praw.x, praw.y, s), w23 = prmt_raw(praw.x, praw.y, s >> 16);
                     const float w0 = __uint_as_float(w01 << 16), w1 = __uint_as_float(w01 & 0xFFFF0000u);
                     const float w2 = __uint_as_float(w23 << 16), w3 = __uint_as_float(w23 & 0xFFFF0000u);
 #pragma unroll
