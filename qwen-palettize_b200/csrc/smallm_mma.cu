@@ -13,9 +13,11 @@
 //   * a work item is 16 rows x 256 input columns (one palette group per row); the items are dealt round-robin to the
 //     16 warps.  Weights go from shared memory straight into mma.sync.m16n8k16 A fragments (the 128-row tcgen05 tile
 //     would be 7/8 padding here): the reduction dimension may be permuted freely as long as x is permuted alike, so
-//     lane (g, t) simply takes the 16 bytes at columns 64 t.. of rows g and g + 8 of the group: byte j of them holds
-//     its four weights of k-step j.  Four weights -> four bf16 values is two byte permutes of the row's palette with
-//     selectors computed arithmetically for a whole 32-bit word (16 weights) at a time (selectors16);
+//     lane (g, t) simply takes the 16 bytes at columns 64 t.. of rows g and g + 8 of the group; k-step 4 w + e uses bit
+//     pair e of each of the four bytes of word w (the weights 16 w + e, + 4, + 8, + 12 of the lane's 64 columns).  One mask
+//     and one multiply-add turn those four indices into four selector bytes (0x22 i + 0x10 = palette bytes 2i, 2i + 1),
+//     and a byte permute of the row's palette per selector half gives two bf16 weights: 19 ALU instructions and 4
+//     multiply-adds per 16 weights;
 //   * x sits in shared memory in the matching order, 8 bytes per (k-step, lane quad), so that a B fragment is one
 //     conflict-free 8-byte load;
 //   * partial sums of an item are added to the CTA's fp32 output tile in shared memory (red.shared; the order in which
@@ -69,19 +71,6 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Byte-permute selectors for the 16 weights of one 32-bit word of packed indices (weight 4j + e = bits 2e.. of byte j).
-// A weight with index i is the two palette bytes 2i, 2i + 1 of {P01, P23}: selector byte 0x22 * i + 0x10.
-// lo[h] / hi[h]: selectors of k-steps 2h (low half-word) and 2h + 1 (high half-word), for the weight pairs (4j, 4j + 1)
-// and (4j + 2, 4j + 3) respectively.
-__device__ __forceinline__ void selectors16(uint32_t w, uint32_t (&lo)[2], uint32_t (&hi)[2]) {
-    const uint32_t sa = (w & 0x03030303u) * 0x22u + 0x10101010u;
-    const uint32_t sb = ((w >> 2) & 0x03030303u) * 0x22u + 0x10101010u;
-    const uint32_t sc = ((w >> 4) & 0x03030303u) * 0x22u + 0x10101010u;
-    const uint32_t sd = ((w >> 6) & 0x03030303u) * 0x22u + 0x10101010u;
-    lo[0] = __byte_perm(sa, sb, 0x5140); lo[1] = __byte_perm(sa, sb, 0x7362);
-    hi[0] = __byte_perm(sc, sd, 0x5140); hi[1] = __byte_perm(sc, sd, 0x7362);
-}
-
 __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  :: "r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
@@ -124,9 +113,10 @@ lut_smallm_mma_kernel(const SmallmParams p) {
             int r = a;
             while (r < b) {
                 const int mi = mat_of(p, r0 + r), lr = r0 + r - p.row_start[mi];
+                const long long pitch = p.pitch[mi];
                 int n = 1;  // rows of this piece
-                if (p.pitch[mi] == (long long)row_bytes) n = min(b - r, p.row_start[mi + 1] - (r0 + r));
-                bulk_load(smem_u32(wsm) + (uint32_t)r * row_bytes, p.packed[mi] + (long long)lr * p.pitch[mi], (uint32_t)n * row_bytes,
+                if (pitch == (long long)row_bytes) n = min(b - r, p.row_start[mi + 1] - (r0 + r));
+                bulk_load(smem_u32(wsm) + (uint32_t)r * row_bytes, p.packed[mi] + (long long)lr * pitch, (uint32_t)n * row_bytes,
                           bar0 + 8u * s);
                 r += n;
             }
@@ -168,15 +158,16 @@ lut_smallm_mma_kernel(const SmallmParams p) {
     const long long t_a = PLZ_PROF_ON(p.prof) ? clock64() : 0;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     {
-        // x in the permuted order of the fragments: 16 bytes = 8 consecutive k of one token = the 8-byte units of k-steps
-        // j and j + 1 of lane quad tq; up to eight loads (one per row) per thread in flight together. Only the M real rows are staged:
-        // a column n >= M of an mma only ever reaches the same column of D, which is never written out, so the lanes of
-        // those columns simply read row 0
+        // x in the permuted order of the fragments. A 16-byte chunk = 8 consecutive k of one token = bytes 2 hh, 2 hh + 1 of word
+        // wi of lane quad tq, all four bit pairs e: its elements (byte c, pair e) go to k-step 4 wi + e, slot c of the quad's
+        // 8-byte unit. Up to eight loads (one per row) per thread in flight together. Only the M real rows are staged: a
+        // column n >= M of an mma only ever reaches the same column of D, which is never written out, so the lanes of those
+        // columns simply read row 0
         const int chunks_per_row = p.K >> 3;
         for (int c = threadIdx.x; c < chunks_per_row; c += kThreads) {
             const int k = c << 3;
-            const int kg = k >> 8, r = k & 255, tq = r >> 6, j = (r & 63) >> 2;
-            uint8_t* dst = xs + (size_t)(((kg * 16 + j) * 4 + tq) * 8);
+            const int kg = k >> 8, r = k & 255, tq = r >> 6, wi = (r & 63) >> 4, hh = (r >> 3) & 1;
+            uint8_t* dst = xs + (size_t)(((kg * 16 + wi * 4) * 4 + tq) * 8 + hh * 4);
             const __nv_bfloat16* src = p.x + k;
 #pragma unroll
             for (int m0 = 0; m0 < 8 * MT; m0 += 8) {
@@ -188,8 +179,11 @@ lut_smallm_mma_kernel(const SmallmParams p) {
                 for (int u = 0; u < 8; ++u) {
                     if (m0 + u < p.M) {
                         uint8_t* d = dst + (size_t)(m0 + u) * p.x_pitch;
-                        *reinterpret_cast<uint2*>(d) = make_uint2(v[u].x, v[u].y);
-                        *reinterpret_cast<uint2*>(d + 32) = make_uint2(v[u].z, v[u].w);  // k-step j + 1, same quad
+                        // v.x = (byte 2hh: pairs 0, 1), v.y = (byte 2hh: pairs 2, 3), v.z / v.w the same of byte 2hh + 1
+                        *reinterpret_cast<uint32_t*>(d) = prmt_raw(v[u].x, v[u].z, 0x5410u);        // pair 0 of both bytes
+                        *reinterpret_cast<uint32_t*>(d + 32) = prmt_raw(v[u].x, v[u].z, 0x7632u);   // pair 1 (next k-step, same quad)
+                        *reinterpret_cast<uint32_t*>(d + 64) = prmt_raw(v[u].y, v[u].w, 0x5410u);
+                        *reinterpret_cast<uint32_t*>(d + 96) = prmt_raw(v[u].y, v[u].w, 0x7632u);
                     }
                 }
             }
@@ -223,11 +217,11 @@ lut_smallm_mma_kernel(const SmallmParams p) {
                 if (!ok) break;
             }
             // two accumulators per m-tile (even / odd k-steps) so that consecutive mma do not wait on each other
-            float d[MT][4], e[MT][4];
+            float d[MT][4], e_acc[MT][4];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 d[mt][0] = d[mt][1] = d[mt][2] = d[mt][3] = 0.f;
-                e[mt][0] = e[mt][1] = e[mt][2] = e[mt][3] = 0.f;
+                e_acc[mt][0] = e_acc[mt][1] = e_acc[mt][2] = e_acc[mt][3] = 0.f;
             }
             uint32_t wra[4], wrb[4];
             const uint32_t wadr = w_base + (uint32_t)(s * 16) * row_bytes + (uint32_t)kg * 64u;
@@ -236,26 +230,21 @@ lut_smallm_mma_kernel(const SmallmParams p) {
             const uint32_t xoff = (uint32_t)kg * (16u * 4u * 8u);
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
-                uint32_t la[2], ha[2], lb[2], hb[2];
-                selectors16(wra[wi], la, ha);
-                selectors16(wrb[wi], lb, hb);
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    const int j = wi * 4 + jj;
-                    const uint32_t s_la = (jj & 1) ? (la[jj >> 1] >> 16) : la[jj >> 1];
-                    const uint32_t s_ha = (jj & 1) ? (ha[jj >> 1] >> 16) : ha[jj >> 1];
-                    const uint32_t s_lb = (jj & 1) ? (lb[jj >> 1] >> 16) : lb[jj >> 1];
-                    const uint32_t s_hb = (jj & 1) ? (hb[jj >> 1] >> 16) : hb[jj >> 1];
+                for (int e = 0; e < 4; ++e) {
+                    const int j = wi * 4 + e;
+                    const uint32_t sa = ((wra[wi] >> (2 * e)) & 0x03030303u) * 0x22u + 0x10101010u;
+                    const uint32_t sb = ((wrb[wi] >> (2 * e)) & 0x03030303u) * 0x22u + 0x10101010u;
                     uint32_t a[4];
-                    a[0] = __byte_perm(pa[q].x, pa[q].y, s_la);
-                    a[1] = __byte_perm(pb[q].x, pb[q].y, s_lb);
-                    a[2] = __byte_perm(pa[q].x, pa[q].y, s_ha);
-                    a[3] = __byte_perm(pb[q].x, pb[q].y, s_hb);
+                    a[0] = prmt_raw(pa[q].x, pa[q].y, sa);
+                    a[1] = prmt_raw(pb[q].x, pb[q].y, sb);
+                    a[2] = prmt_raw(pa[q].x, pa[q].y, sa >> 16);
+                    a[3] = prmt_raw(pb[q].x, pb[q].y, sb >> 16);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         uint32_t b0, b1;
                         asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(xs_base[mt] + xoff + (uint32_t)j * 32u));
-                        if (j & 1) mma_bf16_16816(e[mt], a, b0, b1);
+                        if (j & 1) mma_bf16_16816(e_acc[mt], a, b0, b1);
                         else mma_bf16_16816(d[mt], a, b0, b1);
                     }
                 }
@@ -263,10 +252,10 @@ lut_smallm_mma_kernel(const SmallmParams p) {
             float* o = acc_s + (size_t)(s * 16 + g) * (8 * MT) + 2 * t;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                atomicAdd(o + mt * 8, d[mt][0] + e[mt][0]);
-                atomicAdd(o + mt * 8 + 1, d[mt][1] + e[mt][1]);
-                atomicAdd(o + 8 * (8 * MT) + mt * 8, d[mt][2] + e[mt][2]);
-                atomicAdd(o + 8 * (8 * MT) + mt * 8 + 1, d[mt][3] + e[mt][3]);
+                atomicAdd(o + mt * 8, d[mt][0] + e_acc[mt][0]);
+                atomicAdd(o + mt * 8 + 1, d[mt][1] + e_acc[mt][1]);
+                atomicAdd(o + 8 * (8 * MT) + mt * 8, d[mt][2] + e_acc[mt][2]);
+                atomicAdd(o + 8 * (8 * MT) + mt * 8 + 1, d[mt][3] + e_acc[mt][3]);
             }
         }
     }
