@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
-    python bench.py --case fwd|dx|dw|dwscatter|smallm|smallm8|select|gateup|layer8|decode1|decode8|decode64|prefill [--M 4096]   one kernel, a few launches (ncu captures)
+    python bench.py --case fwd|dx|dw|dwscatter|smallm|smallm8|select|gateup|layer8|decode1|decode8|decode64|prefill|layertrain [--M 4096]   one kernel, a few launches (ncu captures)
     python bench.py --kernels [--iters 200]                                              per-kernel table, one JSON line each
 
 One step = soft forward (straight-through) + full backward of ONE palettized Linear with LoRA at the
@@ -412,15 +412,15 @@ def run_ours(args):
     peak_val = pk["tflops_burst"] if burst_region else pk["tflops_sustained"]
     # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum): one ncu capture of each kernel at 4096
     # tokens (profiles/*.md) gave measured / algorithmic = 0.51 (fwd: most of y was still in L2 when the capture
-    # ended) and 0.87 (dx). The dW launch measured 1391.8 MB there: 1195.4 MB of logits / noise / dLogits that do not
+    # ended) and 0.90 (dx). The dW launch measured 1413.7 MB there: 1195.4 MB of logits / noise / dLogits that do not
     # depend on the token count, plus x and dY streamed twice (once for dW, once more by the dA / dB side items in
     # the last round); the figure below scales that token-proportional part to the full 16384-token launch.
     alg = {"fwd": M_TOK * K_IN * 2 + N_OUT * K_IN // 4 + N_OUT * (K_IN // 256) * 8 + M_TOK * N_OUT * 2,
            "dx": M_TOK * N_OUT * 2 + N_OUT * K_IN // 4 + N_OUT * (K_IN // 256) * 8 + M_TOK * K_IN * 2,
            "dw": 3 * N_OUT * K_IN * 16 + M_TOK * (N_OUT + K_IN) * 2}
     xdy_small = 4096 * (N_OUT + K_IN) * 2
-    traffic = {"fwd": 0.51 * alg["fwd"], "dx": 0.87 * alg["dx"],
-               "dw": (1391.8e6 - 2 * xdy_small) + 2 * M_TOK * (N_OUT + K_IN) * 2}
+    traffic = {"fwd": 0.51 * alg["fwd"], "dx": 0.90 * alg["dx"],
+               "dw": (1413.7e6 - 2 * xdy_small) + 2 * M_TOK * (N_OUT + K_IN) * 2}
     traffic_src = {"fwd": "profiles/lut_gemm_forward_M4096_N9728_K2560.md", "dx": "profiles/lut_gemm_dx_M4096_N9728_K2560.md",
                    "dw": "profiles/tn_gemm_soft_gradient_M4096_N9728_K2560.md"}
     line = {
@@ -790,6 +790,21 @@ def run_case(a):
         run, _ = layer_decode_runner(torch, ops, plz_native, dev, M, 10)
         for i in range(max(a.iters, 1) * 10):
             run(i)
+        torch.cuda.synchronize()
+        print("status", plz_native.device_status())
+        return
+    if a.case == "layertrain":
+        # one full-size decoder layer, forward + backward, at batch 8 x seq 512 (a quarter of the config-2 batch)
+        import decoder_layer as DL
+        cfg = DL.LayerConfig()
+        P_ = DL.random_layer(cfg, dev, seed=10)
+        g = torch.Generator(device=dev).manual_seed(3)
+        Bc, Sc = 8, 512
+        xl = torch.randn(Bc * Sc, cfg.hidden, generator=g, device=dev).to(torch.bfloat16)
+        dyl = torch.randn(Bc * Sc, cfg.hidden, generator=g, device=dev).to(torch.bfloat16)
+        cos, sin = ops.rope_tables(Sc, cfg.head_dim, cfg.rope_theta, dev)
+        for _ in range(max(a.iters, 1)):
+            DL.stack_forward_backward(cfg, [P_], xl, dyl, Bc, Sc, cos, sin)
         torch.cuda.synchronize()
         print("status", plz_native.device_status())
         return
