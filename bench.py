@@ -187,10 +187,20 @@ def run_ours(args):
         # whatever part of the exchange the dX product did not hide
         phases = phases[:4] + (["exch_sync", "exch_reduce"] if scatter is not None else []) + ["dx", "exch_wait"]
     ev = {p: [] for p in phases}
+    # deferred exchange (fused slot mode): the whole exchange of a step runs on the side stream and is waited for only
+    # right before the next step's weight-gradient kernel reuses the staging slots (and once more after the last step)
+    deferred = bool(args.defer_exchange) and scatter is not None and scatter.mode == "slots" and split_rows == 0
+    pending = [None]
+
+    def drain():
+        if deferred and pending[0] is not None:
+            scatter.finish(pending[0])
+            pending[0] = None
 
     def step(record):
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(7)] if record else None
         xm = [torch.cuda.Event(enable_timing=True) for _ in range(2)] if record else None
+        dmark = torch.cuda.Event(enable_timing=True) if record else None
         if record: marks[0].record()
         ops.soft_select(w, logits, "nk4", noise=noise, tau=TAU, want_packed=True)
         if record: marks[1].record()
@@ -201,9 +211,18 @@ def run_ours(args):
         if scatter is not None:
             # dLogits partials go straight from the epilogue into the owner ranks' staging buffers (reduce-scatter fused
             # into the kernel); small all-reduce + slot reduction + all-gather then run beside the dX product
+            if deferred and pending[0] is not None:
+                # the previous step's exchange must be over on every rank before its staging slots are written again
+                scatter.finish(pending[0])
+                pending[0] = None
+            if record and deferred: dmark.record()
             dpal, da, db = scatter.dw(w, x, dy, logits, noise, TAU, lora_ws=(t, dt))
             if record: marks[4].record()
-            if scatter.mode == "add":
+            if deferred:
+                h1 = scatter.start_beside([dpal, da, db])
+                pending[0] = h1
+                if record: xm[0].record(); xm[1].record()
+            elif scatter.mode == "add":
                 h1 = scatter.start([dpal, da, db])
                 if record: xm[0].record(); xm[1].record()
             elif split_rows > 0:
@@ -235,20 +254,22 @@ def run_ours(args):
         if world > 1:
             plz_native.lib().plz_set_cta_limit(0)
         if record: marks[5].record()
-        if scatter is not None:
+        if deferred:
+            dlog = scatter.full          # complete after the finish() that precedes the next dw (or the drain below)
+        elif scatter is not None:
             dlog = scatter.finish(h1)
         else:
             exch.finish(h1)
         if record: marks[6].record()
         if record:
             ev["select"].append((marks[0], marks[1])); ev["fwd"].append((marks[1], marks[2]))
-            ev["lora_dt"].append((marks[2], marks[3])); ev["dw"].append((marks[3], marks[4]))
+            ev["lora_dt"].append((marks[2], marks[3])); ev["dw"].append((dmark if deferred else marks[3], marks[4]))
             if scatter is not None:
                 ev["exch_sync"].append((marks[4], xm[0])); ev["exch_reduce"].append((xm[0], xm[1])); ev["dx"].append((xm[1], marks[5]))
             else:
                 ev["dx"].append((marks[4], marks[5]))
             if world > 1:
-                ev["exch_wait"].append((marks[5], marks[6]))
+                ev["exch_wait"].append((marks[3], dmark) if deferred else (marks[5], marks[6]))
         return y, dx, dlog, dpal, da, db
 
     def barrier():
@@ -267,6 +288,7 @@ def run_ours(args):
         parity["pass"] = bool(parity["pass"] and parity["sharded_optimizer"]["pass"])
     for _ in range(max(args.warmup, 3)):
         step(False)
+    drain()
     barrier()
     plz_native.device_status()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -278,6 +300,7 @@ def run_ours(args):
     t0.record()
     for _ in range(args.steps):
         step(True)
+    drain()      # the last step's exchange ends inside the timed region
     t1.record()
     launches = plz_native.lib().plz_launch_count() - launches0
     barrier()
@@ -303,6 +326,7 @@ def run_ours(args):
         while True:
             for _ in range(n_chunk):
                 step(False)
+            drain()
             n_done += n_chunk
             torch.cuda.synchronize()
             stop = torch.tensor([1.0 if time.time() - s_wall0 >= args.sustained_s else 0.0], device=dev)
@@ -1046,6 +1070,9 @@ def main():
     ap.add_argument("--N", type=int, default=N_OUT)
     ap.add_argument("--K", type=int, default=K_IN)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--defer-exchange", type=int, default=0, help="N > 1, fused slot mode: 1 = the whole exchange of a step runs on the side stream and is "
+                    "waited for right before the next step's weight-gradient kernel (0, the default = waited for at the end of its own step; "
+                    "deferring measured slower at 2 and 8 GPUs: the all-gather then competes with the HBM-bound select pass)")
     ap.add_argument("--split-dx", type=int, default=0, help="N > 1, fused slot mode: rows of dX computed beside the small all-reduce (0 = off; with it the exch_sync phase "
                          "contains that first block of dX)")
     ap.add_argument("--comm-sms", type=int, default=-1, help="N > 1: SMs the dX kernel leaves to the exchange (default: built-in)")

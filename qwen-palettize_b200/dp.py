@@ -250,6 +250,27 @@ class LogitGradScatter:
         self.reduce_and_push(step_fn)
         return handle
 
+    def start_beside(self, small, step_fn=None):
+        """Slot mode with NOTHING of the exchange on the compute stream: the small all-reduce (and with it the wait for the
+        slowest rank's weight-gradient kernel), the slot reduction, the pushes and the completion all-reduce are all queued
+        on the side stream. The caller goes on with work that does not need the gradients (the dX product, the next layer's
+        or the next step's forward) and calls finish() before it reads `full` / `small` and before the next dw(), which
+        reuses the staging slots: finish() returns only after every rank has reduced its slots (completion all-reduce).
+        The side-stream kernels take SMs only between or beside the compute stream's kernels, so the time they need is
+        not hidden, but the skew between the ranks is."""
+        if self.world == 1:
+            return None
+        if self.mode == "add":
+            return self._start_add(small, step_fn)
+        if step_fn is not None and self.param is None:
+            raise ValueError("step_fn needs shard_optimizer=True (the parameter must live in peer-visible memory)")
+        cur = torch.cuda.current_stream(self.device)
+        self._stream.wait_stream(cur)
+        with torch.cuda.stream(self._stream):
+            handle = self.sync_small(small)
+            self.reduce_and_push(step_fn)      # its "current stream" is the side stream here
+        return handle
+
     def _start_add(self, small, step_fn=None):
         """mode 'add': the owner's accumulator already holds the sum once every rank's kernel has finished, so the whole
         exchange runs on the side stream beside dX: small all-reduce (= all kernels finished) -> copy-engine pushes of the
