@@ -716,6 +716,30 @@ def extra_configs(torch, ops, plz_native, dev, pk):
                 "with LoRA, q/k norm + RoPE, causal GQA attention on tcgen05, SwiGLU, residuals; gradients of palettes, LoRA factors and norm weights"}
     del layers, xl, dyl
     torch.cuda.empty_cache()
+    # config 4, one GPU, super-block sized: a distillation step over 4 layers in SOFT mode (index logits trained, counter-based
+    # Gumbel noise) against a dense bf16 teacher of the same 4 layers on a second stream, loss, backward, fused AdamW
+    import distill_step as DS
+    sb = DS.Superblock(DL.LayerConfig(), 4, dev, seed=20, max_positions=512)
+    xs = torch.randn(Bc * Sc, 2560, device=dev).to(torch.bfloat16)
+    n0 = plz_native.lib().plz_launch_count()
+    sb.step(xs, Bc, Sc)
+    launches = plz_native.lib().plz_launch_count() - n0
+    sb.step(xs, Bc, Sc)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(3):
+        stats = sb.step(xs, Bc, Sc)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 3
+    out["config4_superblock_distill_step_B32_S512"] = {
+        "ms": ms, "tokens_per_s": Bc * Sc / (ms * 1e-3), "kernel_launches": int(launches), "loss": float(stats[0].item()),
+        "what": "one optimizer step on 16384 tokens: dense bf16 teacher forward of 4 layers (side stream) + student forward in soft mode "
+                "(logits -> packed argmax per Linear, LUT GEMMs + LoRA) + cos/MSE loss + backward with dLogits, dPalette, dA, dB from the "
+                "weight-gradient epilogues + fused fp32-master AdamW on index logits (403.6 M weights x 4 logits), palettes, LoRA, norms"}
+    sb.close()
+    del sb, xs
+    torch.cuda.empty_cache()
     # config 3: the full 36-layer model (vocab 151936, tied embeddings), every Linear hard-palettized, inference only:
     # prefill of 8 x 2048 tokens, then one decode step at batch 1 / 8 / 64 against a 2048-token bf16 key / value cache
     import decode_model as DM

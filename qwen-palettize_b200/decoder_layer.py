@@ -92,23 +92,44 @@ class LayerCtx:
     t: dict = field(default_factory=dict)   # tensors by name
 
 
-def layer_forward(cfg: LayerConfig, P: LayerParams, x: torch.Tensor, B: int, S: int, cos: torch.Tensor, sin: torch.Tensor, keep: bool = True):
-    """x bf16 [B * S, hidden] -> (y bf16 [B * S, hidden], ctx or None)."""
-    L = P.lin
+class HardLinears:
+    """The seven Linears of a layer with frozen 2-bit indices (hard mode): forward, and in the backward the input gradient plus
+    the gradients of the palette and of the LoRA factors, kept in `grads[name] = (dPalette, dA, dB)`.
+
+    layer_forward / layer_backward take any object with these two methods, so the same layer runs its Linears in another
+    mode (soft training with index logits: distill_step.SoftLinears; dense teacher weights: distill_step.DenseLinears)."""
+
+    def __init__(self, P: LayerParams):
+        self.P, self.grads = P, {}
+
+    def fwd(self, name: str, x: torch.Tensor):
+        """(y bf16 [M, N], t = the LoRA intermediate kept for the backward, or None)."""
+        L = self.P.lin[name]
+        return ops.hard_forward(L.w, x, L.lora)
+
+    def bwd(self, name: str, x_in: torch.Tensor, t_in, d_out: torch.Tensor) -> torch.Tensor:
+        L = self.P.lin[name]
+        dxi, dti = ops.backward_dx(L.w, d_out, L.lora)
+        self.grads[name] = ops.backward_dw_hard_lora(L.w, x_in, d_out, t_in, dti)
+        return dxi
+
+
+def layer_forward(cfg: LayerConfig, P, x: torch.Tensor, B: int, S: int, cos: torch.Tensor, sin: torch.Tensor, keep: bool = True, lin=None):
+    """x bf16 [B * S, hidden] -> (y bf16 [B * S, hidden], ctx or None). P supplies the norm weights (input_ln, post_ln, q_norm,
+    k_norm); lin the Linears (default: HardLinears(P))."""
+    lin = lin if lin is not None else HardLinears(P)
     h1, rstd1 = ops.rmsnorm_forward(x, P.input_ln, cfg.eps)
-    q_raw, t_q = ops.hard_forward(L["q"].w, h1, L["q"].lora)
-    k_raw, t_k = ops.hard_forward(L["k"].w, h1, L["k"].lora)
-    v, t_v = ops.hard_forward(L["v"].w, h1, L["v"].lora)
-    q = ops.qknorm_rope_forward(q_raw, P.q_norm, cos, sin, cfg.n_heads, S, cfg.eps)
-    k = ops.qknorm_rope_forward(k_raw, P.k_norm, cos, sin, cfg.n_kv_heads, S, cfg.eps)
+    q_raw, t_q = lin.fwd("q", h1)
+    k_raw, t_k = lin.fwd("k", h1)
+    v, t_v = lin.fwd("v", h1)
+    q, k = ops.qknorm_rope_forward2(q_raw, P.q_norm, cfg.n_heads, k_raw, P.k_norm, cfg.n_kv_heads, cos, sin, S, cfg.eps)
     a, lse = ops.attention_forward(q, k, v, B, S, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
-    o, t_o = ops.hard_forward(L["o"].w, a, L["o"].lora)
-    x2 = ops.add(x, o)
-    h2, rstd2 = ops.rmsnorm_forward(x2, P.post_ln, cfg.eps)
-    gate, t_g = ops.hard_forward(L["gate"].w, h2, L["gate"].lora)
-    up, t_u = ops.hard_forward(L["up"].w, h2, L["up"].lora)
+    o, t_o = lin.fwd("o", a)
+    x2, h2, rstd2 = ops.add_rmsnorm_forward(x, o, P.post_ln, cfg.eps, want_rstd=True)
+    gate, t_g = lin.fwd("gate", h2)
+    up, t_u = lin.fwd("up", h2)
     act = ops.swiglu_forward(gate, up)
-    d, t_d = ops.hard_forward(L["down"].w, act, L["down"].lora)
+    d, t_d = lin.fwd("down", act)
     y = ops.add(x2, d)
     if not keep:
         return y, None
@@ -117,28 +138,24 @@ def layer_forward(cfg: LayerConfig, P: LayerParams, x: torch.Tensor, B: int, S: 
     return y, ctx
 
 
-def layer_backward(cfg: LayerConfig, P: LayerParams, ctx: LayerCtx, dy: torch.Tensor, B: int, S: int, cos: torch.Tensor, sin: torch.Tensor):
-    """dy bf16 [B * S, hidden] -> (dx, grads) with grads[name] = (dPalette fp32 [groups, 4], dA fp32 [r, K], dB fp32 [N, r]) for the seven
-    Linears and fp32 vectors for 'input_ln', 'post_ln', 'q_norm', 'k_norm'."""
-    L, c, g = P.lin, ctx.t, {}
-
-    def lin_bwd(name, x_in, t_in, d_out):
-        dxi, dti = ops.backward_dx(L[name].w, d_out, L[name].lora)
-        g[name] = ops.backward_dw_hard_lora(L[name].w, x_in, d_out, t_in, dti)
-        return dxi
-
-    dact = lin_bwd("down", c["act"], c["t_d"], dy)
+def layer_backward(cfg: LayerConfig, P, ctx: LayerCtx, dy: torch.Tensor, B: int, S: int, cos: torch.Tensor, sin: torch.Tensor, lin=None):
+    """dy bf16 [B * S, hidden] -> (dx, grads): grads holds fp32 vectors for 'input_ln', 'post_ln', 'q_norm', 'k_norm' and whatever
+    the Linears' object left in its `grads` (HardLinears: grads[name] = (dPalette fp32 [groups, 4], dA fp32 [r, K], dB fp32 [N, r]))."""
+    lin = lin if lin is not None else HardLinears(P)
+    c, g = ctx.t, {}
+    dact = lin.bwd("down", c["act"], c["t_d"], dy)
     dgate, dup = ops.swiglu_backward(c["gate"], c["up"], dact)
-    dh2 = ops.add(lin_bwd("gate", c["h2"], c["t_g"], dgate), lin_bwd("up", c["h2"], c["t_u"], dup))
+    dh2 = ops.add(lin.bwd("gate", c["h2"], c["t_g"], dgate), lin.bwd("up", c["h2"], c["t_u"], dup))
     dx2n, g["post_ln"] = ops.rmsnorm_backward(c["x2"], dh2, c["rstd2"], P.post_ln)
     dx2 = ops.add(dy, dx2n)
-    da = lin_bwd("o", c["a"], c["t_o"], dx2)
+    da = lin.bwd("o", c["a"], c["t_o"], dx2)
     dq, dk, dv = ops.attention_backward(c["q"], c["k"], c["v"], c["a"], da, c["lse"], B, S, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
     dq_raw, g["q_norm"] = ops.qknorm_rope_backward(c["q_raw"], P.q_norm, cos, sin, dq, cfg.n_heads, S, cfg.eps)
     dk_raw, g["k_norm"] = ops.qknorm_rope_backward(c["k_raw"], P.k_norm, cos, sin, dk, cfg.n_kv_heads, S, cfg.eps)
-    dh1 = ops.add(lin_bwd("q", c["h1"], c["t_q"], dq_raw), lin_bwd("k", c["h1"], c["t_k"], dk_raw), lin_bwd("v", c["h1"], c["t_v"], dv))
+    dh1 = ops.add(lin.bwd("q", c["h1"], c["t_q"], dq_raw), lin.bwd("k", c["h1"], c["t_k"], dk_raw), lin.bwd("v", c["h1"], c["t_v"], dv))
     dx1n, g["input_ln"] = ops.rmsnorm_backward(c["x"], dh1, c["rstd1"], P.input_ln)
     dx = ops.add(dx2, dx1n)
+    g.update(getattr(lin, "grads", {}))
     return dx, g
 
 

@@ -567,16 +567,18 @@ def rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor | None, eps: float = 1
     return h, rstd
 
 
-def add_rmsnorm_forward(x: torch.Tensor, addend: torch.Tensor, weight: torch.Tensor | None, eps: float = 1e-6):
-    """(s = x + addend, h = rmsnorm(s) * weight), both bf16 [M, K], in one pass."""
+def add_rmsnorm_forward(x: torch.Tensor, addend: torch.Tensor, weight: torch.Tensor | None, eps: float = 1e-6, want_rstd: bool = False):
+    """(s = x + addend, h = rmsnorm(s) * weight), both bf16 [M, K], in one pass; with want_rstd also rstd fp32 [M] (the
+    backward of the norm needs it)."""
     M, K = x.shape
     _mat(x, K), _mat(addend, K)
     s = torch.empty(M, K, dtype=torch.bfloat16, device=x.device)
     h = torch.empty(M, K, dtype=torch.bfloat16, device=x.device)
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device) if want_rstd else None
     P.check(P.lib().plz_add_rmsnorm_fwd(x.data_ptr(), x.stride(0), addend.data_ptr(), addend.stride(0), s.data_ptr(), s.stride(0),
-                                        weight.data_ptr() if weight is not None else None, M, K, float(eps), h.data_ptr(), h.stride(0), None,
-                                        P.stream_ptr()), "plz_add_rmsnorm_fwd")
-    return s, h
+                                        weight.data_ptr() if weight is not None else None, M, K, float(eps), h.data_ptr(), h.stride(0),
+                                        rstd.data_ptr() if rstd is not None else None, P.stream_ptr()), "plz_add_rmsnorm_fwd")
+    return (s, h, rstd) if want_rstd else (s, h)
 
 
 def qknorm_rope_forward2(xq, wq, n_heads: int, xk, wk, n_kv_heads: int, cos, sin, S: int, eps: float = 1e-6, out_q=None, out_k=None):
