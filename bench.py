@@ -920,6 +920,88 @@ def run_case(a):
     print("status", plz_native.device_status())
 
 
+def run_distill(args):
+    """--workload distill: the super-block distillation step (distill_step.Superblock: 4 layers of the Qwen-4B shape, dense
+    teacher, soft student, loss, backward, optimizer) on N GPUs, 16384 tokens per rank (weak scaling). At N > 1 the
+    index-logit gradients go through the reduce-scatter fused into the weight-gradient kernels with the sharded AdamW
+    (--exchange allreduce: plain NCCL all-reduce of every gradient and a replicated AdamW, for comparison), and before timing
+    the two exchanges are compared on a small super-block (same inputs, 2 steps, parameters must agree)."""
+    import torch
+    import torch.distributed as dist
+    import decoder_layer as DL
+    import distill_step as DS
+    import plz_native
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+    rank, world, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local if world > 1 else 0)
+    fused = args.exchange != "allreduce"
+    parity = None
+    if world > 1 and fused and not args.no_parity:
+        cfg_s = DL.LayerConfig(hidden=256, n_heads=2, n_kv_heads=1, head_dim=128, intermediate=512)
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        xs = torch.randn(256, cfg_s.hidden, generator=g, device=dev).to(torch.bfloat16)
+        res = []
+        for f in (True, False):
+            sb = DS.Superblock(cfg_s, 2, dev, seed=7, fused_exchange=f, max_positions=256)
+            for _ in range(2):
+                sb.step(xs, 1, 256)
+            torch.cuda.synchronize()
+            L = sb.student[0]["down"]
+            res.append((L.logits.clone(), L.w.palette.float().clone(), L.lora_b.float().clone(), sb.norms[1].post_ln.float().clone()))
+            sb.close()
+        worst = max((a - b).abs().max().item() for a, b in zip(*res))
+        t = torch.tensor([worst], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        parity = {"param_max_abs_diff_fused_vs_allreduce": t.item(), "pass": bool(t.item() < 2e-3),
+                  "what": "2 layers (hidden 256), 2 steps: logits, palette, LoRA B, norm weight after the fused exchange + sharded AdamW "
+                          "against all-reduce + replicated AdamW"}
+    cfg = DL.LayerConfig()
+    Bc, Sc, n_layers = 32, 512, 4
+    sb = DS.Superblock(cfg, n_layers, dev, seed=20, fused_exchange=fused, max_positions=Sc)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    x = torch.randn(Bc * Sc, cfg.hidden, generator=g, device=dev).to(torch.bfloat16)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(max(args.warmup, 3)):
+        sb.step(x, Bc, Sc)
+    barrier()
+    plz_native.device_status()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0 = plz_native.lib().plz_launch_count()
+    t0.record()
+    for _ in range(args.steps):
+        stats = sb.step(x, Bc, Sc)
+    t1.record()
+    launches = plz_native.lib().plz_launch_count() - n0
+    barrier()
+    ms = t0.elapsed_time(t1)
+    if world > 1:
+        tt = torch.tensor([ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = tt.item()
+    plz_native.device_status()
+    line = {"metric": "distillation-step tokens/s, 4-layer super-block of the Qwen-4B shape", "value": Bc * Sc * world * args.steps / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "super-block distillation step: dense bf16 teacher + soft palettized student (LoRA r16), 4 layers, "
+                                   "batch 32 x seq 512 per GPU, loss, backward, AdamW on logits / palettes / LoRA / norms",
+                       "exchange": "none" if world == 1 else ("fused reduce-scatter in the weight-gradient kernels + sharded logits AdamW"
+                                                             if fused else "NCCL all-reduce + replicated AdamW"), "parallelism": f"dp{world}"},
+            "gpu_launches": int(launches), "loss": float(stats[0].item()), "parity": parity}
+    sb.close()
+    if rank == 0:
+        os.dup2(saved_stdout, 1)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    if parity is not None and not parity["pass"]:
+        raise SystemExit(3)
+
+
 def run_kernel_table(a):
     """Per-kernel measurements beside the step benchmark, one JSON line each: small-M decode at M in {1, 8, 16, 64} for three
     Linear shapes (weights rotated over more than 2 x L2 of copies, launches inside a CUDA graph), gate + up in one launch,
@@ -1088,6 +1170,8 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the correctness check of the fused exchange that runs before the timed region")
     ap.add_argument("--sustained-s", type=float, default=3.0, help="length of the sustained leg in seconds (0 = off)")
     ap.add_argument("--pair-gemm", type=int, default=1, help="0: keep the large products on the one-CTA-per-tile kernels (comparison)")
+    ap.add_argument("--workload", default="linear", choices=["linear", "distill"],
+                    help="linear (default): the benchmark step of one Linear; distill: the super-block distillation step (its own JSON line)")
     ap.add_argument("--case", default=None, help="run ONE kernel of the hot path a few times on a small case and exit (for ncu captures)")
     ap.add_argument("--kernels", action="store_true", help="per-kernel table: one JSON line per measurement")
     ap.add_argument("--M", type=int, default=4096)
@@ -1103,7 +1187,9 @@ def main():
     ap.add_argument("--exchange", default="fused", choices=["fused", "fused-add", "allreduce"],
                     help="N > 1: dLogits reduce-scatter fused into the weight-gradient kernel (default) or a plain NCCL all-reduce")
     args = ap.parse_args()
-    if args.case:
+    if args.workload == "distill":
+        run_distill(args)
+    elif args.case:
         run_case(args)
     elif args.kernels:
         run_kernel_table(args)
