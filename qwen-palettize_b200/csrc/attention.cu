@@ -7,9 +7,10 @@
 // transformers' Qwen3Attention: softmax(q k^T / sqrt(d) + causal mask) v, fp32 softmax, bf16 operands.
 //
 // All products run on the 5th-generation tensor cores (tcgen05.mma, 128 x 128 x 16, accumulators in TMEM), operands
-// staged by TMA in 128-byte-swizzled tiles. One CTA handles one (batch, head, 128-token tile):
-//   forward        S = Q K^T -> online softmax by 128 threads (one row each, TMEM -> registers) -> P (bf16) to shared
-//                  memory -> O += P V, O rescaled in TMEM when a row maximum grows; also writes the row log-sum-exp.
+// staged by TMA in 128-byte-swizzled tiles. One CTA handles one (batch, head) and one or two 128-token tiles:
+//   forward        two neighbouring query tiles per CTA: S = Q K^T -> online softmax by 128 threads per tile (one row each,
+//                  TMEM -> registers) -> P (bf16) to shared memory -> O += P V, O rescaled in TMEM when a row maximum grows;
+//                  the softmax of one tile runs under the MMAs of the other; also writes the row log-sum-exp.
 //   backward dQ    per q tile: S, dP = dO V^T -> dS = P (dP - D) / sqrt(d) -> dQ += dS K
 //   backward dKdV  per kv tile and kv head, over the q heads of the group and the q tiles at or after it:
 //                  S, dP -> P, dS to shared memory -> dV += P^T dO, dK += dS^T Q  (P^T / dS^T are the same bytes read
@@ -77,8 +78,122 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, 
 // ---------------------------------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int kFwdThreads = 160;   // warps 0..3: softmax (thread = row), warp 4: TMA + MMA
-constexpr uint32_t kFwdSmem = 6 * kTile + 1024 + 256;   // Q, K x 2, V x 2, P
+// One CTA takes TWO neighbouring 128-query tiles (A = tile 2i, B = tile 2i + 1) of one head and walks the key / value tiles
+// they share once. Warps 0-3 are the softmax group of A, warps 4-7 of B (thread = query row = TMEM lane), warp 8 issues the
+// TMA copies and the MMAs. S_A, S_B, O_A, O_B fill the 512 TMEM columns; Q_A, Q_B, two K stages, one V stage and one P tile
+// per group (7 x 32 KB) fill the shared memory. While one group runs its softmax on S(j), the tensor core runs the other group's O += P V(j - 1... j)
+// and S(j + 1): the exponentials (MUFU, 16 per clock) and the MMAs cost about the same per tile, so each hides the other.
+constexpr int kFwdThreads = 288;   // warps 0..3 / 4..7: softmax of tile A / B, warp 8: TMA + MMA
+constexpr uint32_t kFwdSmem = 7 * kTile + 1024 + 256;   // Q x 2, K x 2, V, P x 2
+
+struct FwdGroup {          // what one softmax group works on
+    uint32_t tS, tO;       // TMEM columns of its score and output accumulators
+    uint32_t s_full, p_full, o_full;
+    uint8_t* pP; uint32_t sP;
+    int qt;                // its query tile; it attends key tiles 0 .. qt
+};
+
+__device__ __forceinline__ void fwd_softmax_group(const FwdGroup& G, const AttnParams& p, const CUtensorMap* tmO, int h, int b, int row0,
+                                                  int warp_in_group, int lane, int bar_id, volatile uint32_t* abort_flag) {
+    const int r = warp_in_group * 32 + lane;                       // query row of the tile = TMEM lane
+    const uint32_t lane_off = (uint32_t)(warp_in_group * 32) << 16;
+    const float c = p.scale * kLog2e;
+    const int n_kv = G.qt + 1;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+        ok = mbar_wait(G.s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 20);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const bool diag = (j == G.qt);
+        // pass 1: row maximum of this tile
+        float m_tile = -INFINITY;
+#pragma unroll 1
+        for (int cb = 0; cb < 4; ++cb) {
+            uint32_t v[32];
+            tmem_ld_32x32(G.tS + lane_off + cb * 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float sc = __uint_as_float(v[i]);
+                if (!diag || cb * 32 + i <= r) m_tile = fmaxf(m_tile, sc);
+            }
+        }
+        const float m_new = fmaxf(m_run, m_tile);
+        const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * c);
+        // the previous P V product must have landed before O is rescaled and before P is overwritten
+        if (j > 0) {
+            ok = mbar_wait(G.o_full, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 21);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (__any_sync(0xFFFFFFFFu, m_new > m_run)) {
+#pragma unroll 1
+                for (int cb = 0; cb < 4; ++cb) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(G.tO + lane_off + cb * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st_32x32(G.tO + lane_off + cb * 32, v);
+                }
+            }
+        }
+        // pass 2: P = exp2(s c - m c), row sum, bf16 row into the swizzled P tile
+        const float mc = m_new * c;
+        float l_tile = 0.f;
+#pragma unroll 1
+        for (int cb = 0; cb < 4; ++cb) {
+            uint32_t v[32];
+            tmem_ld_32x32(G.tS + lane_off + cb * 32, v);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c0 = cb * 32 + g * 8 + 2 * i;
+                    float p0 = exp2f(fmaf(__uint_as_float(v[g * 8 + 2 * i]), c, -mc));
+                    float p1 = exp2f(fmaf(__uint_as_float(v[g * 8 + 2 * i + 1]), c, -mc));
+                    if (diag) { if (c0 > r) p0 = 0.f; if (c0 + 1 > r) p1 = 0.f; }
+                    l_tile += p0 + p1;
+                    o[i] = pack_bf16x2(p0, p1);
+                }
+                *reinterpret_cast<uint4*>(tile_chunk(G.pP, r, cb * 4 + g)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+        l_run = l_run * alpha + l_tile;
+        m_run = m_new;
+        tc_fence_before_sync();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(G.p_full);
+    }
+    // epilogue: O / l -> bf16 -> the P tile as staging -> TMA store; log-sum-exp for the backward
+    if (ok) ok = mbar_wait(G.o_full, (n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 22);
+    if (ok) {
+        tc_fence_after_sync();
+        const float inv_l = 1.0f / l_run;
+#pragma unroll 1
+        for (int cb = 0; cb < 4; ++cb) {
+            uint32_t v[32];
+            tmem_ld_32x32(G.tO + lane_off + cb * 32, v);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    o[i] = pack_bf16x2(__uint_as_float(v[g * 8 + 2 * i]) * inv_l, __uint_as_float(v[g * 8 + 2 * i + 1]) * inv_l);
+                *reinterpret_cast<uint4*>(tile_chunk(G.pP, r, cb * 4 + g)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+        if (p.lse) p.lse[((long long)b * p.Hq + h) * p.S + G.qt * kT + r] = m_run * p.scale + logf(l_run);
+        fence_proxy_async_smem();
+        asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+        if (r == 0) {
+            tma_store_2d(tmO, G.sP, h * kD, row0 + G.qt * kT);
+            tma_store_2d(tmO, G.sP + kBlk, h * kD + 64, row0 + G.qt * kT);
+            tma_store_commit();
+            tma_store_wait_all();
+        }
+    }
+}
 
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -87,184 +202,117 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (base - raw);
-    const uint32_t sQ = base, sK0 = base + kTile, sV0 = base + 3 * kTile, sP = base + 5 * kTile;
-    uint8_t* pP = smem + 5 * kTile;
-    const uint32_t bar = base + 6 * kTile;
-    const uint32_t q_full = bar, kv_full0 = bar + 8, kv_empty0 = bar + 24, s_full = bar + 40, p_full = bar + 48, o_full = bar + 56;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 6 * kTile + 64);
+    const uint32_t sQ0 = base, sK0 = base + 2 * kTile, sV = base + 4 * kTile, sP0 = base + 5 * kTile;
+    const uint32_t bar = base + 7 * kTile;
+    const uint32_t q_full = bar, k_full0 = bar + 8, k_empty0 = bar + 24, v_full = bar + 40, v_empty = bar + 48;
+    auto s_full = [&](int g) { return bar + 56u + 8u * g; };
+    auto p_full = [&](int g) { return bar + 72u + 8u * g; };
+    auto o_full = [&](int g) { return bar + 88u + 8u * g; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 7 * kTile + 112);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_qt = p.S / kT;
-    const int qt = n_qt - 1 - (int)blockIdx.x;   // heavy tiles first
+    const int n_pairs = (n_qt + 1) / 2;
+    const int pi = n_pairs - 1 - (int)blockIdx.x;   // heavy pairs first
+    const int qtA = 2 * pi, qtB = 2 * pi + 1;
+    const bool hasB = qtB < n_qt;
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (p.Hq / p.Hkv);
-    const int n_kv = qt + 1;
+    const int n_kvA = qtA + 1;
+    const int n_kv = hasB ? qtB + 1 : n_kvA;
     const int row0 = b * p.S;
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
-        for (int i = 0; i < 2; ++i) { mbar_init(kv_full0 + 8 * i, 1); mbar_init(kv_empty0 + 8 * i, 1); }
-        mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(o_full, 1);
+        mbar_init(q_full, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full0 + 8 * i, 1); mbar_init(k_empty0 + 8 * i, 1);
+            mbar_init(s_full(i), 1); mbar_init(p_full(i), 4); mbar_init(o_full(i), 1);
+        }
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 4) { tmem_alloc(smem_u32((const void*)tmem_slot), 256); tmem_relinquish(); }
+    if (warp == 8) { tmem_alloc(smem_u32((const void*)tmem_slot), 512); tmem_relinquish(); }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tS = tmem, tO = tmem + 128;
+    auto tS = [&](int g) { return tmem + 128u * g; };
+    auto tO = [&](int g) { return tmem + 256u + 128u * g; };
 
-    if (warp == 4) {
+    if (warp == 8) {
         if (lane == 0) {
             tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-            mbar_arrive_expect_tx(q_full, kTile);
-            load_tile(sQ, &tmQ, q_full, h * kD, row0 + qt * kT);
+            mbar_arrive_expect_tx(q_full, hasB ? 2 * kTile : kTile);
+            load_tile(sQ0, &tmQ, q_full, h * kD, row0 + qtA * kT);
+            if (hasB) load_tile(sQ0 + kTile, &tmQ, q_full, h * kD, row0 + qtB * kT);
             bool ok = true;
-            // prologue: K/V tiles 0 (and 1)
             for (int j = 0; j < 2 && j < n_kv; ++j) {
-                mbar_arrive_expect_tx(kv_full0 + 8 * j, 2 * kTile);
-                load_tile(sK0 + j * kTile, &tmK, kv_full0 + 8 * j, hk * kD, row0 + j * kT);
-                load_tile(sV0 + j * kTile, &tmV, kv_full0 + 8 * j, hk * kD, row0 + j * kT);
+                mbar_arrive_expect_tx(k_full0 + 8 * j, kTile);
+                load_tile(sK0 + j * kTile, &tmK, k_full0 + 8 * j, hk * kD, row0 + j * kT);
             }
+            mbar_arrive_expect_tx(v_full, kTile);
+            load_tile(sV, &tmV, v_full, hk * kD, row0);
             ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_TIMEOUT_FULL, 10);
-            for (int j = 0; j < n_kv && ok; ++j) {
-                const int s = j & 1;
-                if (j == 0) {
-                    ok = mbar_wait(kv_full0, 0, abort_flag, p.status, ST_TIMEOUT_FULL, 11);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    mma_128(tS, sQ, false, sK0, false, false);            // S_0 = Q K_0^T
-                    umma_commit(s_full);
-                }
-                // P_j is ready (and S_j has been read): O += P_j V_j, then S_{j+1} while the softmax warps work on nothing else
-                ok = mbar_wait(p_full, j & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 12);
-                if (!ok) break;
+            if (ok) ok = mbar_wait(k_full0, 0, abort_flag, p.status, ST_TIMEOUT_FULL, 11);
+            if (ok) {
                 tc_fence_after_sync();
-                mma_128(tO, sP, false, sV0 + s * kTile, true, j > 0);       // O += P V_j  (V: rows = kv = reduction index)
-                umma_commit(kv_empty0 + 8 * s);
-                umma_commit(o_full);
-                if (j + 1 < n_kv) {
-                    const int s1 = (j + 1) & 1;
-                    ok = mbar_wait(kv_full0 + 8 * s1, ((j + 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 13);
+                mma_128(tS(0), sQ0, false, sK0, false, false);                    // S_A(0) = Q_A K_0^T
+                umma_commit(s_full(0));
+                if (hasB) { mma_128(tS(1), sQ0 + kTile, false, sK0, false, false); umma_commit(s_full(1)); }
+            }
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const int s = j & 1, s1 = (j + 1) & 1;
+                ok = mbar_wait(v_full, j & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 15);
+                if (!ok) break;
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const int n_g = g == 0 ? n_kvA : n_kv;
+                    if ((g == 1 && !hasB) || j >= n_g) continue;
+                    // P_g(j) is ready (and S_g(j) has been read): O_g += P_g V_j, then S_g(j + 1) while the other group's softmax runs
+                    ok = mbar_wait(p_full(g), j & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 12);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    mma_128(tS, sQ, false, sK0 + s1 * kTile, false, false);
-                    umma_commit(s_full);
+                    mma_128(tO(g), sP0 + g * kTile, false, sV, true, j > 0);      // V: rows = kv = reduction index
+                    umma_commit(o_full(g));
+                    if (j + 1 < n_g) {
+                        ok = mbar_wait(k_full0 + 8 * s1, ((j + 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_FULL, 13);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        mma_128(tS(g), sQ0 + g * kTile, false, sK0 + s1 * kTile, false, false);
+                        umma_commit(s_full(g));
+                    }
+                }
+                if (!ok) break;
+                // every product that reads V_j and K_j has been issued: the two buffers are free once those have completed
+                umma_commit(v_empty);
+                umma_commit(k_empty0 + 8 * s);
+                if (j + 1 < n_kv) {
+                    ok = mbar_wait(v_empty, j & 1, abort_flag, p.status, ST_TIMEOUT_EMPTY, 16);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(v_full, kTile);
+                    load_tile(sV, &tmV, v_full, hk * kD, row0 + (j + 1) * kT);
                 }
                 if (j + 2 < n_kv) {
-                    // refill the stage PV_j has just been issued on, once that product has completed
-                    ok = mbar_wait(kv_empty0 + 8 * s, (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_EMPTY, 14);
+                    ok = mbar_wait(k_empty0 + 8 * s, (j >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_EMPTY, 14);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(kv_full0 + 8 * s, 2 * kTile);
-                    load_tile(sK0 + s * kTile, &tmK, kv_full0 + 8 * s, hk * kD, row0 + (j + 2) * kT);
-                    load_tile(sV0 + s * kTile, &tmV, kv_full0 + 8 * s, hk * kD, row0 + (j + 2) * kT);
+                    mbar_arrive_expect_tx(k_full0 + 8 * s, kTile);
+                    load_tile(sK0 + s * kTile, &tmK, k_full0 + 8 * s, hk * kD, row0 + (j + 2) * kT);
                 }
             }
         }
     } else {
-        // ---- softmax warps: thread r owns row r of the tile (TMEM lane r)
-        const int r = threadIdx.x;
-        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-        const float c = p.scale * kLog2e;
-        float m_run = -INFINITY, l_run = 0.f;
-        bool ok = true;
-        for (int j = 0; j < n_kv && ok; ++j) {
-            ok = mbar_wait(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 20);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const bool diag = (j == qt);
-            // pass 1: row maximum of this tile
-            float m_tile = -INFINITY;
-#pragma unroll 1
-            for (int cb = 0; cb < 4; ++cb) {
-                uint32_t v[32];
-                tmem_ld_32x32(tS + lane_off + cb * 32, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float s = __uint_as_float(v[i]);
-                    if (!diag || cb * 32 + i <= r) m_tile = fmaxf(m_tile, s);
-                }
-            }
-            const float m_new = fmaxf(m_run, m_tile);
-            const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_new) * c);
-            // the previous P V product must have landed before O is rescaled and before P is overwritten
-            if (j > 0) {
-                ok = mbar_wait(o_full, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 21);
-                if (!ok) break;
-                tc_fence_after_sync();
-                if (__any_sync(0xFFFFFFFFu, m_new > m_run)) {
-#pragma unroll 1
-                    for (int cb = 0; cb < 4; ++cb) {
-                        uint32_t v[32];
-                        tmem_ld_32x32(tO + lane_off + cb * 32, v);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st_32x32(tO + lane_off + cb * 32, v);
-                    }
-                }
-            }
-            // pass 2: P = exp2((s - m) c), row sum, bf16 row into the swizzled P tile
-            float l_tile = 0.f;
-#pragma unroll 1
-            for (int cb = 0; cb < 4; ++cb) {
-                uint32_t v[32];
-                tmem_ld_32x32(tS + lane_off + cb * 32, v);
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint32_t o[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int c0 = cb * 32 + g * 8 + 2 * i;
-                        float p0 = exp2f((__uint_as_float(v[g * 8 + 2 * i]) - m_new) * c);
-                        float p1 = exp2f((__uint_as_float(v[g * 8 + 2 * i + 1]) - m_new) * c);
-                        if (diag) { if (c0 > r) p0 = 0.f; if (c0 + 1 > r) p1 = 0.f; }
-                        l_tile += p0 + p1;
-                        o[i] = pack_bf16x2(p0, p1);
-                    }
-                    *reinterpret_cast<uint4*>(tile_chunk(pP, r, cb * 4 + g)) = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-            }
-            l_run = l_run * alpha + l_tile;
-            m_run = m_new;
-            tc_fence_before_sync();
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
-        }
-        // epilogue: O / l -> bf16 -> the P tile as staging -> TMA store; log-sum-exp for the backward
-        if (ok) ok = mbar_wait(o_full, (n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 22);
-        if (ok) {
-            tc_fence_after_sync();
-            const float inv_l = 1.0f / l_run;
-#pragma unroll 1
-            for (int cb = 0; cb < 4; ++cb) {
-                uint32_t v[32];
-                tmem_ld_32x32(tO + lane_off + cb * 32, v);
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint32_t o[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        o[i] = pack_bf16x2(__uint_as_float(v[g * 8 + 2 * i]) * inv_l, __uint_as_float(v[g * 8 + 2 * i + 1]) * inv_l);
-                    *reinterpret_cast<uint4*>(tile_chunk(pP, r, cb * 4 + g)) = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-            }
-            if (p.lse) p.lse[((long long)b * p.Hq + h) * p.S + qt * kT + r] = m_run * p.scale + logf(l_run);
-            fence_proxy_async_smem();
-            bar_sync_128();
-            if (threadIdx.x == 0) {
-                tma_store_2d(&tmO, sP, h * kD, row0 + qt * kT);
-                tma_store_2d(&tmO, sP + kBlk, h * kD + 64, row0 + qt * kT);
-                tma_store_commit();
-                tma_store_wait_all();
-            }
+        const int g = warp >> 2;
+        if (g == 0 || hasB) {
+            FwdGroup G;
+            G.tS = tS(g); G.tO = tO(g); G.s_full = s_full(g); G.p_full = p_full(g); G.o_full = o_full(g);
+            G.pP = smem + 5 * kTile + g * kTile; G.sP = sP0 + g * kTile; G.qt = g == 0 ? qtA : qtB;
+            fwd_softmax_group(G, p, &tmO, h, b, row0, warp & 3, lane, 1 + g, abort_flag);
         }
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 4) { tc_fence_after_sync(); tmem_dealloc(tmem, 256); }
+    if (warp == 8) { tc_fence_after_sync(); tmem_dealloc(tmem, 512); }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -597,7 +645,7 @@ int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
     p.B = a.B; p.S = a.S; p.Hq = a.Hq; p.Hkv = a.Hkv; p.scale = a.scale; p.lse = a.lse; p.status = device_status_ptr();
     static bool once = false;
     if (!once) { if ((rc = set_smem(attn_fwd_kernel, kFwdSmem))) return rc; once = true; }
-    attn_fwd_kernel<<<dim3(a.S / kT, a.Hq, a.B), kFwdThreads, kFwdSmem, stream>>>(tmQ, tmK, tmV, tmO, p);
+    attn_fwd_kernel<<<dim3((a.S / kT + 1) / 2, a.Hq, a.B), kFwdThreads, kFwdSmem, stream>>>(tmQ, tmK, tmV, tmO, p);
     PLZ_LAUNCH_CHECK();
     return PLZ_OK;
 }
