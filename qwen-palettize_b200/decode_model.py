@@ -108,13 +108,13 @@ class PalettizedQwen:
         assert cache.length == 0 and S <= cache.k.shape[2] and S % 128 == 0
         cos, sin = self.cos[:S], self.sin[:S]
         h = ops.embed_gather(self.embed, ids)
+        h1, _ = ops.rmsnorm_forward(h, self.layers[0]["input_ln"], c.eps)
+        n = len(self.layers)
         for li, L in enumerate(self.layers):
-            h1, _ = ops.rmsnorm_forward(h, L["input_ln"], c.eps)
             q_raw = ops.hard_forward(L["q"], h1)[0]
             k_raw = ops.hard_forward(L["k"], h1)[0]
             v = ops.hard_forward(L["v"], h1)[0]
-            q = ops.qknorm_rope_forward(q_raw, L["q_norm"], cos, sin, c.n_heads, S, c.eps)
-            k = ops.qknorm_rope_forward(k_raw, L["k_norm"], cos, sin, c.n_kv_heads, S, c.eps)
+            q, k = ops.qknorm_rope_forward2(q_raw, L["q_norm"], c.n_heads, k_raw, L["k_norm"], c.n_kv_heads, cos, sin, S, c.eps)
             a, _ = ops.attention_forward(q, k, v, B, S, c.n_heads, c.n_kv_heads, c.head_dim)
             cache.k[li, :, :S].copy_(k.view(B, S, -1))
             cache.v[li, :, :S].copy_(v.view(B, S, -1))
@@ -126,9 +126,11 @@ class PalettizedQwen:
             else:
                 x2, h2 = ops.add_rmsnorm_forward(h, o, L["post_ln"], c.eps)
                 act = ops.swiglu_forward(ops.hard_forward(L["gate"], h2)[0], ops.hard_forward(L["up"], h2)[0])
-            h = ops.add(x2, ops.hard_forward(L["down"], act)[0])
+            d = ops.hard_forward(L["down"], act)[0]
+            # the residual add closes the layer and the same pass applies the next layer's (or the final) norm
+            h, h1 = ops.add_rmsnorm_forward(x2, d, self.layers[li + 1]["input_ln"] if li + 1 < n else self.final_norm, c.eps)
         cache.length = S
-        last = self.logits(h.view(B, S, -1)[:, -1].contiguous()) if want_logits else None
+        last = self.head(h1.view(B, S, -1)[:, -1].contiguous()) if want_logits else None
         return h, last
 
     # ---- decode --------------------------------------------------------------------------------------------------
