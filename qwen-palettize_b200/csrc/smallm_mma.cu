@@ -11,7 +11,7 @@
 //     capacity, not HBM, was the limit), and one bulk copy per row 50 cycles of issue each;
 //   * while the rows are in flight all warps stage x in shared memory, in the permuted order below;
 //   * a work item is 16 rows x 256 input columns (one palette group per row); the items are dealt round-robin to the
-//     16 warps.  Weights go from shared memory straight into mma.sync.m16n8k16 A fragments (the 128-row tcgen05 tile
+//     warps (32 of them up to eight rows, 16 beyond).  Weights go from shared memory straight into mma.sync.m16n8k16 A fragments (the 128-row tcgen05 tile
 //     would be 7/8 padding here): the reduction dimension may be permuted freely as long as x is permuted alike, so
 //     lane (g, t) simply takes the 16 bytes at columns 64 t.. of rows g and g + 8 of the group; k-step 4 w + e uses bit
 //     pair e of each of the four bytes of word w (the weights 16 w + e, + 4, + 8, + 12 of the lane's 64 columns).  One mask
@@ -34,10 +34,14 @@ namespace plz {
 
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kWarps = kThreads / 32;
+// Up to eight rows (MT = 1) the kernel runs 1024 threads of 64 registers (measured 5 % faster than 512: more warps to cover the
+// dependent decode -> mma chains); with sixteen rows the second accumulator set needs the registers of 512 threads.
+template <int MT> struct SmallmCfg {
+    static constexpr int kThreads = MT == 1 ? 1024 : 512;
+    static constexpr int kWarps = kThreads / 32;
+    static constexpr int kBatch = MT == 1 ? 2 : 4;    // items whose palette loads a warp keeps in flight together
+};
 constexpr int kHeader = 1024;        // mbarriers (one per strip, up to 126) and the abort flags
-constexpr int kBatch = 4;            // items whose loads a warp keeps in flight together
 
 constexpr int kMaxMats = 4;
 
@@ -77,8 +81,9 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
 }
 
 template <int MT>  // MT m8 tiles: M <= 8 * MT
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(SmallmCfg<MT>::kThreads, 1)
 lut_smallm_mma_kernel(const SmallmParams p) {
+    constexpr int kThreads = SmallmCfg<MT>::kThreads, kWarps = SmallmCfg<MT>::kWarps, kBatch = SmallmCfg<MT>::kBatch;
     extern __shared__ __align__(128) uint8_t smem[];
     // [0, kHeader): one mbarrier per 16-row strip + abort flags | packed rows | x rows | fp32 output tile
     const uint32_t bar0 = smem_u32(smem);
@@ -361,7 +366,7 @@ int launch_lut_smallm_mma_multi(const GemvArgs* mats, int count, cudaStream_t st
         attr_smem[mt - 1][dev & 63] = 227 * 1024;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(mt == 1 ? SmallmCfg<1>::kThreads : SmallmCfg<2>::kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
