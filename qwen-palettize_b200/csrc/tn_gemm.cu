@@ -152,9 +152,13 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         if (item >= p.n_items) {
             job = (p.side[1].splits > 0 && item >= p.side[1].first_item) ? 1 : 0;
             const int r = item - p.side[job].first_item;
-            ti = PAIR ? (int)rank : 0;   // PAIR: the partner's 128 rows lie past the skinny operand: zeros in, nothing out
             tj = r % p.side[job].tiles_j;
             sp = r / p.side[job].tiles_j;
+            // PAIR: the operands change sides, D[big-matrix column, rank index]: the 256 rows of the pair are 256 columns of
+            // x / dY (all of them useful) and the skinny matrix is the 128-column N side (16 or 32 real columns), so an MMA costs
+            // half of what the 256-column shape with 240 padded rows would
+            ti = PAIR ? 2 * tj + (int)rank : 0;
+            if (PAIR) c_num = 128;
             return;
         }
         int t = item;
@@ -190,7 +194,8 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                 tile_coords(t, sp, ti, tj, c_off, c_num, job);
                 m_range(sp, job, m_begin, nkb);
                 const int c_mine = PAIR ? (c_num >> 1) : c_num;                  // j columns this CTA stages
-                const int j_mine = tj * 256 + c_off + (PAIR ? (int)rank * c_mine : 0);
+                const bool swapped = PAIR && job >= 0;                           // side item of a pair: skinny matrix on the N side
+                const int j_mine = swapped ? (int)rank * c_mine : tj * 256 + c_off + (PAIR ? (int)rank * c_mine : 0);
                 for (int it = 0; it < nkb; ++it, ++git) {
                     const int s = git % kStages;
                     const uint32_t ph = (git / kStages) & 1;
@@ -202,8 +207,10 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
                     if (!PAIR) mbar_arrive_expect_tx(full(s), kTnABytes + (uint32_t)c_num * 128u);
                     else if (rank == 0) mbar_arrive_expect_tx(full(s), 2u * (kTnABytes + (uint32_t)c_mine * 128u));
                     const int m = m_begin + it * 64;
-                    const CUtensorMap* mp = (job < 0) ? &tmP : (job == 0 ? &tmS0 : &tmS1);
-                    const CUtensorMap* mq = (job < 0) ? &tmQ : (p.side[job].q_is_p ? &tmP : &tmQ);
+                    const CUtensorMap* m_skinny = (job == 0) ? &tmS0 : &tmS1;
+                    const CUtensorMap* m_big = (job >= 0 && p.side[job].q_is_p) ? &tmP : &tmQ;
+                    const CUtensorMap* mp = (job < 0) ? &tmP : (swapped ? m_big : m_skinny);
+                    const CUtensorMap* mq = (job < 0) ? &tmQ : (swapped ? m_skinny : m_big);
                     if (PAIR) {
 #pragma unroll
                         for (int q = 0; q < 2; ++q) tma_load_2d_pair(sA + q * 8192u, mp, lead_full(s), ti * 128 + q * 64, m);
@@ -304,7 +311,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             const int wcols = c_num >> 1;  // columns per epilogue warp: 128, or 64 in a half tile
             const uint32_t trow = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * 256u + col_half * wcols;
             const bool row_ok = row < p.I;
-            const int colbase = tj * 256 + c_off + col_half * wcols;
+            const int colbase = (PAIR && job >= 0) ? col_half * wcols : tj * 256 + c_off + col_half * wcols;
 
             if (EPI == EPI_STORE || job >= 0) {
                 float* o_ptr = (job < 0) ? p.out : p.side[job].out;
@@ -726,6 +733,10 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
         sd.splits = (a.M + sd.m_chunk - 1) / sd.m_chunk;
         sd.out = a.side_out[b]; sd.out_si = a.side_si[b]; sd.out_sj = a.side_sj[b];
         sd.out_I = a.side_rank; sd.out_J = width;
+        if (pair) {   // the pair kernel computes the transposed product: D rows walk the big matrix's columns
+            sd.out_si = a.side_sj[b]; sd.out_sj = a.side_si[b];
+            sd.out_I = width; sd.out_J = a.side_rank;
+        }
     }
     if (a.epi != EPI_STORE) {
         // the last, partially filled round of the persistent schedule is cut into half tiles
