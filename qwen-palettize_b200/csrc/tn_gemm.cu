@@ -49,6 +49,11 @@ struct TnParams {
         float* out; long long out_si, out_sj;
     } side[2];
     int n_side_items;
+    // Tail of the persistent schedule. After the whole tiles come the half tiles (one per work unit, n_items - n_whole of
+    // them) and then the side items, which are dealt only to the units that did not get a half tile: tail slots that fall on
+    // a unit with a half tile stay empty, so that no unit carries a half tile AND a second side item while others idle.
+    // tail_free = units without a half tile (0: the side items simply follow the halves); n_total = items including holes.
+    int tail_free, n_total;
     // Fused reduce-scatter of dLogits over peer memory (rows = k layout only): weight row n belongs to rank
     // n / rows_per_rank; its gradient is stored into that rank's staging buffer, slot `rank`, instead of into `dlogits`.
     // scatter_add: the owner's buffer is one fp32 [rows_per_rank][K][4] accumulator (zeroed by its owner) and the partials
@@ -117,7 +122,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     const int n_units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const int tiles_i = PAIR ? (p.I + 255) / 256 : (p.I + 127) / 128;
     const int tiles_j = (p.J + 255) / 256;
-    const int n_tiles = p.n_items + p.n_side_items;
+    const int n_tiles = p.n_total;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -150,8 +155,17 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     auto tile_coords = [&](int item, int& sp, int& ti, int& tj, int& c_off, int& c_num, int& job) {
         c_off = 0; c_num = 256; job = -1;
         if (item >= p.n_items) {
-            job = (p.side[1].splits > 0 && item >= p.side[1].first_item) ? 1 : 0;
-            const int r = item - p.side[job].first_item;
+            // side item number: tail slots on units that hold a half tile are holes (job -2: the unit is done)
+            int sidx = item - p.n_items;
+            if (p.tail_free > 0) {
+                const int n_halves = p.n_items - p.n_whole;
+                const int rt = item - p.n_whole, slot = rt % n_units, round = rt / n_units;
+                if (slot < n_halves) { job = -2; sp = ti = tj = 0; return; }
+                sidx = round * p.tail_free + slot - n_halves;
+            }
+            if (sidx >= p.n_side_items) { job = -2; sp = ti = tj = 0; return; }
+            job = (p.side[1].splits > 0 && sidx >= p.side[1].first_item) ? 1 : 0;
+            const int r = sidx - p.side[job].first_item;
             tj = r % p.side[job].tiles_j;
             sp = r / p.side[job].tiles_j;
             // PAIR: the operands change sides, D[big-matrix column, rank index]: the 256 rows of the pair are 256 columns of
@@ -192,6 +206,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             for (int t = unit; t < n_tiles && ok; t += n_units) {
                 int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
                 tile_coords(t, sp, ti, tj, c_off, c_num, job);
+                if (job == -2) break;      // a hole of the tail: nothing more for this unit
                 m_range(sp, job, m_begin, nkb);
                 const int c_mine = PAIR ? (c_num >> 1) : c_num;                  // j columns this CTA stages
                 const bool swapped = PAIR && job >= 0;                           // side item of a pair: skinny matrix on the N side
@@ -259,6 +274,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
             for (int t = unit; t < n_tiles && ok; t += n_units, ++lt) {
                 int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
                 tile_coords(t, sp, ti, tj, c_off, c_num, job);
+                if (job == -2) break;
                 m_range(sp, job, m_begin, nkb);
                 const int buf = lt & 1;
                 const uint32_t idesc = make_idesc(PAIR ? 256 : 128, c_num, 1, 1);
@@ -302,6 +318,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
         for (int t = unit; t < n_tiles && ok; t += n_units, ++lt) {
             int sp, ti, tj, c_off, c_num, job, m_begin, nkb;
             tile_coords(t, sp, ti, tj, c_off, c_num, job);
+            if (job == -2) break;
             m_range(sp, job, m_begin, nkb);
             const int buf = lt & 1;
             ok = mbar_wait(acc_full(buf), (lt >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACCUM, 2);
@@ -744,15 +761,24 @@ int launch_tn_gemm(const TnArgs& a, cudaStream_t stream) {
         if (tiles > grid && rem > 0 && 2 * rem <= grid) { p.n_whole = tiles - rem; p.n_items = p.n_whole + 2 * rem; }
     }
     {
-        int next = p.n_items;
+        int next = 0;      // side items are numbered from 0
         for (int b = 0; b < 2; ++b) {
             p.side[b].first_item = next;
             next += p.side[b].splits * p.side[b].tiles_j * (p.side[b].splits > 0 ? 1 : 0);
         }
-        p.n_side_items = next - p.n_items;
+        p.n_side_items = next;
         if (p.side[0].splits == 0 && p.side[1].splits > 0) {
             // keep job 0 populated so that the item -> job mapping stays a simple threshold
-            p.side[0] = p.side[1]; tmS0 = tmS1; p.side[1].splits = 0; p.side[0].first_item = p.n_items;
+            p.side[0] = p.side[1]; tmS0 = tmS1; p.side[1].splits = 0; p.side[0].first_item = 0;
+        }
+        const int n_halves = p.n_items - p.n_whole;
+        p.tail_free = (n_halves > 0 && n_halves < grid && p.n_side_items > 0) ? grid - n_halves : 0;
+        if (p.tail_free > 0) {
+            const int full_rounds = p.n_side_items / p.tail_free, rest = p.n_side_items % p.tail_free;
+            const int tail_len = full_rounds * grid + (rest > 0 ? n_halves + rest : 0);
+            p.n_total = p.n_whole + (tail_len > n_halves ? tail_len : n_halves);
+        } else {
+            p.n_total = p.n_items + p.n_side_items;
         }
     }
     const int ctas = pair ? 2 * grid : grid;
