@@ -26,7 +26,7 @@ def _ref(q, k, v, do, B, S, Hq, Hkv, D):
     return back(o.detach(), Hq), lse.detach(), back(qf.grad, Hq), back(kf.grad, Hkv), back(vf.grad, Hkv)
 
 
-@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 1, 1), (2, 256, 4, 1), (1, 512, 8, 2), (3, 384, 4, 4)])
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 1, 1), (2, 256, 4, 1), (1, 512, 8, 2), (3, 384, 4, 4), (1, 1152, 2, 1)])
 def test_attention_forward_backward(B, S, Hq, Hkv):
     import plz_ops as ops
     D = 128
